@@ -1,0 +1,270 @@
+// Row-wise kernels of the decoder: embedding gather, residual add + RMSNorm,
+// row gather + RMSNorm for the logits rows, SiLU-gated product, rotary
+// embedding fused with the write of keys and values into the paged cache.
+//
+// Activations are float (32-bit path) or bfloat16; the residual stream, sums of
+// squares, rotation and SiLU are always computed in float.  Formulas follow the
+// reference's kernels (src/cuda/kernels/elementwise.cu:19-89,
+// src/cuda/kernels/rope_kv.cu:13-87) but the residual stream stays in float
+// here instead of being rounded to the activation type after every layer.
+#include "common.cuh"
+
+namespace rl {
+
+// ---------------------------------------------------------- token feed
+// ids[i] = src[i] >= 0 ? sampled[src[i]] : ids[i]: a decode token whose value is
+// still on the device (sampled by the step before, not yet read by the host) is
+// taken from that step's output (reference: elementwise.cu:12-16).
+__global__ void resolve_ids_kernel(int32_t* __restrict__ ids, const int32_t* __restrict__ src,
+                                   const int32_t* __restrict__ sampled, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n && src[i] >= 0) ids[i] = sampled[src[i]];
+}
+
+// ---------------------------------------------------------------- embedding
+// out[t, :] = float(table[ids[t], :]); `out` is the float residual stream.
+// A token id outside [0, vocab) sets bit 0 of *status and yields a zero row.
+template <typename TW>
+__global__ void embedding_kernel(const int32_t* __restrict__ ids, const TW* __restrict__ table,
+                                 float* __restrict__ out, int hidden, int vocab, int* status) {
+  const int t = blockIdx.x;
+  const int id = ids[t];
+  float* o = out + static_cast<size_t>(t) * hidden;
+  if (id < 0 || id >= vocab) {
+    if (threadIdx.x == 0) atomicOr(status, 1);
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) o[c] = 0.f;
+    return;
+  }
+  const TW* row = table + static_cast<size_t>(id) * hidden;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) o[c] = to_float(row[c]);
+}
+
+// ------------------------------------------------------- add + RMSNorm
+// residual[r, :] += delta[r, :] (if delta), then
+// out[r, :] = residual[r, :] * rsqrt(mean(residual^2) + eps) * w   (elementwise.cu:29-64).
+// `rows_idx` (optional) selects which rows are normalised: out row i comes from
+// row rows_idx[i] of residual (+ delta); the sum is then not written back (a row
+// may be asked for twice), which is what the logits rows after the last layer need.
+template <typename TA, typename TD, typename TW>
+__global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __restrict__ delta,
+                                   const TW* __restrict__ weight, TA* __restrict__ out,
+                                   const int32_t* __restrict__ rows_idx, int hidden, float eps) {
+  __shared__ float scratch[32];
+  const int r = blockIdx.x;
+  const int src = rows_idx ? rows_idx[r] : r;
+  float* res = residual + static_cast<size_t>(src) * hidden;
+  const TD* d = delta ? delta + static_cast<size_t>(src) * hidden : nullptr;
+  const bool write_back = (d != nullptr) && (rows_idx == nullptr);
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+    float v = res[c];
+    if (d) v += to_float(d[c]);
+    if (write_back) res[c] = v;
+    ss += v * v;
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = rsqrtf(ss / static_cast<float>(hidden) + eps);
+  TA* o = out + static_cast<size_t>(r) * hidden;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+    float v = res[c];
+    if (d && !write_back) v += to_float(d[c]);
+    o[c] = from_float<TA>(v * inv * to_float(weight[c]));
+  }
+}
+
+// residual[r, :] += delta[r, :] only (after the last layer when nothing follows).
+template <typename TD>
+__global__ void add_residual_kernel(float* __restrict__ residual, const TD* __restrict__ delta,
+                                    size_t n) {
+  const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i < n) residual[i] += to_float(delta[i]);
+}
+
+// --------------------------------------------------------------- SwiGLU
+// out[t, i] = silu(gu[t, i]) * gu[t, inter + i], silu(g) = g / (1 + exp(-g))
+// (elementwise.cu:66-82), computed in float and rounded once.
+template <typename TA>
+__global__ void swiglu_kernel(const TA* __restrict__ gu, TA* __restrict__ out, int inter) {
+  const int t = blockIdx.y;
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= inter) return;
+  const TA* row = gu + static_cast<size_t>(t) * 2 * inter;
+  const float g = to_float(row[i]);
+  const float u = to_float(row[inter + i]);
+  out[static_cast<size_t>(t) * inter + i] = from_float<TA>(g / (1.f + expf(-g)) * u);
+}
+
+// ------------------------------------------------------------- add bias
+template <typename TA, typename TW>
+__global__ void add_bias_kernel(TA* __restrict__ x, const TW* __restrict__ bias, int n, size_t total) {
+  const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i < total) x[i] = from_float<TA>(to_float(x[i]) + to_float(bias[i % n]));
+}
+
+// ------------------------------------------------- RoPE + paged KV write
+// qkv [T, (Hq + 2 Hkv) * D]: rotates every q and k head in place by the angle of
+// the token's position (pairs (i, i + D/2), cos/sin tables [max_pos, D/2] in
+// float: rope_kv.cu:26-51), then writes k and v of every kv head to the cache
+// slot of the token: page = slot / page_size, offset = slot % page_size, cache
+// layout [pages, Hkv, page_size, D] (rope_kv.cu:60-70).  A negative slot skips
+// the write (a call that reads another call's cache).  cos == nullptr: no rotation.
+template <typename TA>
+__global__ void rope_kv_write_kernel(TA* __restrict__ qkv, const int32_t* __restrict__ positions,
+                                     const int32_t* __restrict__ slots,
+                                     const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                     TA* __restrict__ kcache, TA* __restrict__ vcache, int hq, int hkv,
+                                     int d, int page_size, int max_pos, int* status) {
+  const int t = blockIdx.x;
+  const int half = d >> 1;
+  const int pos = positions[t];
+  TA* row = qkv + static_cast<size_t>(t) * (hq + 2 * hkv) * d;
+  const int slot = slots ? slots[t] : -1;
+  const bool bad_pos = (pos < 0 || pos >= max_pos);
+  if (bad_pos && threadIdx.x == 0) atomicOr(status, 2);
+  const float* c = cos_t ? cos_t + static_cast<size_t>(bad_pos ? 0 : pos) * half : nullptr;
+  const float* s = sin_t ? sin_t + static_cast<size_t>(bad_pos ? 0 : pos) * half : nullptr;
+  const size_t page = slot >= 0 ? slot / page_size : 0;
+  const int off = slot >= 0 ? slot % page_size : 0;
+  const int rot_heads = hq + hkv;
+  // one (head, pair) per thread-iteration over q and k heads
+  for (int idx = threadIdx.x; idx < rot_heads * half; idx += blockDim.x) {
+    const int h = idx / half, i = idx - h * half;
+    TA* v = row + h * d;
+    float x0 = to_float(v[i]), x1 = to_float(v[i + half]);
+    if (c) {
+      const float cc = c[i], sn = s[i];
+      const float y0 = x0 * cc - x1 * sn;
+      const float y1 = x1 * cc + x0 * sn;
+      x0 = y0;
+      x1 = y1;
+    }
+    const TA r0 = from_float<TA>(x0), r1 = from_float<TA>(x1);
+    v[i] = r0;
+    v[i + half] = r1;
+    if (h >= hq && slot >= 0) {
+      TA* dst = kcache + ((page * hkv + (h - hq)) * page_size + off) * d;
+      dst[i] = r0;
+      dst[i + half] = r1;
+    }
+  }
+  if (slot >= 0) {
+    const TA* vrow = row + (hq + hkv) * d;
+    for (int idx = threadIdx.x; idx < hkv * d; idx += blockDim.x) {
+      const int h = idx / d, i = idx - h * d;
+      vcache[((page * hkv + h) * page_size + off) * d + i] = vrow[idx];
+    }
+  }
+}
+
+}  // namespace rl
+
+using namespace rl;
+
+static inline int row_threads(int n) {
+  int t = 32;
+  while (t < n && t < 512) t <<= 1;
+  return t;
+}
+
+// dtype codes shared with the Python side: 0 = float32, 1 = bfloat16.
+#define RL_F32 0
+#define RL_BF16 1
+
+extern "C" {
+
+int rl_resolve_ids(int32_t* ids, const int32_t* src, const int32_t* sampled, int n, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  resolve_ids_kernel<<<(n + 255) / 256, 256, 0, stream>>>(ids, src, sampled, n);
+  RL_LAUNCH_END();
+}
+
+int rl_embedding(const int32_t* ids, const void* table, int table_dtype, float* out, int tokens,
+                 int hidden, int vocab, int* status, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  const int th = row_threads(hidden);
+  if (table_dtype == RL_F32) {
+    embedding_kernel<float><<<tokens, th, 0, stream>>>(ids, static_cast<const float*>(table), out,
+                                                       hidden, vocab, status);
+  } else {
+    embedding_kernel<bf16><<<tokens, th, 0, stream>>>(ids, static_cast<const bf16*>(table), out,
+                                                      hidden, vocab, status);
+  }
+  RL_LAUNCH_END();
+}
+
+// act_dtype: type of `delta` and `out`; w_dtype: type of `weight`.
+int rl_add_rmsnorm(float* residual, const void* delta, const void* weight, int w_dtype, void* out,
+                   int act_dtype, const int32_t* rows_idx, int rows, int hidden, float eps,
+                   cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  const int th = row_threads(hidden);
+#define RL_NORM_CASE(TA, TW)                                                                 \
+  add_rmsnorm_kernel<TA, TA, TW><<<rows, th, 0, stream>>>(                                   \
+      residual, static_cast<const TA*>(delta), static_cast<const TW*>(weight),               \
+      static_cast<TA*>(out), rows_idx, hidden, eps)
+  if (act_dtype == RL_F32 && w_dtype == RL_F32) RL_NORM_CASE(float, float);
+  else if (act_dtype == RL_F32) RL_NORM_CASE(float, bf16);
+  else if (w_dtype == RL_F32) RL_NORM_CASE(bf16, float);
+  else RL_NORM_CASE(bf16, bf16);
+#undef RL_NORM_CASE
+  RL_LAUNCH_END();
+}
+
+int rl_add_residual(float* residual, const void* delta, int act_dtype, long long n,
+                    cudaStream_t stream) {
+  if (n <= 0) return 0;
+  const int th = 256;
+  const unsigned blocks = static_cast<unsigned>((n + th - 1) / th);
+  if (act_dtype == RL_F32)
+    add_residual_kernel<float><<<blocks, th, 0, stream>>>(residual, static_cast<const float*>(delta), n);
+  else
+    add_residual_kernel<bf16><<<blocks, th, 0, stream>>>(residual, static_cast<const bf16*>(delta), n);
+  RL_LAUNCH_END();
+}
+
+int rl_swiglu(const void* gu, void* out, int act_dtype, int tokens, int inter, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  const int th = 256;
+  dim3 grid((inter + th - 1) / th, tokens);
+  if (act_dtype == RL_F32)
+    swiglu_kernel<float><<<grid, th, 0, stream>>>(static_cast<const float*>(gu), static_cast<float*>(out), inter);
+  else
+    swiglu_kernel<bf16><<<grid, th, 0, stream>>>(static_cast<const bf16*>(gu), static_cast<bf16*>(out), inter);
+  RL_LAUNCH_END();
+}
+
+int rl_add_bias(void* x, int act_dtype, const void* bias, int b_dtype, int rows, int n,
+                cudaStream_t stream) {
+  const size_t total = static_cast<size_t>(rows) * n;
+  if (total == 0) return 0;
+  const int th = 256;
+  const unsigned blocks = static_cast<unsigned>((total + th - 1) / th);
+#define RL_BIAS_CASE(TA, TW)                                                               \
+  add_bias_kernel<TA, TW><<<blocks, th, 0, stream>>>(static_cast<TA*>(x),                  \
+                                                     static_cast<const TW*>(bias), n, total)
+  if (act_dtype == RL_F32 && b_dtype == RL_F32) RL_BIAS_CASE(float, float);
+  else if (act_dtype == RL_F32) RL_BIAS_CASE(float, bf16);
+  else if (b_dtype == RL_F32) RL_BIAS_CASE(bf16, float);
+  else RL_BIAS_CASE(bf16, bf16);
+#undef RL_BIAS_CASE
+  RL_LAUNCH_END();
+}
+
+int rl_rope_kv_write(void* qkv, int act_dtype, const int32_t* positions, const int32_t* slots,
+                     const float* cos_t, const float* sin_t, void* kcache, void* vcache, int tokens,
+                     int hq, int hkv, int d, int page_size, int max_pos, int* status,
+                     cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  const int th = 256;
+  if (act_dtype == RL_F32)
+    rope_kv_write_kernel<float><<<tokens, th, 0, stream>>>(
+        static_cast<float*>(qkv), positions, slots, cos_t, sin_t, static_cast<float*>(kcache),
+        static_cast<float*>(vcache), hq, hkv, d, page_size, max_pos, status);
+  else
+    rope_kv_write_kernel<bf16><<<tokens, th, 0, stream>>>(
+        static_cast<bf16*>(qkv), positions, slots, cos_t, sin_t, static_cast<bf16*>(kcache),
+        static_cast<bf16*>(vcache), hq, hkv, d, page_size, max_pos, status);
+  RL_LAUNCH_END();
+}
+
+}  // extern "C"

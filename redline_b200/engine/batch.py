@@ -1,0 +1,304 @@
+"""Turns the segments of one step into ONE flat int32 buffer in pinned host memory,
+uploads it with one copy, and hands the model typed device views of it.
+
+A segment is (request cache, its next tokens, the position of the first of them,
+which of them want logits).  Segments of one token go to the decode work list,
+longer ones are cut into tiles of 32 query rows for the prefill kernel.  The
+buffer holds, in this order (sizes in int32 words; T tokens, S segments, R rows,
+G cache groups, B block-table width, L tiles):
+
+    token_ids[T] token_src[T] positions[T] seq_of_token[T]
+    slots[G][T] block_table[G][S*B]
+    state_slot[S] decode_tok[S] tile_seq[L] tile_tok[L] tile_rows[L]
+    logit_rows[R] temperature[R] top_k[R] top_p[R] seed_lo[R] seed_hi[R] sample_pos[R]
+
+(the reference's layout: src/core/batch_builder.cpp:17-46; one upload:
+src/cuda/engine/engine.cpp:267-278).  The layout depends only on the capacities
+(T, S, R, L), so a fixed-shape decode batch has the same device addresses every
+time and can be replayed as a CUDA graph.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache.manager import CacheManager, RequestCache
+from ..ops.kernels import DECODE_PARTITION, PREFILL_TILE_ROWS
+
+
+@dataclass
+class RowSampling:
+    """Sampling parameters of one logits row (sampling/params.py: SamplingParams)."""
+
+    temperature: float = 0.0
+    top_k: int = 0
+    top_p: float = 1.0
+    seed: int = 0
+
+
+@dataclass
+class Segment:
+    cache: RequestCache
+    tokens: Sequence[int]          # the segment's token ids (ignored where src_row >= 0)
+    start_pos: int                 # position of tokens[0]
+    want: Sequence[int] = ()       # indices into tokens whose logits are wanted
+    src_row: int = -1              # >= 0: the single token is row src_row of the previous step's samples
+    sampling: Optional[RowSampling] = None   # applies to every wanted row of the segment
+
+
+@dataclass
+class GroupView:
+    slots: torch.Tensor         # [T] cache slot of every token in this group (-1: none)
+    block_table: torch.Tensor   # [S, B]
+
+
+class Layout:
+    def __init__(self, T: int, S: int, R: int, L: int, G: int, B: int):
+        self.T, self.S, self.R, self.L, self.G, self.B = T, S, R, L, G, B
+        off = 0
+
+        def take(n: int) -> int:
+            nonlocal off
+            o = off
+            off += n
+            return o
+
+        self.token_ids = take(T)
+        self.token_src = take(T)
+        self.positions = take(T)
+        self.seq_of_token = take(T)
+        self.slots = [take(T) for _ in range(G)]
+        self.block_table = [take(S * B) for _ in range(G)]
+        self.state_slot = take(S)
+        self.decode_tok = take(S)
+        self.tile_seq = take(L)
+        self.tile_tok = take(L)
+        self.tile_rows = take(L)
+        self.logit_rows = take(R)
+        self.temperature = take(R)
+        self.top_k = take(R)
+        self.top_p = take(R)
+        self.seed_lo = take(R)
+        self.seed_hi = take(R)
+        self.sample_pos = take(R)
+        self.words = off
+
+
+@dataclass
+class StepContext:
+    """Device views of one step's metadata plus the host numbers kernels need for
+    their grids.  ``host`` keeps the numpy arrays for parts that work on the host side
+    (test parts) and for debugging."""
+
+    T: int
+    S: int
+    R: int
+    num_decode: int
+    num_tiles: int
+    decode_parts: int        # partitions per decode item in this launch
+    max_items: int           # capacity of the decode workspace in items
+    parts_capacity: int      # capacity of the decode workspace in partitions per item
+    token_ids: torch.Tensor
+    token_src: torch.Tensor
+    positions: torch.Tensor
+    seq_of_token: torch.Tensor
+    state_slot: torch.Tensor
+    decode_tok: torch.Tensor
+    tile_seq: torch.Tensor
+    tile_tok: torch.Tensor
+    tile_rows: torch.Tensor
+    logit_rows: torch.Tensor
+    temperature: torch.Tensor
+    top_k: torch.Tensor
+    top_p: torch.Tensor
+    seed_lo: torch.Tensor
+    seed_hi: torch.Tensor
+    sample_pos: torch.Tensor
+    groups: List[GroupView]
+    status: torch.Tensor
+    has_src: bool = False
+    any_sampling: bool = False
+    host: Optional["HostBatch"] = None
+
+
+@dataclass
+class HostBatch:
+    q_start: List[int] = field(default_factory=list)
+    q_len: List[int] = field(default_factory=list)
+    start_pos: List[int] = field(default_factory=list)
+    state_slot: List[int] = field(default_factory=list)
+    keys: List[object] = field(default_factory=list)
+
+
+class BatchBuilder:
+    def __init__(self, cache: CacheManager, max_tokens: int, max_seqs: int, max_rows: int,
+                 max_seq_len: int, device: torch.device):
+        self.cache = cache
+        self.G = len(cache.groups)
+        self.page_size = cache.page_size
+        self.max_tokens, self.max_seqs, self.max_rows = max_tokens, max_seqs, max_rows
+        self.max_seq_len = max_seq_len
+        self.B = cache.blocks_for(max_seq_len)
+        self.max_tiles = (max_tokens + PREFILL_TILE_ROWS - 1) // PREFILL_TILE_ROWS + max_seqs
+        self.parts_capacity = (max_seq_len + DECODE_PARTITION - 1) // DECODE_PARTITION
+        cap = Layout(max_tokens, max_seqs, max_rows, self.max_tiles, self.G, self.B)
+        self.device = device
+        self.capacity_words = cap.words
+        on_gpu = device.type == "cuda"
+        self.num_slots = 4
+        self.host_bufs = [torch.zeros(cap.words, dtype=torch.int32, pin_memory=on_gpu) for _ in range(self.num_slots)]
+        self.host_np = [b.numpy() for b in self.host_bufs]
+        self.events = [torch.cuda.Event() if on_gpu else None for _ in range(self.num_slots)]
+        self.used = [False] * self.num_slots
+        self.dev_buf = torch.zeros(cap.words, dtype=torch.int32, device=device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        self._turn = 0
+
+    def _views(self, lay: Layout, dev: torch.Tensor, T: int, S: int, R: int, L: int) -> dict:
+        def v(off, n):
+            return dev[off:off + n]
+
+        f32 = lambda off, n: dev[off:off + n].view(torch.float32)  # noqa: E731
+        return dict(
+            token_ids=v(lay.token_ids, lay.T), token_src=v(lay.token_src, lay.T),
+            positions=v(lay.positions, lay.T), seq_of_token=v(lay.seq_of_token, lay.T),
+            state_slot=v(lay.state_slot, lay.S), decode_tok=v(lay.decode_tok, lay.S),
+            tile_seq=v(lay.tile_seq, lay.L), tile_tok=v(lay.tile_tok, lay.L), tile_rows=v(lay.tile_rows, lay.L),
+            logit_rows=v(lay.logit_rows, lay.R), temperature=f32(lay.temperature, lay.R),
+            top_k=v(lay.top_k, lay.R), top_p=f32(lay.top_p, lay.R), seed_lo=v(lay.seed_lo, lay.R),
+            seed_hi=v(lay.seed_hi, lay.R), sample_pos=v(lay.sample_pos, lay.R),
+            groups=[GroupView(v(lay.slots[g], lay.T), v(lay.block_table[g], lay.S * lay.B).view(lay.S, lay.B))
+                    for g in range(self.G)],
+        )
+
+    def build(self, segments: Sequence[Segment], pad_to: int = 0) -> StepContext:
+        """Fills a pinned buffer, uploads it, returns the context.  ``pad_to`` > 0 (only
+        for steps of single tokens that all want their logits) pads the batch with dummy
+        one-token sequences on page 0 up to that many, so the shape is fixed."""
+        S_real = len(segments)
+        T_real = sum(len(s.tokens) for s in segments)
+        R_real = sum(len(s.want) for s in segments)
+        if S_real == 0 or T_real == 0:
+            raise ValueError("a step needs at least one token")
+        if S_real > self.max_seqs or T_real > self.max_tokens or R_real > self.max_rows:
+            raise ValueError(f"step of {T_real} tokens, {S_real} sequences, {R_real} logits rows exceeds the "
+                             f"engine's limits ({self.max_tokens}, {self.max_seqs}, {self.max_rows})")
+        ps = self.page_size
+        tiles = []
+        for si, s in enumerate(segments):
+            n = len(s.tokens)
+            if n > 1:
+                tiles.append((si, n))
+        L_real = sum((n + PREFILL_TILE_ROWS - 1) // PREFILL_TILE_ROWS for _, n in tiles)
+        if pad_to:
+            T = S = R = pad_to
+            L = 0
+        else:
+            T, S, R, L = T_real, S_real, R_real, L_real
+        lay = Layout(T, S, R, L, self.G, self.B)
+
+        slot = self._turn % self.num_slots
+        self._turn += 1
+        if self.used[slot] and self.events[slot] is not None:
+            self.events[slot].synchronize()
+        h = self.host_np[slot]
+        h[:lay.words] = 0
+        hb = HostBatch()
+        t = 0
+        r = 0
+        nd = 0
+        li = 0
+        has_src = False
+        any_sampling = False
+        max_ctx = 1
+        for si, s in enumerate(segments):
+            n = len(s.tokens)
+            end = s.start_pos + n
+            if n <= 0:
+                raise ValueError("empty segment")
+            if end > self.max_seq_len:
+                raise ValueError(f"request {s.cache.key!r} would reach position {end}, beyond max_seq_len "
+                                 f"{self.max_seq_len}")
+            if s.src_row >= 0:
+                if n != 1:
+                    raise ValueError("a device-fed segment has exactly one token")
+                h[lay.token_src + t] = s.src_row
+                has_src = True
+            else:
+                h[lay.token_ids + t:lay.token_ids + t + n] = np.asarray(s.tokens, dtype=np.int32)
+                h[lay.token_src + t:lay.token_src + t + n] = -1
+            pos = np.arange(s.start_pos, end, dtype=np.int32)
+            h[lay.positions + t:lay.positions + t + n] = pos
+            h[lay.seq_of_token + t:lay.seq_of_token + t + n] = si
+            for g in range(self.G):
+                table = s.cache.tables[g]
+                if len(table) * ps < end:
+                    raise ValueError(f"request {s.cache.key!r}: pages reserved for {len(table) * ps} positions, "
+                                     f"step needs {end}")
+                tb = np.asarray(table, dtype=np.int32)
+                h[lay.slots[g] + t:lay.slots[g] + t + n] = tb[pos // ps] * ps + pos % ps
+                o = lay.block_table[g] + si * self.B
+                h[o:o + len(tb)] = tb
+            h[lay.state_slot + si] = s.cache.state_slot
+            if n == 1:
+                h[lay.decode_tok + nd] = t
+                nd += 1
+                max_ctx = max(max_ctx, end)
+            else:
+                for r0 in range(0, n, PREFILL_TILE_ROWS):
+                    h[lay.tile_seq + li] = si
+                    h[lay.tile_tok + li] = t + r0
+                    h[lay.tile_rows + li] = min(PREFILL_TILE_ROWS, n - r0)
+                    li += 1
+            sp = s.sampling
+            for wi in s.want:
+                if not 0 <= wi < n:
+                    raise ValueError(f"wanted index {wi} outside a segment of {n} tokens")
+                h[lay.logit_rows + r] = t + wi
+                if sp is not None:
+                    any_sampling = True
+                    h[lay.temperature + r:lay.temperature + r + 1].view(np.float32)[0] = sp.temperature
+                    h[lay.top_k + r] = sp.top_k
+                    h[lay.top_p + r:lay.top_p + r + 1].view(np.float32)[0] = sp.top_p
+                    h[lay.seed_lo + r:lay.seed_lo + r + 1].view(np.uint32)[0] = sp.seed & 0xFFFFFFFF
+                    h[lay.seed_hi + r:lay.seed_hi + r + 1].view(np.uint32)[0] = (sp.seed >> 32) & 0xFFFFFFFF
+                else:
+                    h[lay.top_p + r:lay.top_p + r + 1].view(np.float32)[0] = 1.0
+                h[lay.sample_pos + r] = s.start_pos + wi + 1  # position of the token being drawn
+                r += 1
+            hb.q_start.append(t)
+            hb.q_len.append(n)
+            hb.start_pos.append(s.start_pos)
+            hb.state_slot.append(s.cache.state_slot)
+            hb.keys.append(s.cache.key)
+            t += n
+        if pad_to:
+            if nd != S_real or R_real != S_real or T_real != S_real:
+                raise ValueError("only steps of single tokens that all want logits can be padded")
+            # dummy rows: token 0 at position 0 of a sequence whose table is all page 0
+            for i in range(S_real, pad_to):
+                h[lay.token_src + i] = -1
+                h[lay.seq_of_token + i] = i
+                h[lay.decode_tok + i] = i
+                h[lay.logit_rows + i] = i
+                h[lay.top_p + i:lay.top_p + i + 1].view(np.float32)[0] = 1.0
+                h[lay.sample_pos + i] = 1
+            nd = pad_to
+            decode_parts = self.parts_capacity
+        else:
+            decode_parts = (max_ctx + DECODE_PARTITION - 1) // DECODE_PARTITION
+        dev = self.dev_buf
+        if self.device.type == "cuda":
+            dev[:lay.words].copy_(self.host_bufs[slot][:lay.words], non_blocking=True)
+            self.events[slot].record()
+            self.used[slot] = True
+        else:
+            dev[:lay.words].copy_(self.host_bufs[slot][:lay.words])
+        views = self._views(lay, dev, T, S, R, L)
+        return StepContext(T=T, S=S, R=R, num_decode=nd, num_tiles=li, decode_parts=decode_parts,
+                           max_items=self.max_seqs, parts_capacity=self.parts_capacity, status=self.status,
+                           has_src=has_src, any_sampling=any_sampling, host=hb, **views)

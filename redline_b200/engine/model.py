@@ -1,0 +1,126 @@
+"""A decoder put together from a ``ModelSpec``: embedding, blocks run in the order
+the spec lists (an entry may name a layer twice, or read an earlier entry's cache),
+final norm on the rows whose logits are wanted, head.  The forward pass is the
+reference's (src/cuda/model/llama.cpp:56-151) with the residual stream in float32
+and the final norm applied to the wanted rows only.
+"""
+
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+from ..cache.manager import GroupInfo
+from ..parts import base as parts_base
+from ..parts.base import Block, Runtime, build_part, lookup
+from ..parts.spec import CacheSpec, ModelSpec, StateSpec, TensorSpec
+from ..weights import loader
+from ..weights.safetensors_io import CheckpointReader
+
+
+class DecoderModel:
+    def __init__(self, spec: ModelSpec, rt: Runtime):
+        self.spec, self.rt = spec, rt
+        self.embedding = build_part("embedding", spec.embedding, rt)
+        self.blocks: List[Block] = []
+        for ls in spec.layers:
+            block_cls = lookup("block", ls.arrangement)
+            self.blocks.append(block_cls(build_part("norm", ls.mixer_norm, rt), build_part("mixer", ls.mixer, rt),
+                                         build_part("norm", ls.ffn_norm, rt), build_part("ffn", ls.ffn, rt), rt))
+        self.final_norm = build_part("norm", spec.final_norm, rt)
+        self.head = build_part("head", spec.head, rt)
+        self._check_order()
+
+    # -------------------------------------------------------------- layout
+    def _check_order(self) -> None:
+        for i, call in enumerate(self.spec.order):
+            if not 0 <= call.layer < len(self.blocks):
+                raise ValueError(f"run order entry {i} names layer {call.layer} of {len(self.blocks)}")
+            if call.cache_of is not None:
+                if not 0 <= call.cache_of < i:
+                    raise ValueError(f"run order entry {i} reads the cache of entry {call.cache_of}, "
+                                     "which does not come before it")
+                if self.spec.order[call.cache_of].cache_of is not None:
+                    raise ValueError(f"run order entry {i} reads the cache of entry {call.cache_of}, "
+                                     "which owns none")
+                a = self.blocks[call.layer].mixer.cache_spec()
+                b = self.blocks[self.spec.order[call.cache_of].layer].mixer.cache_spec()
+                if a is None or b is None or a.group_key() != b.group_key():
+                    raise ValueError(f"run order entry {i} cannot read the cache of entry {call.cache_of}: "
+                                     "the two mixers need different caches")
+
+    def cache_groups(self) -> List[GroupInfo]:
+        """Groups of cache-owning run-order entries whose mixers need the same cache."""
+        groups: Dict[Tuple, GroupInfo] = {}
+        for i, call in enumerate(self.spec.order):
+            if call.cache_of is not None:
+                continue
+            cs = self.blocks[call.layer].mixer.cache_spec()
+            if cs is None:
+                continue
+            groups.setdefault(cs.group_key(), GroupInfo(cs)).owners.append(i)
+        return list(groups.values())
+
+    def state_specs(self) -> Dict[int, StateSpec]:
+        out = {}
+        for i, call in enumerate(self.spec.order):
+            ss = self.blocks[call.layer].mixer.state_spec()
+            if ss is not None:
+                out[i] = ss
+        return out
+
+    # ------------------------------------------------------------- weights
+    def _named_parts(self):
+        yield self.embedding
+        for b in self.blocks:
+            yield from b.parts()
+        yield self.final_norm
+        yield self.head
+
+    def expected_tensors(self) -> Dict[str, TensorSpec]:
+        exp: Dict[str, TensorSpec] = {}
+        for part in self._named_parts():
+            for local, ts in part.tensors().items():
+                name = part.spec.names.get(local)
+                if name is None:
+                    if ts.optional:
+                        continue
+                    raise ValueError(f"part '{part.spec.kind}' has no checkpoint name for its tensor '{local}'")
+                exp[name] = ts
+        return exp
+
+    def load_weights(self, reader: CheckpointReader) -> None:
+        rt = self.rt
+        tensors = loader.load(reader, self.expected_tensors(), rt.dtype, rt.device)
+        for part in self._named_parts():
+            mine = {}
+            for local in part.tensors():
+                name = part.spec.names.get(local)
+                if name is not None and name in tensors:
+                    mine[local] = tensors[name]
+            part.load(mine)
+        if getattr(self.head, "weight", None) is None:
+            # no head tensor in use: the head shares the embedding table
+            self.head.tie(self.embedding.table())
+
+    def weight_bytes(self) -> int:
+        return sum(p.nbytes() for p in self._named_parts())
+
+    # ------------------------------------------------------------- forward
+    def forward(self, ctx, caches, states, logits: torch.Tensor) -> torch.Tensor:
+        """Runs the step's tokens; returns logits[:R] (float32) at the wanted rows.
+        ``caches[i]`` / ``states[i]`` belong to run-order entry i (None where unused)."""
+        rt = self.rt
+        T, R = ctx.T, ctx.R
+        ws = rt.workspace
+        residual = ws.get("residual", (rt.max_tokens, self.spec.hidden_size), torch.float32)[:T]
+        self.embedding.forward(ctx, residual)
+        pending = None
+        for i, call in enumerate(self.spec.order):
+            pending = self.blocks[call.layer].forward(residual, pending, ctx, caches[i], states[i])
+        if R > 0:
+            xr = ws.get("head.in", (logits.shape[0], self.spec.hidden_size), rt.dtype)[:R]
+            self.final_norm.add_norm(residual, pending, xr, rows_idx=ctx.logit_rows, rows=R)
+            self.head.forward(xr, R, logits)
+        return logits[:R]

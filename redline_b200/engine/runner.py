@@ -1,0 +1,185 @@
+"""The step function: runs one batch of (request, its next tokens) from the cache
+and returns float32 logits at the wanted places.
+
+``ModelRunner`` owns the model, the cache manager with its device memory, the batch
+builder and the sampler.  ``run`` takes segments cut anywhere (portions of prompts
+beside single decoded tokens), runs only those tokens, and leaves their keys and
+values in the cache for later steps.  The scheduler-driven engine and the trace
+replay program both drive this one function (reference: Engine::launch_step and
+forward_and_sample, src/cuda/engine/engine.cpp:280-295,420-483).
+"""
+
+from __future__ import annotations
+
+import os
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from ..cache.manager import CacheManager, GroupInfo, RequestCache
+from ..cache.storage import CacheStorage, StateStorage, bytes_per_page
+from ..config.engine_config import EngineConfig
+from ..config.model_config import ModelConfig
+from ..config.registry import load_config, model_spec
+from ..ops import kernels
+from ..parts.base import Runtime
+from ..parts.spec import ModelSpec
+from ..sampling.sampler import Sampler
+from ..weights.safetensors_io import CheckpointReader
+from .batch import BatchBuilder, Segment, StepContext
+from .model import DecoderModel
+
+GRAPH_BUCKETS = (1, 2, 4, 8, 12, 16, 24, 32, 48, 64, 96, 128, 160, 192, 256)
+STATUS_MESSAGES = {1: "a token id outside the vocabulary", 2: "a position beyond the rotary table"}
+
+
+class EngineError(RuntimeError):
+    pass
+
+
+def require_cuda(device_index: int) -> torch.device:
+    if not torch.cuda.is_available():
+        raise EngineError("redline_b200 needs a CUDA device (B200, sm_100a); there is no CPU fallback")
+    return torch.device("cuda", device_index)
+
+
+class ModelRunner:
+    def __init__(self, cfg: EngineConfig, model_config: Optional[ModelConfig] = None,
+                 spec: Optional[ModelSpec] = None):
+        cfg.validate()
+        self.cfg = cfg
+        self.device = require_cuda(cfg.device)
+        torch.cuda.set_device(self.device)
+        self.model_config = model_config or load_config(cfg.model)
+        self.spec = spec or model_spec(self.model_config)
+        self.dtype = cfg.torch_dtype
+        self.max_seq_len = cfg.max_seq_len
+        self.rt = Runtime(device=self.device, dtype=self.dtype, max_tokens=cfg.max_num_batched_tokens,
+                          max_seqs=cfg.max_num_seqs, max_seq_len=cfg.max_seq_len, page_size=cfg.block_size)
+        self.model = DecoderModel(self.spec, self.rt)
+        self.model.load_weights(CheckpointReader(cfg.model))
+        self.vocab_size = self.spec.vocab_size
+
+        self.max_rows = cfg.logit_rows
+        self.logits = torch.zeros((self.max_rows, self.vocab_size), dtype=torch.float32, device=self.device)
+        self.sampler = Sampler(self.max_rows, self.device)
+
+        self.groups: List[GroupInfo] = self.model.cache_groups()
+        pages = self._size_cache()
+        self.cache = CacheManager(self.groups, pages, cfg.block_size, num_state_slots=cfg.max_num_seqs)
+        self.storage = CacheStorage(self.groups, pages, cfg.block_size, self.dtype, self.device)
+        self.states = StateStorage(self.model.state_specs(), cfg.max_num_seqs, self.device)
+        if self.states.pools:   # a fresh request starts from zero state
+            self.cache.on_open = lambda rc: self.states.reset_slot(rc.state_slot)
+        self.builder = BatchBuilder(self.cache, cfg.max_num_batched_tokens, cfg.max_num_seqs, self.max_rows,
+                                    cfg.max_seq_len, self.device)
+        order = self.spec.order
+        self._caches = []
+        for i, call in enumerate(order):
+            if self.model.blocks[call.layer].mixer.cache_spec() is None:
+                self._caches.append(None)
+            elif call.cache_of is None:
+                self._caches.append(self.storage.of_owner(i, True))
+            else:
+                self._caches.append(self.storage.of_owner(call.cache_of, False))
+        self._states = [self.states.of_call(i) for i in range(len(order))]
+        self._graphs: Dict[int, torch.cuda.CUDAGraph] = {}
+        self.num_graph_steps = 0
+        self.num_eager_steps = 0
+
+    # ---------------------------------------------------------------- sizing
+    def _size_cache(self) -> List[int]:
+        cfg = self.cfg
+        ps = cfg.block_size
+        elem = torch.empty((), dtype=self.dtype).element_size()
+        per_page = bytes_per_page(self.groups, ps, elem)
+        need_one = (cfg.max_seq_len + ps - 1) // ps
+        if cfg.kv_cache_tokens > 0:
+            n = (cfg.kv_cache_tokens + ps - 1) // ps
+        else:
+            free, total = torch.cuda.mem_get_info(self.device)
+            budget = int(cfg.gpu_memory_utilization * total) - (total - free) - (1 << 30)
+            n = max(budget, 0) // max(sum(per_page), 1)
+            n = min(n, cfg.max_num_seqs * need_one)
+            if n < need_one:
+                raise EngineError(f"the memory budget holds {n} pages; one sequence of max_seq_len="
+                                  f"{cfg.max_seq_len} needs {need_one}")
+        return [n + 1 for _ in self.groups]   # + the reserved page 0
+
+    # -------------------------------------------------------------- requests
+    def open(self, key: object) -> RequestCache:
+        return self.cache.open(key)
+
+    def close(self, key: object) -> None:
+        self.cache.close(key)
+
+    # ------------------------------------------------------------------ step
+    def run(self, segments: Sequence[Segment], sample: bool = False, allow_graph: bool = True
+            ) -> Tuple[torch.Tensor, StepContext]:
+        """Runs the segments as one batch.  Pages for every position touched must have
+        been reserved.  Returns (logits[:R], ctx); with ``sample`` the sampler's
+        ``tokens[:R]`` / ``logprobs[:R]`` are filled too.  A segment with ``src_row`` >= 0
+        takes its token from that row of the sampler's tokens as the previous step left them."""
+        bucket = self._graph_bucket(segments) if (allow_graph and self.cfg.cuda_graphs and sample) else 0
+        ctx = self.builder.build(segments, pad_to=bucket)
+        if bucket:
+            g = self._graphs.get(bucket)
+            if g is None:
+                g = self._capture(bucket, ctx)
+            else:
+                g.replay()
+            self.num_graph_steps += 1
+        else:
+            self._forward(ctx, sample, ctx.has_src)
+            self.num_eager_steps += 1
+        return self.logits[:ctx.R], ctx
+
+    def _forward(self, ctx: StepContext, sample: bool, resolve: bool) -> None:
+        if resolve:
+            kernels.resolve_ids(ctx.token_ids, ctx.token_src, self.sampler.tokens, ctx.T)
+        self.model.forward(ctx, self._caches, self._states, self.logits)
+        if sample and ctx.R > 0:
+            self.sampler.sample(self.logits, ctx)
+
+    def _graph_bucket(self, segments: Sequence[Segment]) -> int:
+        n = len(segments)
+        for s in segments:
+            if len(s.tokens) != 1 or len(s.want) != 1:
+                return 0
+        for b in GRAPH_BUCKETS:
+            if n <= b <= self.cfg.max_num_seqs:
+                return b
+        return 0
+
+    def _capture(self, bucket: int, ctx: StepContext) -> torch.cuda.CUDAGraph:
+        # The graph always resolves device-fed ids (token_src is -1 where there are none),
+        # so one graph serves steps with and without them.  The step runs once eagerly
+        # (compiles kernels, sizes workspaces), is captured, and the first replay runs it
+        # again: every kernel of a step gives the same result when repeated.
+        fed = self.sampler.tokens.clone()       # the warm-up run overwrites what the step reads
+        self._forward(ctx, True, True)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self._forward(ctx, True, True)
+        self._graphs[bucket] = g
+        self.sampler.tokens.copy_(fed)
+        g.replay()
+        return g
+
+    def check_status(self) -> None:
+        """Raises if a kernel flagged bad input since the last check (synchronises)."""
+        code = int(self.builder.status.item())
+        if code:
+            self.builder.status.zero_()
+            what = [m for bit, m in STATUS_MESSAGES.items() if code & bit]
+            raise EngineError("a kernel met " + " and ".join(what))
+
+    def memory_report(self) -> Dict[str, int]:
+        return {
+            "weights": self.model.weight_bytes(),
+            "kv_cache": self.storage.nbytes(),
+            "state": self.states.nbytes(),
+            "activations": self.rt.workspace.nbytes() + self.logits.numel() * 4,
+            "metadata": self.builder.capacity_words * 4,
+        }

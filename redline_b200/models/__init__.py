@@ -1,0 +1,3 @@
+"""Built-in architectures; importing this package registers them."""
+
+from . import llama  # noqa: F401

@@ -1,0 +1,237 @@
+"""ctypes bindings of the package's CUDA kernels, taking torch tensors.
+
+Every function launches on torch's current stream and raises ``KernelError`` when
+the launch fails.  There is no CPU fallback: without a CUDA device or without the
+compiled extension these functions raise.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_uint, c_void_p
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from . import build
+
+DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_libs: Dict[Tuple, ctypes.CDLL] = {}
+
+
+def _lib(name: str, source: str, defines: Optional[Dict[str, object]] = None) -> ctypes.CDLL:
+    key = (name, source, tuple(sorted((defines or {}).items())))
+    lib = _libs.get(key)
+    if lib is None:
+        path = build.compile_module(name, source, defines)
+        lib = ctypes.CDLL(path)
+        _libs[key] = lib
+    return lib
+
+
+def _fn(lib: ctypes.CDLL, name: str, argtypes):
+    f = getattr(lib, name)
+    if f.argtypes is None:
+        f.argtypes = argtypes
+        f.restype = c_int
+    return f
+
+
+def _stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(t: Optional[torch.Tensor]) -> c_void_p:
+    return c_void_p(0 if t is None else t.data_ptr())
+
+
+def _check(code: int, what: str) -> None:
+    if code != 0:
+        raise KernelError(f"{what}: CUDA error {code}")
+
+
+def _code(dtype: torch.dtype) -> int:
+    try:
+        return DTYPE_CODE[dtype]
+    except KeyError:
+        raise KernelError(f"dtype {dtype} is not supported (float32, bfloat16)") from None
+
+
+def _need_cuda(*ts: Optional[torch.Tensor]) -> None:
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise KernelError("redline_b200 kernels run on CUDA tensors only; there is no CPU fallback")
+
+
+# ------------------------------------------------------------------ elementwise
+
+def _ew() -> ctypes.CDLL:
+    return _lib("elementwise", "elementwise.cu")
+
+
+def resolve_ids(ids: torch.Tensor, src: torch.Tensor, sampled: torch.Tensor, n: int) -> None:
+    """ids[i] = sampled[src[i]] where src[i] >= 0."""
+    _need_cuda(ids, src, sampled)
+    f = _fn(_ew(), "rl_resolve_ids", [c_void_p, c_void_p, c_void_p, c_int, c_void_p])
+    _check(f(_ptr(ids), _ptr(src), _ptr(sampled), n, _stream()), "resolve_ids")
+
+
+def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, status: torch.Tensor) -> None:
+    """out[t] = float(table[ids[t]]); out is the float32 residual stream [T, H]."""
+    _need_cuda(ids, table, out)
+    f = _fn(_ew(), "rl_embedding", [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p])
+    _check(f(_ptr(ids), _ptr(table), _code(table.dtype), _ptr(out), ids.numel(), table.shape[1],
+             table.shape[0], _ptr(status), _stream()), "embedding")
+
+
+def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor,
+                out: torch.Tensor, eps: float, rows_idx: Optional[torch.Tensor] = None,
+                rows: Optional[int] = None) -> None:
+    """residual += delta (if given); out = rmsnorm(residual) * weight.  With
+    ``rows_idx`` only those rows are normalised (out row i <- row rows_idx[i]) and
+    residual is left as it is."""
+    _need_cuda(residual, weight, out)
+    n = rows if rows is not None else (rows_idx.numel() if rows_idx is not None else residual.shape[0])
+    f = _fn(_ew(), "rl_add_rmsnorm", [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p,
+                                       c_int, c_int, c_float, c_void_p])
+    if delta is not None and delta.dtype != out.dtype:
+        raise KernelError("add_rmsnorm: delta and out must have the same dtype")
+    _check(f(_ptr(residual), _ptr(delta), _ptr(weight), _code(weight.dtype), _ptr(out), _code(out.dtype),
+             _ptr(rows_idx), n, residual.shape[-1], float(eps), _stream()), "add_rmsnorm")
+
+
+def add_residual(residual: torch.Tensor, delta: torch.Tensor) -> None:
+    _need_cuda(residual, delta)
+    f = _fn(_ew(), "rl_add_residual", [c_void_p, c_void_p, c_int, c_longlong, c_void_p])
+    _check(f(_ptr(residual), _ptr(delta), _code(delta.dtype), delta.numel(), _stream()), "add_residual")
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]."""
+    _need_cuda(gate_up, out)
+    f = _fn(_ew(), "rl_swiglu", [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(gate_up), _ptr(out), _code(out.dtype), gate_up.shape[0], out.shape[1], _stream()), "swiglu")
+
+
+def add_bias(x: torch.Tensor, bias: torch.Tensor) -> None:
+    _need_cuda(x, bias)
+    f = _fn(_ew(), "rl_add_bias", [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(x), _code(x.dtype), _ptr(bias), _code(bias.dtype), x.shape[0], x.shape[1], _stream()), "add_bias")
+
+
+def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, slots: Optional[torch.Tensor],
+                  cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], kcache: Optional[torch.Tensor],
+                  vcache: Optional[torch.Tensor], num_heads: int, num_kv_heads: int, head_dim: int,
+                  page_size: int, status: torch.Tensor, tokens: Optional[int] = None) -> None:
+    """Rotates q and k heads of qkv [T, (Hq + 2 Hkv) D] in place and writes k, v to
+    the cache slot of each token (``slots`` None or negative: no write)."""
+    _need_cuda(qkv, positions)
+    f = _fn(_ew(), "rl_rope_kv_write", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                         c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+    max_pos = cos.shape[0] if cos is not None else 2 ** 31 - 1
+    _check(f(_ptr(qkv), _code(qkv.dtype), _ptr(positions), _ptr(slots), _ptr(cos), _ptr(sin), _ptr(kcache),
+             _ptr(vcache), tokens if tokens is not None else qkv.shape[0], num_heads, num_kv_heads, head_dim,
+             page_size, max_pos, _ptr(status), _stream()), "rope_kv_write")
+
+
+# ------------------------------------------------------------------------ gemm
+
+def gemm_tn_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, rows: Optional[int] = None) -> None:
+    """out[M, N] = x[M, K] @ w[N, K]^T, float accumulation on the CUDA cores."""
+    _need_cuda(x, w, out)
+    f = _fn(_lib("gemm_simt", "gemm_simt.cu"), "rl_gemm_tn_simt",
+            [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    M = rows if rows is not None else x.shape[0]
+    N, K = w.shape
+    if x.shape[1] != K or out.shape[1] != N or x.stride(1) != 1 or out.stride(1) != 1 or not w.is_contiguous():
+        raise KernelError(f"gemm_tn_simt: shapes x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)}")
+    _check(f(_ptr(x), _code(x.dtype), _ptr(w), _code(w.dtype), _ptr(out), _code(out.dtype), M, N, K,
+             x.stride(0), out.stride(0), _stream()), "gemm_tn_simt")
+
+
+# ------------------------------------------------------------------- attention
+
+MAX_HEAD_DIM = 256
+
+
+def _attn(head_dim: int) -> ctypes.CDLL:
+    if head_dim % 16 != 0 or head_dim < 16 or head_dim > MAX_HEAD_DIM:
+        raise KernelError(f"attention kernels take head sizes that are multiples of 16 up to "
+                          f"{MAX_HEAD_DIM}; got {head_dim}")
+    return _lib(f"attention_d{head_dim}", "attention.cu", {"RL_HEAD_DIM": head_dim})
+
+
+DECODE_PARTITION = 256
+PREFILL_TILE_ROWS = 32
+
+
+def attn_decode(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcache: torch.Tensor,
+                block_table: torch.Tensor, item_tok: torch.Tensor, seq_of_token: torch.Tensor,
+                positions: torch.Tensor, part_o: torch.Tensor, part_ml: torch.Tensor, max_parts: int,
+                out: torch.Tensor, items: int, num_heads: int, num_kv_heads: int, head_dim: int,
+                page_size: int, window: int, scale: float) -> None:
+    _need_cuda(q, kcache, out)
+    f = _fn(_attn(head_dim), "rl_attn_decode",
+            [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+             c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p])
+    need = items * num_heads * max_parts
+    if part_o.numel() < need * head_dim or part_ml.numel() < need * 2:
+        raise KernelError("attn_decode: partition workspace too small")
+    _check(f(_code(q.dtype), _ptr(q), q_stride, _ptr(kcache), _ptr(vcache), _ptr(block_table),
+             block_table.shape[1], _ptr(item_tok), _ptr(seq_of_token), _ptr(positions), _ptr(part_o),
+             _ptr(part_ml), max_parts, _ptr(out), out.stride(0), items, num_heads, num_kv_heads, page_size,
+             window, float(scale), _stream()), "attn_decode")
+
+
+def attn_prefill(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcache: torch.Tensor,
+                 block_table: torch.Tensor, tile_seq: torch.Tensor, tile_tok: torch.Tensor,
+                 tile_rows: torch.Tensor, positions: torch.Tensor, out: torch.Tensor, tiles: int,
+                 num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, window: int,
+                 scale: float) -> None:
+    _need_cuda(q, kcache, out)
+    f = _fn(_attn(head_dim), "rl_attn_prefill",
+            [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+             c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p])
+    _check(f(_code(q.dtype), _ptr(q), q_stride, _ptr(kcache), _ptr(vcache), _ptr(block_table),
+             block_table.shape[1], _ptr(tile_seq), _ptr(tile_tok), _ptr(tile_rows), _ptr(positions),
+             _ptr(out), out.stride(0), tiles, num_heads, num_kv_heads, page_size, window, float(scale),
+             _stream()), "attn_prefill")
+
+
+# -------------------------------------------------------------------- sampling
+
+def sample(logits: torch.Tensor, rows: int, temperature: torch.Tensor, top_k: torch.Tensor,
+           top_p: torch.Tensor, seed_lo: torch.Tensor, seed_hi: torch.Tensor, position: torch.Tensor,
+           out_token: torch.Tensor, out_logprob: Optional[torch.Tensor], stream_id: int = 0) -> None:
+    _need_cuda(logits, out_token)
+    if logits.dtype != torch.float32:
+        raise KernelError("sample: logits must be float32")
+    f = _fn(_lib("sampling", "sampling.cu"), "rl_sample",
+            [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+             c_uint, c_void_p, c_void_p, c_void_p])
+    _check(f(_ptr(logits), rows, logits.shape[1], logits.stride(0), _ptr(temperature), _ptr(top_k),
+             _ptr(top_p), _ptr(seed_lo), _ptr(seed_hi), _ptr(position), stream_id, _ptr(out_token),
+             _ptr(out_logprob), _stream()), "sample")
+
+
+def gather_logprob(logits: torch.Tensor, rows: int, target: torch.Tensor, out: torch.Tensor) -> None:
+    _need_cuda(logits, target, out)
+    f = _fn(_lib("sampling", "sampling.cu"), "rl_gather_logprob",
+            [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p])
+    _check(f(_ptr(logits), rows, logits.shape[1], logits.stride(0), _ptr(target), _ptr(out), _stream()),
+           "gather_logprob")
+
+
+def build_all(head_dims=(64, 128), verbose: bool = True) -> None:
+    """Compiles every kernel family (attention for the given head sizes)."""
+    build.compile_module("elementwise", "elementwise.cu", verbose=verbose)
+    build.compile_module("gemm_simt", "gemm_simt.cu", verbose=verbose)
+    build.compile_module("sampling", "sampling.cu", verbose=verbose)
+    for d in head_dims:
+        build.compile_module(f"attention_d{d}", "attention.cu", {"RL_HEAD_DIM": d}, verbose=verbose)

@@ -1,0 +1,121 @@
+"""Grouped-query causal attention over the paged cache.
+
+q, k, v come from one fused projection [q | k | v]; q and k are rotated by the
+position encoding in the kernel that writes k and v into the cache; sequences that
+bring one token go to the split-K decode kernel, longer portions to the tiled
+prefill kernel; then the output projection.  Query head h reads kv head h // G, the
+scale is 1 / sqrt(head_dim) unless given, a window w > 0 keeps only the last w keys
+(reference: src/cuda/model/llama.cpp:116-131, src/cuda/kernels/attention.cu).
+"""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Dict, Optional
+
+import torch
+
+from ..ops import kernels
+from ..ops.linear import linear
+from .base import LayerCache, Mixer, build_part, register
+from .spec import CacheSpec, PartSpec, TensorSpec
+
+
+@dataclass(frozen=True)
+class AttentionParams:
+    hidden_size: int
+    num_heads: int
+    num_kv_heads: int
+    head_dim: int
+    position: PartSpec
+    bias: bool = False          # q, k, v projections have biases
+    out_bias: bool = False
+    window: int = 0             # 0: every earlier key
+    scale: Optional[float] = None
+
+
+@register("mixer", "gqa_attention")
+class GQAttention(Mixer):
+    def __init__(self, spec, rt):
+        super().__init__(spec, rt)
+        p = self.params
+        if p.num_heads % p.num_kv_heads != 0:
+            raise ValueError(f"num_heads {p.num_heads} is no multiple of num_kv_heads {p.num_kv_heads}")
+        if p.head_dim % 16 != 0 or not 16 <= p.head_dim <= kernels.MAX_HEAD_DIM:
+            raise ValueError(f"attention kernels take head sizes that are multiples of 16 up to "
+                             f"{kernels.MAX_HEAD_DIM}; got head_dim={p.head_dim}")
+        self.position = build_part("position", p.position, rt)
+        self.scale = p.scale if p.scale is not None else 1.0 / math.sqrt(p.head_dim)
+        self.q_size = p.num_heads * p.head_dim
+        self.kv_size = p.num_kv_heads * p.head_dim
+        self.qkv_size = self.q_size + 2 * self.kv_size
+
+    def cache_spec(self) -> CacheSpec:
+        p = self.params
+        return CacheSpec("window" if p.window > 0 else "full", p.num_kv_heads, p.head_dim, p.window)
+
+    def tensors(self) -> Dict[str, TensorSpec]:
+        p = self.params
+        t = {
+            "q": TensorSpec((self.q_size, p.hidden_size)),
+            "k": TensorSpec((self.kv_size, p.hidden_size)),
+            "v": TensorSpec((self.kv_size, p.hidden_size)),
+            "o": TensorSpec((p.hidden_size, self.q_size)),
+            "q_bias": TensorSpec((self.q_size,), optional=not p.bias),
+            "k_bias": TensorSpec((self.kv_size,), optional=not p.bias),
+            "v_bias": TensorSpec((self.kv_size,), optional=not p.bias),
+            "o_bias": TensorSpec((p.hidden_size,), optional=not p.out_bias),
+        }
+        return t
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        q, k, v = tensors["q"], tensors["k"], tensors["v"]
+        dt = torch.float32 if torch.float32 in (q.dtype, k.dtype, v.dtype) else q.dtype
+        self.w_qkv = torch.cat([q.to(dt), k.to(dt), v.to(dt)], dim=0).contiguous()
+        self.w_o = tensors["o"]
+        self.b_qkv = None
+        if all(n in tensors for n in ("q_bias", "k_bias", "v_bias")):
+            self.b_qkv = torch.cat([tensors[n].float() for n in ("q_bias", "k_bias", "v_bias")]).contiguous()
+        elif any(n in tensors for n in ("q_bias", "k_bias", "v_bias")):
+            raise ValueError("attention: q, k and v biases must come together")
+        self.b_o = tensors.get("o_bias")
+
+    def nbytes(self) -> int:
+        n = self.w_qkv.numel() * self.w_qkv.element_size() + self.w_o.numel() * self.w_o.element_size()
+        return n + self.position.nbytes()
+
+    def forward(self, x, ctx, cache: Optional[LayerCache], state=None) -> torch.Tensor:
+        p, rt = self.params, self.rt
+        T = ctx.T
+        ws = rt.workspace
+        qkv = ws.get("attn.qkv", (rt.max_tokens, self.qkv_size), rt.dtype)[:T]
+        linear(x, self.w_qkv, qkv)
+        if self.b_qkv is not None:
+            kernels.add_bias(qkv, self.b_qkv)
+        tables = self.position.rotary_tables()
+        if tables is None:
+            self.position.apply(qkv, p.num_heads, p.num_kv_heads, p.head_dim, ctx)
+        cos, sin = tables if tables is not None else (None, None)
+        g = ctx.groups[cache.group]
+        kernels.rope_kv_write(qkv, ctx.positions, g.slots if cache.write else None, cos, sin, cache.k, cache.v,
+                              p.num_heads, p.num_kv_heads, p.head_dim, rt.page_size, ctx.status, tokens=T)
+        attn = ws.get("attn.out", (rt.max_tokens, self.q_size), rt.dtype)[:T]
+        if ctx.num_decode > 0:
+            part_o = ws.get("attn.part_o", (ctx.max_items * p.num_heads * ctx.parts_capacity * p.head_dim,),
+                            torch.float32)
+            part_ml = ws.get("attn.part_ml", (ctx.max_items * p.num_heads * ctx.parts_capacity * 2,),
+                             torch.float32)
+            kernels.attn_decode(qkv, self.qkv_size, cache.k, cache.v, g.block_table, ctx.decode_tok,
+                                ctx.seq_of_token, ctx.positions, part_o, part_ml, ctx.decode_parts, attn,
+                                ctx.num_decode, p.num_heads, p.num_kv_heads, p.head_dim, rt.page_size,
+                                p.window, self.scale)
+        if ctx.num_tiles > 0:
+            kernels.attn_prefill(qkv, self.qkv_size, cache.k, cache.v, g.block_table, ctx.tile_seq,
+                                 ctx.tile_tok, ctx.tile_rows, ctx.positions, attn, ctx.num_tiles, p.num_heads,
+                                 p.num_kv_heads, p.head_dim, rt.page_size, p.window, self.scale)
+        out = ws.get("mixer.out", (rt.max_tokens, p.hidden_size), rt.dtype)[:T]
+        linear(attn, self.w_o, out)
+        if self.b_o is not None:
+            kernels.add_bias(out, self.b_o)
+        return out

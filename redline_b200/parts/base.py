@@ -1,0 +1,192 @@
+"""Interfaces of the parts a layer is put together from, and their registries.
+
+A part is built from its ``PartSpec`` and the ``Runtime`` (device, activation type,
+workspace); it declares the tensors it wants from the checkpoint under its own
+names, receives them, and then runs on a ``StepContext``.  No part knows which
+model it is in.  A new kind of part is added by subclassing one of the classes
+below and registering it under a name:
+
+    @register("mixer", "my_mixer")
+    class MyMixer(Mixer): ...
+
+after which a ``PartSpec(kind="my_mixer", ...)`` in a ``ModelSpec`` builds it.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Callable, Dict, List, Optional, Tuple
+
+import torch
+
+from .spec import CacheSpec, PartSpec, StateSpec, TensorSpec
+
+_REGISTRIES: Dict[str, Dict[str, type]] = {
+    "norm": {}, "mixer": {}, "ffn": {}, "position": {}, "block": {}, "embedding": {}, "head": {},
+}
+
+
+def register(family: str, kind: str) -> Callable[[type], type]:
+    if family not in _REGISTRIES:
+        raise KeyError(f"unknown part family '{family}' (known: {sorted(_REGISTRIES)})")
+
+    def deco(cls: type) -> type:
+        _REGISTRIES[family][kind] = cls
+        return cls
+
+    return deco
+
+
+def lookup(family: str, kind: str) -> type:
+    reg = _REGISTRIES[family]
+    if kind not in reg:
+        raise KeyError(f"no {family} part is registered as '{kind}' (known: {sorted(reg)})")
+    return reg[kind]
+
+
+def build_part(family: str, spec: PartSpec, rt: "Runtime"):
+    return lookup(family, spec.kind)(spec, rt)
+
+
+class Workspace:
+    """Activation buffers shared by all layers (they run one after another).  A
+    buffer is asked for by name with its widest shape and lives as long as the
+    engine, so addresses are stable for CUDA graphs and no step allocates."""
+
+    def __init__(self, device: torch.device):
+        self.device = device
+        self._bufs: Dict[str, torch.Tensor] = {}
+        self._retired: List[torch.Tensor] = []
+
+    def get(self, name: str, shape: Tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
+        n = 1
+        for s in shape:
+            n *= int(s)
+        key = f"{name}:{dtype}"
+        buf = self._bufs.get(key)
+        if buf is None or buf.numel() < n:
+            if buf is not None:
+                self._retired.append(buf)   # a captured graph may still point at it
+            buf = torch.empty(max(n, 1), dtype=dtype, device=self.device)
+            self._bufs[key] = buf
+        return buf[:n].view(shape)
+
+    def nbytes(self) -> int:
+        return sum(b.numel() * b.element_size() for b in self._bufs.values())
+
+
+@dataclass
+class Runtime:
+    """What a part may know of the engine it runs in."""
+
+    device: torch.device
+    dtype: torch.dtype            # activation / cache type: float32 or bfloat16
+    max_tokens: int               # most tokens in one step
+    max_seqs: int                 # most sequences in one step
+    max_seq_len: int              # longest sequence
+    page_size: int
+    workspace: Workspace = None   # type: ignore[assignment]
+
+    def __post_init__(self):
+        if self.workspace is None:
+            self.workspace = Workspace(self.device)
+
+
+@dataclass
+class LayerCache:
+    """The cache one call of a layer works on: K and V [pages, heads, page_size, D]
+    of its cache group, and whether this call writes its tokens there."""
+
+    group: int
+    k: torch.Tensor
+    v: torch.Tensor
+    write: bool = True
+
+
+class Part:
+    def __init__(self, spec: PartSpec, rt: Runtime):
+        self.spec = spec
+        self.params = spec.params
+        self.rt = rt
+
+    def tensors(self) -> Dict[str, TensorSpec]:
+        """Own tensor name -> what is expected of it."""
+        return {}
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        """Receives the tensors of ``tensors()`` that the checkpoint had, on the device."""
+
+    def nbytes(self) -> int:
+        return 0
+
+
+class Norm(Part):
+    def add_norm(self, residual: torch.Tensor, delta: Optional[torch.Tensor], out: torch.Tensor,
+                 rows_idx: Optional[torch.Tensor] = None, rows: Optional[int] = None) -> None:
+        """residual (float32) += delta; out = norm(residual).  With ``rows_idx`` only
+        those rows are produced and residual is not changed."""
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    """How positions enter a mixer.  A rotary encoding exposes ``rotary_tables()``
+    (cos, sin [max_pos, D/2] float32) and the attention mixer rotates q and k in the
+    kernel that writes the cache; any other encoding implements ``apply`` on the
+    projected q and k."""
+
+    def rotary_tables(self) -> Optional[Tuple[torch.Tensor, torch.Tensor]]:
+        return None
+
+    def apply(self, qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, ctx) -> None:
+        """In place on qkv [T, (Hq + 2 Hkv) D]; the default does nothing."""
+
+
+class Mixer(Part):
+    def cache_spec(self) -> Optional[CacheSpec]:
+        return None
+
+    def state_spec(self) -> Optional[StateSpec]:
+        return None
+
+    def forward(self, x: torch.Tensor, ctx, cache: Optional[LayerCache],
+                state: Optional[torch.Tensor]) -> torch.Tensor:
+        """x [T, H] -> [T, H] (what is added to the residual stream).  ``state`` is this
+        call's slot pool [slots, *state shape]; ``ctx.state_slot`` maps sequences to slots."""
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Embedding(Part):
+    def forward(self, ctx, out: torch.Tensor) -> None:
+        """out [T, H] float32 <- embeddings of ctx.token_ids."""
+        raise NotImplementedError
+
+    def table(self) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Head(Part):
+    def forward(self, x: torch.Tensor, rows: int, out: torch.Tensor) -> None:
+        """x [R, H] -> out [R, V] float32."""
+        raise NotImplementedError
+
+
+class Block:
+    """Arrangement of a mixer and a feed-forward around the float32 residual stream.
+    ``forward`` gets the stream and a delta that has not been added yet (the previous
+    block's last output, so that the add is fused with this block's first norm) and
+    returns its own last output the same way."""
+
+    def __init__(self, mixer_norm: Norm, mixer: Mixer, ffn_norm: Norm, ffn: FeedForward, rt: Runtime):
+        self.mixer_norm, self.mixer, self.ffn_norm, self.ffn, self.rt = mixer_norm, mixer, ffn_norm, ffn, rt
+
+    def parts(self) -> List[Part]:
+        return [self.mixer_norm, self.mixer, self.ffn_norm, self.ffn]
+
+    def forward(self, residual: torch.Tensor, pending: Optional[torch.Tensor], ctx,
+                cache: Optional[LayerCache], state: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+        raise NotImplementedError

@@ -1,0 +1,66 @@
+"""SiLU-gated feed-forward: down(silu(gate(x)) * up(x)), gate and up fused into one
+projection [gate | up] (reference: src/cuda/model/llama.cpp:134-136,
+src/cuda/kernels/elementwise.cu:66-82)."""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict
+
+import torch
+
+from ..ops import kernels
+from ..ops.linear import linear
+from .base import FeedForward, register
+from .spec import TensorSpec
+
+
+@dataclass(frozen=True)
+class GatedMLPParams:
+    hidden_size: int
+    intermediate_size: int
+    bias: bool = False
+
+
+@register("ffn", "swiglu_mlp")
+class SwiGLUMLP(FeedForward):
+    def tensors(self) -> Dict[str, TensorSpec]:
+        p = self.params
+        return {
+            "gate": TensorSpec((p.intermediate_size, p.hidden_size)),
+            "up": TensorSpec((p.intermediate_size, p.hidden_size)),
+            "down": TensorSpec((p.hidden_size, p.intermediate_size)),
+            "gate_bias": TensorSpec((p.intermediate_size,), optional=not p.bias),
+            "up_bias": TensorSpec((p.intermediate_size,), optional=not p.bias),
+            "down_bias": TensorSpec((p.hidden_size,), optional=not p.bias),
+        }
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        g, u = tensors["gate"], tensors["up"]
+        dt = torch.float32 if torch.float32 in (g.dtype, u.dtype) else g.dtype
+        self.w_gate_up = torch.cat([g.to(dt), u.to(dt)], dim=0).contiguous()
+        self.w_down = tensors["down"]
+        self.b_gate_up = None
+        if "gate_bias" in tensors and "up_bias" in tensors:
+            self.b_gate_up = torch.cat([tensors["gate_bias"].float(), tensors["up_bias"].float()]).contiguous()
+        self.b_down = tensors.get("down_bias")
+
+    def nbytes(self) -> int:
+        return (self.w_gate_up.numel() * self.w_gate_up.element_size()
+                + self.w_down.numel() * self.w_down.element_size())
+
+    def forward(self, x, ctx) -> torch.Tensor:
+        p, rt = self.params, self.rt
+        T = ctx.T
+        ws = rt.workspace
+        gu = ws.get("ffn.gate_up", (rt.max_tokens, 2 * p.intermediate_size), rt.dtype)[:T]
+        linear(x, self.w_gate_up, gu)
+        if self.b_gate_up is not None:
+            kernels.add_bias(gu, self.b_gate_up)
+        act = ws.get("ffn.act", (rt.max_tokens, p.intermediate_size), rt.dtype)[:T]
+        kernels.swiglu(gu, act)
+        out = ws.get("ffn.out", (rt.max_tokens, p.hidden_size), rt.dtype)[:T]
+        linear(act, self.w_down, out)
+        if self.b_down is not None:
+            kernels.add_bias(out, self.b_down)
+        return out
