@@ -26,6 +26,17 @@ import torch
 
 F64 = torch.float64
 
+# When set to a 16-bit type, every tensor that a 16-bit engine stores in that type
+# (outputs of norms, projections, the rotation, attention and the gated product; the
+# cached keys and values) is rounded to it here as well, while all arithmetic stays in
+# double precision and the residual stream and the logits stay unrounded.  With it the
+# oracle differs from a 16-bit engine only by the order of its sums.
+STORE_DTYPE: Optional[torch.dtype] = None
+
+
+def stored(x: torch.Tensor) -> torch.Tensor:
+    return x if STORE_DTYPE is None else x.to(STORE_DTYPE).to(F64)
+
 
 # --------------------------------------------------------------------------
 # configuration (python/redline/convert.py:86-150, src/core/model_config.cpp:25-59)
@@ -137,7 +148,7 @@ def rope_rotate(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.
     half = x.shape[-1] // 2
     x0, x1 = x[..., :half], x[..., half:]
     c, s = cos[:, None, :], sin[:, None, :]
-    return torch.cat([x0 * c - x1 * s, x1 * c + x0 * s], dim=-1)
+    return stored(torch.cat([x0 * c - x1 * s, x1 * c + x0 * s], dim=-1))
 
 
 # --------------------------------------------------------------------------
@@ -154,15 +165,15 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
     """y = x * rsqrt(mean(x^2) + eps) * w (src/cpu/reference_model.cpp:145-155)."""
     x = x.to(F64)
     inv = 1.0 / torch.sqrt((x * x).mean(dim=-1, keepdim=True) + eps)
-    return x * inv * w.to(F64)
+    return stored(x * inv * w.to(F64))
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor] = None) -> torch.Tensor:
     """y = x W^T (+ b), W stored [out, in] (src/cpu/reference_model.cpp:132-143)."""
     y = x.to(F64) @ w.to(F64).T
     if b is not None:
-        y = y + b.to(F64)
-    return y
+        y = stored(y) + b.to(F64)
+    return stored(y)
 
 
 def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float,
@@ -190,12 +201,12 @@ def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: f
         p = torch.exp(s)
         p = p / p.sum(dim=-1, keepdim=True)
         out[:, h, :] = p @ v[:, kh, :]
-    return out
+    return stored(out)
 
 
 def swiglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     """silu(g) * u with silu(g) = g / (1 + exp(-g)) (src/cpu/reference_model.cpp:222-229)."""
-    return gate / (1.0 + torch.exp(-gate)) * up
+    return stored(gate / (1.0 + torch.exp(-gate)) * up)
 
 
 # --------------------------------------------------------------------------
@@ -257,7 +268,7 @@ def forward(cfg: PlainConfig, w: Dict[str, torch.Tensor], tokens: Sequence[int])
     h = hidden_states(cfg, w, tokens)
     xn = rmsnorm(h, w["model.norm.weight"], cfg.rms_norm_eps)
     head = w["lm_head.weight"] if "lm_head.weight" in w else w["model.embed_tokens.weight"]
-    return linear(xn, head)
+    return xn.to(F64) @ head.to(F64).T
 
 
 def greedy_generate(cfg: PlainConfig, w: Dict[str, torch.Tensor], prompt: Sequence[int], n: int) -> List[int]:

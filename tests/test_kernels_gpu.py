@@ -1,0 +1,328 @@
+"""Each CUDA kernel alone against a plain float64 torch restatement of the same op,
+at sizes other than the engine's: head sizes in steps of 16, odd group counts, widths
+and vocabularies that are no power of two, shuffled page ids, lengths that cross page,
+tile and partition edges, a far key that must be found among hundreds."""
+
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_llama as P
+from redline_b200.ops import kernels
+from redline_b200.ops.linear import linear
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+TOL = {"float32": 2e-5, "bfloat16": 1.2e-2}     # of max |ref|: float32 sums, one bfloat16 rounding
+
+
+def close(got, ref, tol):
+    err = (got.double().cpu() - ref.double().cpu()).abs().max().item() / (ref.abs().max().item() + 1e-30)
+    assert err < tol, f"rel-max error {err:.3e} >= {tol}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("hidden,vocab", [(200, 331), (2048, 1000), (72, 17)])
+def test_embedding(dtype, hidden, vocab):
+    table = torch.randn(vocab, hidden, device=DEV).to(DT[dtype])
+    ids = torch.randint(0, vocab, (37,), device=DEV, dtype=torch.int32)
+    out = torch.full((37, hidden), float("nan"), device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    kernels.embedding(ids, table, out, status)
+    assert torch.equal(out, table[ids.long()].float()) and status.item() == 0
+    ids[3] = vocab
+    kernels.embedding(ids, table, out, status)
+    assert status.item() == 1 and out[3].abs().max().item() == 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("hidden,eps", [(200, 3e-6), (2048, 1e-5), (72, 1e-2), (4100, 1e-6)])
+def test_add_rmsnorm(dtype, hidden, eps):
+    T = 19
+    res = torch.randn(T, hidden, device=DEV) * 3
+    delta = torch.randn(T, hidden, device=DEV).to(DT[dtype])
+    w = (1 + 0.1 * torch.randn(hidden, device=DEV)).to(DT[dtype])
+    want_res = res.double() + delta.double()
+    ref = P.rmsnorm(want_res.cpu(), w.cpu(), eps)
+    out = torch.empty(T, hidden, device=DEV, dtype=DT[dtype])
+    r = res.clone()
+    kernels.add_rmsnorm(r, delta, w, out, eps)
+    close(out, ref, TOL[dtype])
+    assert torch.allclose(r.double(), want_res, atol=1e-6)          # the stream holds the float32 sum
+    r2 = res.clone()                                                 # no delta: a plain norm, stream untouched
+    kernels.add_rmsnorm(r2, None, w, out, eps)
+    close(out, P.rmsnorm(res.double().cpu(), w.cpu(), eps), TOL[dtype])
+    assert torch.equal(r2, res)
+    idx = torch.tensor([4, 4, 0, 18], dtype=torch.int32, device=DEV)  # rows picked, stream left alone
+    out4 = torch.empty(4, hidden, device=DEV, dtype=DT[dtype])
+    r3 = res.clone()
+    kernels.add_rmsnorm(r3, delta, w, out4, eps, rows_idx=idx)
+    close(out4, ref[idx.long().cpu()], TOL[dtype])
+    assert torch.equal(r3, res)
+    wf = w.float()                                                   # a weight stored in 32-bit
+    kernels.add_rmsnorm(res.clone(), delta, wf, out, eps)
+    close(out, ref, TOL[dtype])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("inter", [704, 328, 1000])
+def test_swiglu(dtype, inter):
+    gu = (torch.randn(11, 2 * inter, device=DEV) * 4).to(DT[dtype])
+    out = torch.empty(11, inter, device=DEV, dtype=DT[dtype])
+    kernels.swiglu(gu, out)
+    g, u = gu[:, :inter].double().cpu(), gu[:, inter:].double().cpu()
+    close(out, P.swiglu(g, u), TOL[dtype])
+
+
+@pytest.mark.parametrize("tx,tw,ty", [("float32", "float32", "float32"), ("bfloat16", "bfloat16", "float32"),
+                                       ("bfloat16", "float32", "bfloat16"), ("float32", "bfloat16", "bfloat16")])
+@pytest.mark.parametrize("M,N,K", [(1, 331, 200), (37, 1000, 384), (130, 70, 1024), (5, 64, 18)])
+def test_gemm_simt(tx, tw, ty, M, N, K):
+    x = torch.randn(M, K, device=DEV).to(DT[tx])
+    w = torch.randn(N, K, device=DEV).to(DT[tw])
+    y = torch.empty(M, N, device=DEV, dtype=DT[ty])
+    kernels.gemm_tn_simt(x, w, y)
+    close(y, x.double() @ w.double().T, TOL[ty] if ty == "bfloat16" else 2e-6)
+    if M > 1:       # a row does not depend on its neighbours: bit for bit
+        y1 = torch.empty(1, N, device=DEV, dtype=DT[ty])
+        kernels.gemm_tn_simt(x[M // 2:M // 2 + 1], w, y1)
+        assert torch.equal(y1[0], y[M // 2])
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 3072, 2048), (8, 1000, 384), (200, 704, 256), (64, 331, 200)])
+def test_linear_bfloat16(M, N, K):
+    x = torch.randn(M, K, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(N, K, device=DEV) * 0.05).to(torch.bfloat16)
+    ref = x.double() @ w.double().T
+    y = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    close(linear(x, w, y), ref, 1.2e-2)
+    yf = torch.empty(M, N, device=DEV, dtype=torch.float32)
+    close(linear(x, w, yf), ref, 1e-4)
+
+
+def paged_setup(dtype, Hq, Hkv, D, lens_past, lens_new, page_size, seed, sharp=None, cos=None, sin=None):
+    """Random q/k/v for several sequences; pages with shuffled ids; returns everything a
+    kernel launch needs plus the dense per-sequence tensors for the reference."""
+    g = torch.Generator().manual_seed(seed)
+    S = len(lens_past)
+    total = [p + n for p, n in zip(lens_past, lens_new)]
+    max_blocks = max((t + page_size - 1) // page_size for t in total) + 1
+    npages = sum((t + page_size - 1) // page_size for t in total) + 3
+    perm = (torch.randperm(npages - 1, generator=g) + 1).tolist()
+    bt = torch.zeros(S, max_blocks, dtype=torch.int32)
+    it = iter(perm)
+    for s in range(S):
+        for b in range((total[s] + page_size - 1) // page_size):
+            bt[s, b] = next(it)
+    qkv_w = (Hq + 2 * Hkv) * D
+    seqs = []
+    for s in range(S):
+        x = torch.randn(total[s], qkv_w, generator=g)
+        seqs.append(x)
+    if sharp is not None:
+        sharp(seqs, cos, sin)
+    seqs = [x.to(DT[dtype]) for x in seqs]
+    return dict(S=S, total=total, bt=bt, npages=npages, seqs=seqs, max_blocks=max_blocks)
+
+
+def reference_attention(seqs, Hq, Hkv, D, cos, sin, scale, window, dtype):
+    """Per sequence: rotate q, k (rounded to the cache type), causal attention in float64."""
+    outs = []
+    P.STORE_DTYPE = DT[dtype] if dtype == "bfloat16" else None
+    try:
+        for x in seqs:
+            T = x.shape[0]
+            x = x.double().cpu()
+            q = x[:, :Hq * D].reshape(T, Hq, D)
+            k = x[:, Hq * D:(Hq + Hkv) * D].reshape(T, Hkv, D)
+            v = x[:, (Hq + Hkv) * D:].reshape(T, Hkv, D)
+            q = P.rope_rotate(q, cos[:T].double(), sin[:T].double())
+            k = P.rope_rotate(k, cos[:T].double(), sin[:T].double())
+            P.STORE_DTYPE = None
+            outs.append(P.causal_attention(q, k, v, scale, window).reshape(T, Hq * D))
+            P.STORE_DTYPE = DT[dtype] if dtype == "bfloat16" else None
+    finally:
+        P.STORE_DTYPE = None
+    return outs
+
+
+def run_attention(dtype, Hq, Hkv, D, lens_past, lens_new, page_size=16, window=0, seed=0, sharp=None,
+                  poison=True):
+    """Writes the past through rope_kv_write, then runs the new tokens (decode kernel for
+    single tokens, prefill kernel for portions) and compares with the reference."""
+    from redline_b200.config.model_config import RopeScaling
+    from redline_b200.parts.rope import RotaryParams, rope_tables
+    cos, sin = rope_tables(RotaryParams(D, 10000.0, RopeScaling(), 4096),
+                           max(p + n for p, n in zip(lens_past, lens_new)) + 1)
+    st = paged_setup(dtype, Hq, Hkv, D, lens_past, lens_new, page_size, seed, sharp, cos, sin)
+    S, total, seqs = st["S"], st["total"], st["seqs"]
+    scale = 1.0 / math.sqrt(D)
+    ref = reference_attention(seqs, Hq, Hkv, D, cos, sin, scale, window, dtype)
+    fill = float("nan") if poison else 0.0
+    kc = torch.full((st["npages"], Hkv, page_size, D), fill, device=DEV, dtype=DT[dtype])
+    vc = torch.full((st["npages"], Hkv, page_size, D), fill, device=DEV, dtype=DT[dtype])
+    kc[0], vc[0] = 0, 0
+    bt = st["bt"].to(DEV)
+    cosd, sind = cos.to(DEV), sin.to(DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+
+    def launch(ranges):
+        """ranges: per sequence (start, n) of tokens to run now."""
+        toks, pos, seq_of, slots = [], [], [], []
+        dec, tiles = [], []
+        t = 0
+        for s, (a, n) in enumerate(ranges):
+            if n == 0:
+                continue
+            toks.append(seqs[s][a:a + n])
+            for i in range(a, a + n):
+                pos.append(i)
+                seq_of.append(s)
+                slots.append(int(st["bt"][s, i // page_size]) * page_size + i % page_size)
+            if n == 1:
+                dec.append(t)
+            else:
+                for r0 in range(0, n, 32):
+                    tiles.append((s, t + r0, min(32, n - r0)))
+            t += n
+        qkv = torch.cat(toks).to(DEV).contiguous()
+        i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)  # noqa: E731
+        pos_d, seq_d, slot_d = i32(pos), i32(seq_of), i32(slots)
+        kernels.rope_kv_write(qkv, pos_d, slot_d, cosd, sind, kc, vc, Hq, Hkv, D, page_size, status)
+        out = torch.full((t, Hq * D), float("nan"), device=DEV, dtype=DT[dtype])
+        if dec:
+            parts = (max(total) + 255) // 256
+            po = torch.empty(len(dec) * Hq * parts * D, device=DEV)
+            pm = torch.empty(len(dec) * Hq * parts * 2, device=DEV)
+            kernels.attn_decode(qkv, qkv.shape[1], kc, vc, bt, i32(dec), seq_d, pos_d, po, pm, parts, out,
+                                len(dec), Hq, Hkv, D, page_size, window, scale)
+        if tiles:
+            kernels.attn_prefill(qkv, qkv.shape[1], kc, vc, bt, i32([x[0] for x in tiles]),
+                                 i32([x[1] for x in tiles]), i32([x[2] for x in tiles]), pos_d, out, len(tiles),
+                                 Hq, Hkv, D, page_size, window, scale)
+        return out
+
+    if any(lens_past):
+        launch([(0, p) for p in lens_past])
+    out = launch([(p, n) for p, n in zip(lens_past, lens_new)])
+    assert status.item() == 0
+    want = torch.cat([ref[s][p:p + n] for s, (p, n) in enumerate(zip(lens_past, lens_new)) if n])
+    assert not torch.isnan(out.float()).any(), "attention read a cache slot that was never written"
+    close(out, want, 2e-5 if dtype == "float32" else 1.6e-2)
+
+
+ATTN_SHAPES = [  # Hq, Hkv, D
+    (4, 2, 64), (3, 1, 128), (5, 5, 48), (8, 1, 16), (6, 2, 80), (2, 1, 256), (14, 2, 32),
+]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("Hq,Hkv,D", ATTN_SHAPES)
+def test_attention_prefill_whole_and_with_a_cached_past(dtype, Hq, Hkv, D):
+    run_attention(dtype, Hq, Hkv, D, [0, 0, 0], [1 + 4, 33, 129], seed=1)
+    run_attention(dtype, Hq, Hkv, D, [17, 64, 5], [40, 2, 70], seed=2)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("Hq,Hkv,D", ATTN_SHAPES)
+def test_attention_decode_lengths_across_pages_and_partitions(dtype, Hq, Hkv, D):
+    run_attention(dtype, Hq, Hkv, D, [0, 4, 15, 16, 128], [1, 1, 1, 1, 1], seed=3)
+    run_attention(dtype, Hq, Hkv, D, [255, 256, 257, 699], [1, 1, 1, 1], seed=4)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_attention_mixed_launch_and_other_page_sizes(dtype):
+    run_attention(dtype, 4, 2, 64, [300, 31, 0, 90], [1, 33, 2, 1], page_size=32, seed=5)
+    run_attention(dtype, 3, 1, 128, [63, 64, 200], [1, 65, 1], page_size=64, seed=6)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("window", [1, 7, 16, 40, 300])
+def test_attention_window(dtype, window):
+    run_attention(dtype, 4, 2, 64, [0, 50, 290], [45, 35, 1], window=window, seed=7)
+    run_attention(dtype, 3, 3, 32, [99, 300], [1, 1], window=window, seed=8)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_far_key_is_found_among_hundreds(dtype):
+    """One key far back is made to match the last query after rotation (both are the
+    inverse rotation of the same vector u, |u|^2 = 4 D), so its score is 32 while all
+    others are about N(0, 4): the output is that key's value, and a kernel that loses a
+    partition, a page or a tile gives something else entirely."""
+    Hq, Hkv, D = 4, 2, 64
+    half = D // 2
+
+    def unrotate(u, c, s):
+        return torch.cat([u[:half] * c + u[half:] * s, u[half:] * c - u[:half] * s])
+
+    for far, total in [(3, 700), (255, 700), (256, 530), (511, 530), (17, 300)]:
+        def sharp(seqs, cos, sin, far=far, total=total):
+            x = seqs[0]
+            u = torch.full((D,), 2.0)
+            for h in range(Hq):
+                x[total - 1, h * D:(h + 1) * D] = unrotate(u, cos[total - 1], sin[total - 1])
+            for h in range(Hkv):
+                x[far, (Hq + h) * D:(Hq + h + 1) * D] = unrotate(u, cos[far], sin[far])
+        run_attention(dtype, Hq, Hkv, D, [total - 1], [1], seed=9, sharp=sharp)     # decode kernel
+        run_attention(dtype, Hq, Hkv, D, [total - 40], [40], seed=9, sharp=sharp)   # prefill kernel
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_rope_kv_write_values_and_skipped_writes(dtype):
+    from redline_b200.config.model_config import RopeScaling
+    from redline_b200.parts.rope import RotaryParams, rope_tables
+    Hq, Hkv, D, ps = 3, 2, 48, 16
+    cos, sin = rope_tables(RotaryParams(D, 5e4, RopeScaling("linear", 2.0), 512), 512)
+    T = 9
+    x = torch.randn(T, (Hq + 2 * Hkv) * D).to(DT[dtype])
+    pos = torch.tensor([0, 1, 15, 16, 17, 100, 255, 300, 511], dtype=torch.int32)
+    slots = torch.tensor([32, 33, 47, 80, 81, -1, 16, 17, 95], dtype=torch.int32)
+    kc = torch.zeros(6, Hkv, ps, D, device=DEV, dtype=DT[dtype])
+    vc = torch.zeros_like(kc)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    qkv = x.to(DEV).clone()
+    kernels.rope_kv_write(qkv, pos.to(DEV), slots.to(DEV), cos.to(DEV), sin.to(DEV), kc, vc, Hq, Hkv, D, ps, status)
+    xd = x.double()
+    c, s = cos[pos.long()].double(), sin[pos.long()].double()
+    q = P.rope_rotate(xd[:, :Hq * D].reshape(T, Hq, D), c, s)
+    k = P.rope_rotate(xd[:, Hq * D:(Hq + Hkv) * D].reshape(T, Hkv, D), c, s)
+    v = xd[:, (Hq + Hkv) * D:].reshape(T, Hkv, D)
+    tol = 1e-6 if dtype == "float32" else 8e-3
+    close(qkv[:, :Hq * D], q.reshape(T, -1), tol)
+    close(qkv[:, Hq * D:(Hq + Hkv) * D], k.reshape(T, -1), tol)
+    assert torch.equal(qkv[:, (Hq + Hkv) * D:].cpu(), x[:, (Hq + Hkv) * D:])
+    written = torch.zeros(6 * ps, dtype=torch.bool)
+    for t in range(T):
+        sl = int(slots[t])
+        if sl < 0:
+            continue
+        written[sl] = True
+        close(kc[sl // ps, :, sl % ps, :], k[t], tol)
+        assert torch.equal(vc[sl // ps, :, sl % ps, :].cpu().double(), v[t])
+    flat_k = kc.permute(0, 2, 1, 3).reshape(6 * ps, -1)
+    assert flat_k[~written.to(DEV)].abs().max().item() == 0      # nothing else was touched
+    assert status.item() == 0
+    kernels.rope_kv_write(qkv, torch.full((T,), 512, dtype=torch.int32, device=DEV), None, cos.to(DEV),
+                          sin.to(DEV), kc, vc, Hq, Hkv, D, ps, status)
+    assert status.item() == 2                                     # a position beyond the table is flagged
+
+
+def test_resolve_ids_and_bias_and_residual():
+    ids = torch.tensor([5, 6, 7, 8], dtype=torch.int32, device=DEV)
+    src = torch.tensor([-1, 2, -1, 0], dtype=torch.int32, device=DEV)
+    sampled = torch.tensor([100, 200, 300], dtype=torch.int32, device=DEV)
+    kernels.resolve_ids(ids, src, sampled, 4)
+    assert ids.tolist() == [5, 300, 7, 100]
+    x = torch.randn(5, 33, device=DEV).to(torch.bfloat16)
+    b = torch.randn(33, device=DEV)
+    want = (x.float() + b).to(torch.bfloat16)
+    kernels.add_bias(x, b)
+    assert torch.equal(x, want)
+    r = torch.randn(7, 50, device=DEV)
+    d = torch.randn(7, 50, device=DEV).to(torch.bfloat16)
+    want = r + d.float()
+    kernels.add_residual(r, d)
+    assert torch.equal(r, want)
