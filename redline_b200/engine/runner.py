@@ -84,6 +84,8 @@ class ModelRunner:
                 self._caches.append(self.storage.of_owner(call.cache_of, False))
         self._states = [self.states.of_call(i) for i in range(len(order))]
         self._graphs: Dict[int, torch.cuda.CUDAGraph] = {}
+        self._graph_kernels: Dict[int, int] = {}   # kernels of this package in each captured graph
+        self.num_kernel_launches = 0               # kernels of this package run by steps so far
         self.num_graph_steps = 0
         self.num_eager_steps = 0
 
@@ -129,9 +131,12 @@ class ModelRunner:
             else:
                 g.replay()
             self.num_graph_steps += 1
+            self.num_kernel_launches += self._graph_kernels[bucket]
         else:
+            before = kernels.LAUNCHES
             self._forward(ctx, sample, ctx.has_src)
             self.num_eager_steps += 1
+            self.num_kernel_launches += kernels.LAUNCHES - before
         return self.logits[:ctx.R], ctx
 
     def _forward(self, ctx: StepContext, sample: bool, resolve: bool) -> None:
@@ -160,8 +165,10 @@ class ModelRunner:
         self._forward(ctx, True, True)
         torch.cuda.synchronize()
         g = torch.cuda.CUDAGraph()
+        before = kernels.LAUNCHES
         with torch.cuda.graph(g):
             self._forward(ctx, True, True)
+        self._graph_kernels[bucket] = kernels.LAUNCHES - before
         self._graphs[bucket] = g
         self.sampler.tokens.copy_(fed)
         g.replay()

@@ -51,9 +51,14 @@ def _ptr(t: Optional[torch.Tensor]) -> c_void_p:
     return c_void_p(0 if t is None else t.data_ptr())
 
 
-def _check(code: int, what: str) -> None:
+LAUNCHES = 0   # kernels of this package launched (or captured into a graph) so far
+
+
+def _check(code: int, what: str, n: int = 1) -> None:
+    global LAUNCHES
     if code != 0:
         raise KernelError(f"{what}: CUDA error {code}")
+    LAUNCHES += n
 
 
 def _code(dtype: torch.dtype) -> int:
@@ -186,7 +191,7 @@ def attn_decode(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcache: to
     _check(f(_code(q.dtype), _ptr(q), q_stride, _ptr(kcache), _ptr(vcache), _ptr(block_table),
              block_table.shape[1], _ptr(item_tok), _ptr(seq_of_token), _ptr(positions), _ptr(part_o),
              _ptr(part_ml), max_parts, _ptr(out), out.stride(0), items, num_heads, num_kv_heads, page_size,
-             window, float(scale), _stream()), "attn_decode")
+             window, float(scale), _stream()), "attn_decode", 2)
 
 
 def attn_prefill(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcache: torch.Tensor,
