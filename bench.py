@@ -166,7 +166,7 @@ def decode_run(model: str, batch: int, prompt_len: int, steps: int, warmup: int,
     from redline_b200.engine.engine import Engine
     from redline_b200.sampling import SamplingParams
 
-    new_tokens = warmup + 2 * steps + 8
+    new_tokens = warmup + 2 * steps + 32
     eng = Engine(model, dtype="bfloat16", max_num_seqs=batch, max_num_batched_tokens=2048, max_seq_len=max_seq_len,
                  kv_cache_tokens=batch * ((prompt_len + new_tokens + 15) // 16 * 16 + 16))
     rng = np.random.RandomState(0)
@@ -214,6 +214,7 @@ def decode_run(model: str, batch: int, prompt_len: int, steps: int, warmup: int,
         eng.step()
     torch.cuda.synchronize()
     wall = time.perf_counter() - t1
+    assert len(eng._seqs) == batch, "a request finished inside the timed region"
     produced = sum(len(s.tokens) for s in eng._seqs.values()) - done_before
     ctx_mid = prompt_len + warmup + steps // 2
     words = eng.runner.builder.capacity_words
@@ -269,7 +270,7 @@ def run_ours(args) -> Dict[str, Any]:
         nums = model_numbers(cfg)
         sampler.start()
         K, W = args.steps, args.warmup
-        prompt = CONTEXT - (W + 2 * K + 10)
+        prompt = CONTEXT - (W + 2 * K + 34)
         main = decode_run(model, BATCH, prompt, K, W, sampler, CONTEXT)
         pre = prefill_run(model, PREFILL_TOKENS)
         pts = {}
@@ -327,7 +328,7 @@ def run_reference(args) -> Dict[str, Any]:
         if r.returncode != 0:
             return {"impl": "reference", "unavailable": "the reference's converter failed: " + r.stderr.strip()[-300:]}
         K, W = args.steps, args.warmup
-        prompt = CONTEXT - (W + 2 * K + 10)
+        prompt = CONTEXT - (W + 2 * K + 34)
         out = os.path.join(tmp, "report.json")
         cmd = [binary, "--model", rlm, "--synthetic", f"{BATCH},{prompt},{W + K}", "--max-seqs", str(BATCH),
                "--max-seq-len", str(CONTEXT), "--out", out]

@@ -165,3 +165,26 @@ def test_command_line(models, tmp_path):
     assert r.returncode == 0, r.stderr[-2000:]
     assert os.path.exists(tmp_path / "rand" / "model.safetensors")
     assert len(json.loads([x for x in r.stdout.splitlines() if x.startswith("{")][0])["output_ids"]) == 4
+
+
+def test_benchmark_harness_report(models, tmp_path):
+    """The fields of the report (reference: tests/cuda/test_engine.cpp:233-248) and the
+    redline_bench program."""
+    from redline_b200.runtime import Engine
+    d, _ = models["tiny_a"]
+    eng = Engine(d, dtype="bfloat16", max_seqs=4, max_batched_tokens=64, max_seq_len=256, kv_cache_tokens=1024)
+    doc = {"name": "t", "requests": [{"prompt_len": 20 + 7 * i, "max_new_tokens": 10} for i in range(5)]}
+    rep = eng.benchmark(doc, warmup=1)
+    assert rep["num_requests"] == 5 and rep["output_tokens"] == 50 and rep["prompt_tokens"] == sum(20 + 7 * i for i in range(5))
+    for k in ("ttft_ms", "itl_ms", "tpot_ms", "e2e_latency_ms", "decode_step_gpu_ms", "host_overhead_ms"):
+        assert rep[k]["count"] > 0 and rep[k]["p50"] > 0, k
+    assert rep["decode_throughput_gpu_tok_s"] > 0 and rep["prefill_throughput_gpu_tok_s"] > 0
+    assert rep["output_throughput_tok_s"] > 0 and 0 < rep["cuda_graph_step_fraction"] <= 1
+    assert rep["memory"]["weights"] > 0 and rep["engine"]["engine"] == "redline_b200"
+    out = tmp_path / "rep.json"
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "redline_bench"), "--model", d, "--synthetic", "3,16,6",
+                        "--max-seqs", "4", "--max-seq-len", "128", "--kv-cache-tokens", "512", "--out", str(out),
+                        "--per-request"], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    rep = json.loads(out.read_text())
+    assert rep["workload"] == "synthetic_n3_in16_out6" and rep["output_tokens"] == 18 and len(rep["requests"]) == 3
