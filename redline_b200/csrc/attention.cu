@@ -2,7 +2,7 @@
 // D a multiple of 16 up to 256) and both element types (float, bfloat16).
 //
 //   rl_attn_decode   one query token per item; the keys are cut into absolute
-//                    256-key partitions, one CTA per (partition, kv head, item)
+//                    128-key partitions, one CTA per (partition, kv head, item)
 //                    computes all G query heads of the group from one read of K
 //                    and V and leaves (max, sum, unnormalised output); a second
 //                    kernel merges the partitions with w_i = exp(m_i - m).
@@ -25,11 +25,12 @@ namespace rl {
 
 constexpr int kD = RL_HEAD_DIM;
 static_assert(kD % 16 == 0 && kD >= 16 && kD <= 256, "head size must be a multiple of 16, at most 256");
-constexpr int kPart = 256;      // keys per decode partition (absolute boundaries)
+constexpr int kPart = 128;      // keys per decode partition (absolute boundaries)
 constexpr int kDecThreads = 128;
 constexpr int kLPK = 8;         // lanes that share one key
 constexpr int kKeysPerIter = kDecThreads / kLPK;  // 16
 constexpr int kGT = 4;          // query heads per pass over the keys
+constexpr int kMaxMergeParts = 256;    // the fused merge of the tensor-core kernel holds this many weights
 
 template <typename T>
 struct DecodeArgs {
@@ -39,12 +40,13 @@ struct DecodeArgs {
   const T* vcache;
   const int32_t* block_table;  // [seqs, max_blocks]
   int max_blocks;
-  const int32_t* item_tok;     // [items] token index of the query
-  const int32_t* seq_of_token; // [tokens]
-  const int32_t* positions;    // [tokens]
+  const int4* items;           // [items] (token index of the query, sequence index, context length, 0)
   float* part_o;               // [items, Hq, max_parts, D]
   float* part_ml;              // [items, Hq, max_parts, 2]
   int max_parts;
+  int* counters;               // [items, Hkv] zero between launches (tensor-core kernel: fused merge)
+  T* out;                      // [tokens, out_stride]
+  int out_stride;
   int hq, hkv, page_size, window;
   float scale;
 };
@@ -61,9 +63,8 @@ decode_attn_kernel(const DecodeArgs<T> a) {
   __shared__ float stat_m[kGT], stat_l[kGT];
 
   const int part = blockIdx.x, kvh = blockIdx.y, item = blockIdx.z;
-  const int tok = a.item_tok[item];
-  const int seq = a.seq_of_token[tok];
-  const int ctx = a.positions[tok] + 1;
+  const int4 info = a.items[item];
+  const int tok = info.x, seq = info.y, ctx = info.z;
   const int lo = (a.window > 0 && ctx > a.window) ? ctx - a.window : 0;
   const int j_lo = max(lo, part * kPart), j_hi = min(ctx, (part + 1) * kPart);
   if (j_lo >= j_hi) return;
@@ -205,12 +206,11 @@ decode_attn_kernel(const DecodeArgs<T> a) {
 // Merges the partitions of one (item, head): out = sum_i w_i o_i / sum_i w_i l_i.
 template <typename T>
 __global__ void decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                    const int32_t* __restrict__ item_tok,
-                                    const int32_t* __restrict__ positions, T* __restrict__ out,
+                                    const int4* __restrict__ items, T* __restrict__ out,
                                     int out_stride, int hq, int max_parts, int window) {
   const int item = blockIdx.x, head = blockIdx.y;
-  const int tok = item_tok[item];
-  const int ctx = positions[tok] + 1;
+  const int4 info = items[item];
+  const int tok = info.x, ctx = info.z;
   const int lo = (window > 0 && ctx > window) ? ctx - window : 0;
   const int p_lo = lo / kPart, p_hi = (ctx - 1) / kPart;  // inclusive
   const size_t row0 = (static_cast<size_t>(item) * hq + head) * max_parts;
@@ -226,6 +226,278 @@ __global__ void decode_merge_kernel(const float* __restrict__ part_o, const floa
     out[static_cast<size_t>(tok) * out_stride + head * kD + d] = from_float<T>(num / den);
   }
 }
+
+// ------------------------------------------------- decode on the tensor cores
+// The same work as decode_attn_kernel for bfloat16 and head sizes 64 and 128, with mma.sync.m16n8k16: the G query heads of the group are the 16 rows of the
+// MMA (rows past G are zero), the keys its 8-wide side.  K and V go from global memory
+// straight into MMA fragments in 16-byte pieces: within a 32-wide block of d (for
+// Q.K^T) the MMA's k index is permuted so that a thread's two fragment words are
+// adjacent in memory, and for P.V the head dimension is permuted so that the eight
+// output tiles of a thread come from one 16-byte piece of a V row.  Four warps take 32
+// keys each of the CTA's 128-key partition, issue all their loads at once, and merge
+// through shared memory; the CTA that finishes last among an item's partitions merges
+// those (in partition order, so the result does not depend on which CTA that is).
+#if RL_HEAD_DIM == 64 || RL_HEAD_DIM == 128
+#define RL_HAVE_MMA_DECODE 1
+
+__device__ __forceinline__ void mma_16816(float* d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                          uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+__global__ void __launch_bounds__(128)
+decode_attn_mma_kernel(const DecodeArgs<bf16> a) {
+  constexpr int DB = kD / 32;   // 32-wide blocks of d for Q.K^T
+  constexpr int DG = kD / 64;   // 64-wide groups of d for P.V
+  constexpr float kLog2e = 1.4426950408889634f, kLn2 = 0.6931471805599453f;
+  // a warp's output row as its threads hold it: column c = dg*64 + j*8 + (t*2+e) holds
+  // d = dg*64 + (t*2+e)*8 + j; rows are 8 floats longer than D so that the 8-byte stores of a
+  // half-warp fall into distinct banks
+  constexpr int LDO = kD + 8;
+  __shared__ __align__(16) float sm_o[4][16][LDO];
+  __shared__ float sm_m[4][16], sm_l[4][16];
+  static_assert(16 * (kMaxMergeParts + 1) <= 4 * 16 * LDO, "the merge weights reuse the output rows");
+  float (*sm_w)[kMaxMergeParts + 1] = reinterpret_cast<float (*)[kMaxMergeParts + 1]>(&sm_o[0][0][0]);
+  __shared__ int sm_last;
+
+  const int part = blockIdx.x, kvh = blockIdx.y, item = blockIdx.z;
+  const int4 info = a.items[item];
+  const int tok = info.x, seq = info.y, ctx = info.z;
+  const int lo = (a.window > 0 && ctx > a.window) ? ctx - a.window : 0;
+  if (max(lo, part * kPart) >= min(ctx, (part + 1) * kPart)) return;
+  const int G = a.hq / a.hkv;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int32_t* bt = a.block_table + static_cast<size_t>(seq) * a.max_blocks;
+  const size_t head_stride = static_cast<size_t>(a.page_size) * kD;   // one (page, head) box
+  const int k0 = part * kPart + warp * 32;                            // this warp's 32 keys
+  const int ps_shift = __ffs(a.page_size) - 1, ps_mask = a.page_size - 1;   // page sizes are powers of two
+
+  // ---- every load of the warp is issued up front: K and V (through the block table), then Q
+  uint4 kf[4][DB];
+#pragma unroll
+  for (int nt = 0; nt < 4; ++nt) {
+    const int key = k0 + nt * 8 + g;
+    const bool live = key < ctx;
+    const size_t page = live ? bt[key >> ps_shift] : 0;
+    const bf16* kp = a.kcache + (page * a.hkv + kvh) * head_stride + static_cast<size_t>(key & ps_mask) * kD + t * 8;
+#pragma unroll
+    for (int db = 0; db < DB; ++db)
+      kf[nt][db] = live ? *reinterpret_cast<const uint4*>(kp + db * 32) : make_uint4(0, 0, 0, 0);
+  }
+  // V pieces: for each 16-key step the keys t*2, t*2+1, t*2+8, t*2+9, d = dg*64 + g*8 ..
+  uint4 vf[2][4][DG];
+#pragma unroll
+  for (int ks = 0; ks < 2; ++ks)
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int key = k0 + ks * 16 + t * 2 + (q & 1) + (q >> 1) * 8;
+      const bool live = key < ctx;
+      const size_t page = live ? bt[key >> ps_shift] : 0;
+      const bf16* vp = a.vcache + (page * a.hkv + kvh) * head_stride + static_cast<size_t>(key & ps_mask) * kD + g * 8;
+#pragma unroll
+      for (int dg = 0; dg < DG; ++dg)
+        vf[ks][q][dg] = live ? *reinterpret_cast<const uint4*>(vp + dg * 64) : make_uint4(0, 0, 0, 0);
+    }
+  // Q fragments: rows g and g + 8 of the group, all of d
+  uint4 qlo[DB], qhi[DB];
+#pragma unroll
+  for (int db = 0; db < DB; ++db) {
+    const bf16* qp = a.q + static_cast<size_t>(tok) * a.q_stride + static_cast<size_t>(kvh * G) * kD + db * 32 + t * 8;
+    qlo[db] = g < G ? *reinterpret_cast<const uint4*>(qp + g * kD) : make_uint4(0, 0, 0, 0);
+    qhi[db] = g + 8 < G ? *reinterpret_cast<const uint4*>(qp + (g + 8) * kD) : make_uint4(0, 0, 0, 0);
+  }
+  float o[DG][8][4];
+#pragma unroll
+  for (int dg = 0; dg < DG; ++dg)
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) o[dg][j][e] = 0.f;
+  float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;   // rows g and g + 8, log2 units
+  const float sc = a.scale * kLog2e;
+
+  if (k0 < ctx && k0 + 32 > lo) {      // the warp has a live key (the same for all its lanes)
+    // ---- S = Q K^T
+    float s[4][4];
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) s[nt][e] = 0.f;
+#pragma unroll
+      for (int db = 0; db < DB; ++db) {
+        mma_16816(s[nt], qlo[db].x, qhi[db].x, qlo[db].y, qhi[db].y, kf[nt][db].x, kf[nt][db].y);
+        mma_16816(s[nt], qlo[db].z, qhi[db].z, qlo[db].w, qhi[db].w, kf[nt][db].z, kf[nt][db].w);
+      }
+    }
+    // ---- mask and softmax (rows g and g + 8; the 4 lanes of a row share by shuffles)
+    float mx_lo = -INFINITY, mx_hi = -INFINITY;
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int key = k0 + nt * 8 + t * 2 + e;
+        const bool ok = key < ctx && key >= lo;
+        s[nt][e] = ok ? s[nt][e] * sc : -INFINITY;
+        s[nt][2 + e] = ok ? s[nt][2 + e] * sc : -INFINITY;
+        mx_lo = fmaxf(mx_lo, s[nt][e]);
+        mx_hi = fmaxf(mx_hi, s[nt][2 + e]);
+      }
+    mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+    mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+    mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+    mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+    m_lo = mx_lo;                       // finite: the warp has a live key
+    m_hi = mx_hi;
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        s[nt][e] = exp2f(s[nt][e] - m_lo);
+        s[nt][2 + e] = exp2f(s[nt][2 + e] - m_hi);
+        l_lo += s[nt][e];
+        l_hi += s[nt][2 + e];
+      }
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+    // ---- O = P V
+#pragma unroll
+    for (int ks = 0; ks < 2; ++ks) {
+      const uint32_t p0 = pack_bf16(s[2 * ks][0], s[2 * ks][1]), p1 = pack_bf16(s[2 * ks][2], s[2 * ks][3]);
+      const uint32_t p2 = pack_bf16(s[2 * ks + 1][0], s[2 * ks + 1][1]), p3 = pack_bf16(s[2 * ks + 1][2], s[2 * ks + 1][3]);
+#pragma unroll
+      for (int dg = 0; dg < DG; ++dg) {
+        const uint32_t va[4] = {vf[ks][0][dg].x, vf[ks][0][dg].y, vf[ks][0][dg].z, vf[ks][0][dg].w};
+        const uint32_t vb[4] = {vf[ks][1][dg].x, vf[ks][1][dg].y, vf[ks][1][dg].z, vf[ks][1][dg].w};
+        const uint32_t vc[4] = {vf[ks][2][dg].x, vf[ks][2][dg].y, vf[ks][2][dg].z, vf[ks][2][dg].w};
+        const uint32_t vd[4] = {vf[ks][3][dg].x, vf[ks][3][dg].y, vf[ks][3][dg].z, vf[ks][3][dg].w};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const uint32_t sel = (j & 1) ? 0x7632u : 0x5410u;
+          const uint32_t b0 = __byte_perm(va[j >> 1], vb[j >> 1], sel);   // keys t*2, t*2+1 at d = g*8 + j
+          const uint32_t b1 = __byte_perm(vc[j >> 1], vd[j >> 1], sel);   // keys t*2+8, t*2+9
+          mma_16816(o[dg][j], p0, p1, p2, p3, b0, b1);
+        }
+      }
+    }
+  }
+  // ---- the four warps merge: row r of warp w has (m, l) and o[r][:]
+  if (t == 0) {
+    sm_m[warp][g] = m_lo;
+    sm_m[warp][g + 8] = m_hi;
+    sm_l[warp][g] = l_lo;
+    sm_l[warp][g + 8] = l_hi;
+  }
+#pragma unroll
+  for (int dg = 0; dg < DG; ++dg)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int c = dg * 64 + j * 8 + t * 2;
+      *reinterpret_cast<float2*>(&sm_o[warp][g][c]) = make_float2(o[dg][j][0], o[dg][j][1]);
+      *reinterpret_cast<float2*>(&sm_o[warp][g + 8][c]) = make_float2(o[dg][j][2], o[dg][j][3]);
+    }
+  __syncthreads();
+  const int p_lo = lo / kPart, p_hi = (ctx - 1) / kPart;     // the item's live partitions, inclusive
+  const bool single = (p_lo == p_hi);
+  for (int i = threadIdx.x; i < G * kD; i += 128) {
+    const int r = i / kD, c = i - r * kD;                     // c: column as stored
+    const int d = (c & ~63) + (c & 7) * 8 + ((c & 63) >> 3);
+    float m = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) m = fmaxf(m, sm_m[w][r]);
+    float acc = 0.f, l = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float f = exp2f(sm_m[w][r] - m);     // a warp without live keys has m = -inf: weight 0
+      acc += f * sm_o[w][r][c];
+      l += f * sm_l[w][r];
+    }
+    const int head = kvh * G + r;
+    if (single) {                                  // the only partition: this is the result
+      a.out[static_cast<size_t>(tok) * a.out_stride + head * kD + d] = __float2bfloat16_rn(acc / l);
+    } else {
+      const size_t row = (static_cast<size_t>(item) * a.hq + head) * a.max_parts + part;
+      a.part_o[row * kD + d] = acc;
+      if (c == 0) {
+        a.part_ml[row * 2] = m * kLn2;             // natural-log units
+        a.part_ml[row * 2 + 1] = l;
+      }
+    }
+  }
+  if (single) return;
+  // ---- the CTA that finishes last among the item's partitions (for this kv head) merges them
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int* c = a.counters + item * a.hkv + kvh;
+    const int done = atomicAdd(c, 1) + 1;
+    sm_last = (done == p_hi - p_lo + 1);
+    if (sm_last) *c = 0;                           // ready for the next launch
+  }
+  __syncthreads();
+  if (!sm_last) return;
+  __threadfence();          // (every thread is past its reads of sm_o: the barrier above)
+  // weights of the partitions, all heads at once: w[r][p] = exp(m_p - max m) (sm_w), and the
+  // denominators; then the weighted sums in partition order, so that the result does not
+  // depend on which CTA merges
+  const int np = p_hi - p_lo + 1;
+  for (int r = warp; r < G; r += 4) {
+    const size_t row0 = (static_cast<size_t>(item) * a.hq + kvh * G + r) * a.max_parts + p_lo;
+    float m = -INFINITY;
+    for (int p = lane; p < np; p += 32) m = fmaxf(m, __ldcg(a.part_ml + (row0 + p) * 2));
+    m = warp_max(m);
+    float den = 0.f;
+    for (int p0 = 0; p0 < np; p0 += 32) {          // lanes in partition order, summed in that order below
+      const int p = p0 + lane;
+      float w = 0.f, l = 0.f;
+      if (p < np) {
+        w = expf(__ldcg(a.part_ml + (row0 + p) * 2) - m);
+        l = __ldcg(a.part_ml + (row0 + p) * 2 + 1);
+        sm_w[r][p] = w;
+      }
+      // ordered sum over the lanes: lane 0 first
+      float wl = w * l;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const float up = __shfl_up_sync(0xffffffffu, wl, o);
+        if (lane >= o) wl += up;
+      }
+      den += __shfl_sync(0xffffffffu, wl, 31);
+    }
+    if (lane == 0) sm_w[r][kMaxMergeParts] = den;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < G * kD; i += 128) {
+    const int r = i / kD, d = i - r * kD;
+    const int head = kvh * G + r;
+    const size_t row0 = (static_cast<size_t>(item) * a.hq + head) * a.max_parts + p_lo;
+    const float* po = a.part_o + row0 * kD + d;
+    float num = 0.f;
+    int p = 0;
+    for (; p + 4 <= np; p += 4) {                  // four loads in flight, added in order
+      const float v0 = __ldcg(po + static_cast<size_t>(p) * kD), v1 = __ldcg(po + static_cast<size_t>(p + 1) * kD);
+      const float v2 = __ldcg(po + static_cast<size_t>(p + 2) * kD), v3 = __ldcg(po + static_cast<size_t>(p + 3) * kD);
+      num += sm_w[r][p] * v0;
+      num += sm_w[r][p + 1] * v1;
+      num += sm_w[r][p + 2] * v2;
+      num += sm_w[r][p + 3] * v3;
+    }
+    for (; p < np; ++p) num += sm_w[r][p] * __ldcg(po + static_cast<size_t>(p) * kD);
+    a.out[static_cast<size_t>(tok) * a.out_stride + head * kD + d] = __float2bfloat16_rn(num / sm_w[r][kMaxMergeParts]);
+  }
+}
+#endif  // head size 64 or 128
 
 // ------------------------------------------------------------------ prefill
 constexpr int kBQ = 32, kBK = 32, kPreThreads = 128;
@@ -362,10 +634,9 @@ namespace {
 
 template <typename T>
 int launch_decode(const void* q, int q_stride, const void* kc, const void* vc, const int32_t* bt,
-                  int max_blocks, const int32_t* item_tok, const int32_t* seq_of_token,
-                  const int32_t* positions, float* part_o, float* part_ml, int max_parts, void* out,
-                  int out_stride, int items, int hq, int hkv, int page_size, int window, float scale,
-                  cudaStream_t stream) {
+                  int max_blocks, const int32_t* items, float* part_o, float* part_ml, int max_parts,
+                  int* counters, void* out, int out_stride, int nitems, int hq, int hkv, int page_size,
+                  int window, float scale, int impl, cudaStream_t stream) {
   DecodeArgs<T> a;
   a.q = static_cast<const T*>(q);
   a.q_stride = q_stride;
@@ -373,25 +644,36 @@ int launch_decode(const void* q, int q_stride, const void* kc, const void* vc, c
   a.vcache = static_cast<const T*>(vc);
   a.block_table = bt;
   a.max_blocks = max_blocks;
-  a.item_tok = item_tok;
-  a.seq_of_token = seq_of_token;
-  a.positions = positions;
+  a.items = reinterpret_cast<const int4*>(items);
   a.part_o = part_o;
   a.part_ml = part_ml;
   a.max_parts = max_parts;
+  a.counters = counters;
+  a.out = static_cast<T*>(out);
+  a.out_stride = out_stride;
   a.hq = hq;
   a.hkv = hkv;
   a.page_size = page_size;
   a.window = window;
   a.scale = scale;
-  dim3 grid(max_parts, hkv, items);
+  dim3 grid(max_parts, hkv, nitems);
+#ifdef RL_HAVE_MMA_DECODE
+  if constexpr (sizeof(T) == 2) {
+    // tensor-core kernel: groups of up to 16 heads, pages that hold whole 16-key steps
+    if (impl != 1 && hq / hkv <= 16 && page_size % 16 == 0 && counters != nullptr && max_parts <= kMaxMergeParts) {
+      decode_attn_mma_kernel<<<grid, 128, 0, stream>>>(a);
+      return static_cast<int>(cudaGetLastError());
+    }
+  }
+#endif
+  if (impl == 2) return static_cast<int>(cudaErrorInvalidValue);
   decode_attn_kernel<T><<<grid, kDecThreads, 0, stream>>>(a);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return static_cast<int>(e);
   int th = 32;
   while (th < kD) th <<= 1;
-  decode_merge_kernel<T><<<dim3(items, hq), th, 0, stream>>>(
-      part_o, part_ml, item_tok, positions, static_cast<T*>(out), out_stride, hq, max_parts, window);
+  decode_merge_kernel<T><<<dim3(nitems, hq), th, 0, stream>>>(
+      part_o, part_ml, a.items, static_cast<T*>(out), out_stride, hq, max_parts, window);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -441,21 +723,24 @@ int rl_attn_partition() { return kPart; }
 int rl_attn_tile_rows() { return kBQ; }
 
 // dtype: 0 = float32, 1 = bfloat16 (type of q, the cache and out).
-// max_parts = ceil(longest context this launch may see / 256); the grid has that many
+// items: int32 [nitems, 4] = (token index of the query, sequence index, context length, 0).
+// max_parts = ceil(longest context this launch may see / 128); the grid has that many
 // partitions per item and CTAs past an item's context return at once.
+// counters: int32 [nitems * hkv], zero before the first launch (the kernel leaves them zero).
+// impl: 0 = the tensor-core kernel where it applies (bfloat16, head size 64 or 128,
+// at most 16 heads per group), 1 = the CUDA-core kernel, 2 = the tensor-core kernel or an error.
 int rl_attn_decode(int dtype, const void* q, int q_stride, const void* kc, const void* vc,
-                   const int32_t* bt, int max_blocks, const int32_t* item_tok,
-                   const int32_t* seq_of_token, const int32_t* positions, float* part_o,
-                   float* part_ml, int max_parts, void* out, int out_stride, int items, int hq,
-                   int hkv, int page_size, int window, float scale, cudaStream_t stream) {
-  if (items <= 0) return 0;
+                   const int32_t* bt, int max_blocks, const int32_t* items, float* part_o,
+                   float* part_ml, int max_parts, int* counters, void* out, int out_stride, int nitems,
+                   int hq, int hkv, int page_size, int window, float scale, int impl, cudaStream_t stream) {
+  if (nitems <= 0) return 0;
   if (dtype == 0)
-    return launch_decode<float>(q, q_stride, kc, vc, bt, max_blocks, item_tok, seq_of_token, positions,
-                                part_o, part_ml, max_parts, out, out_stride, items, hq, hkv, page_size,
-                                window, scale, stream);
-  return launch_decode<bf16>(q, q_stride, kc, vc, bt, max_blocks, item_tok, seq_of_token, positions,
-                             part_o, part_ml, max_parts, out, out_stride, items, hq, hkv, page_size,
-                             window, scale, stream);
+    return launch_decode<float>(q, q_stride, kc, vc, bt, max_blocks, items, part_o, part_ml, max_parts,
+                                counters, out, out_stride, nitems, hq, hkv, page_size, window, scale, impl,
+                                stream);
+  return launch_decode<bf16>(q, q_stride, kc, vc, bt, max_blocks, items, part_o, part_ml, max_parts,
+                             counters, out, out_stride, nitems, hq, hkv, page_size, window, scale, impl,
+                             stream);
 }
 
 int rl_attn_prefill(int dtype, const void* q, int q_stride, const void* kc, const void* vc,

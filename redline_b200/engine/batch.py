@@ -9,7 +9,7 @@ G cache groups, B block-table width, L tiles):
 
     token_ids[T] token_src[T] positions[T] seq_of_token[T]
     slots[G][T] block_table[G][S*B]
-    state_slot[S] decode_tok[S] tile_seq[L] tile_tok[L] tile_rows[L]
+    state_slot[S] decode_info[S][4] tile_seq[L] tile_tok[L] tile_rows[L]
     logit_rows[R] temperature[R] top_k[R] top_p[R] seed_lo[R] seed_hi[R] sample_pos[R]
 
 (the reference's layout: src/core/batch_builder.cpp:17-46; one upload:
@@ -64,7 +64,7 @@ class Layout:
         def take(n: int) -> int:
             nonlocal off
             o = off
-            off += n
+            off += (n + 3) // 4 * 4      # every field starts on a 16-byte boundary
             return o
 
         self.token_ids = take(T)
@@ -74,7 +74,7 @@ class Layout:
         self.slots = [take(T) for _ in range(G)]
         self.block_table = [take(S * B) for _ in range(G)]
         self.state_slot = take(S)
-        self.decode_tok = take(S)
+        self.decode_info = take(4 * S)   # per decode item: token index, sequence index, context length, 0
         self.tile_seq = take(L)
         self.tile_tok = take(L)
         self.tile_rows = take(L)
@@ -107,7 +107,7 @@ class StepContext:
     positions: torch.Tensor
     seq_of_token: torch.Tensor
     state_slot: torch.Tensor
-    decode_tok: torch.Tensor
+    decode_info: torch.Tensor    # [S, 4]
     tile_seq: torch.Tensor
     tile_tok: torch.Tensor
     tile_rows: torch.Tensor
@@ -166,7 +166,7 @@ class BatchBuilder:
         return dict(
             token_ids=v(lay.token_ids, lay.T), token_src=v(lay.token_src, lay.T),
             positions=v(lay.positions, lay.T), seq_of_token=v(lay.seq_of_token, lay.T),
-            state_slot=v(lay.state_slot, lay.S), decode_tok=v(lay.decode_tok, lay.S),
+            state_slot=v(lay.state_slot, lay.S), decode_info=v(lay.decode_info, 4 * lay.S).view(lay.S, 4),
             tile_seq=v(lay.tile_seq, lay.L), tile_tok=v(lay.tile_tok, lay.L), tile_rows=v(lay.tile_rows, lay.L),
             logit_rows=v(lay.logit_rows, lay.R), temperature=f32(lay.temperature, lay.R),
             top_k=v(lay.top_k, lay.R), top_p=f32(lay.top_p, lay.R), seed_lo=v(lay.seed_lo, lay.R),
@@ -245,7 +245,7 @@ class BatchBuilder:
                 h[o:o + len(tb)] = tb
             h[lay.state_slot + si] = s.cache.state_slot
             if n == 1:
-                h[lay.decode_tok + nd] = t
+                h[lay.decode_info + 4 * nd:lay.decode_info + 4 * nd + 3] = (t, si, end)
                 nd += 1
                 max_ctx = max(max_ctx, end)
             else:
@@ -283,7 +283,7 @@ class BatchBuilder:
             for i in range(S_real, pad_to):
                 h[lay.token_src + i] = -1
                 h[lay.seq_of_token + i] = i
-                h[lay.decode_tok + i] = i
+                h[lay.decode_info + 4 * i:lay.decode_info + 4 * i + 3] = (i, i, 1)
                 h[lay.logit_rows + i] = i
                 h[lay.top_p + i:lay.top_p + i + 1].view(np.float32)[0] = 1.0
                 h[lay.sample_pos + i] = 1

@@ -119,7 +119,9 @@ class DecoderModel:
         pending = None
         for i, call in enumerate(self.spec.order):
             pending = self.blocks[call.layer].forward(residual, pending, ctx, caches[i], states[i])
-        if R > 0:
+        if R > 0 and pending is None and self.head.forward_from(residual, self.final_norm, ctx.logit_rows, R, logits):
+            pass
+        elif R > 0:
             xr = ws.get("head.in", (logits.shape[0], self.spec.hidden_size), rt.dtype)[:R]
             self.final_norm.add_norm(residual, pending, xr, rows_idx=ctx.logit_rows, rows=R)
             self.head.forward(xr, R, logits)

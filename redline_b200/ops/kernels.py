@@ -160,6 +160,60 @@ def gemm_tn_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, rows: Opti
              x.stride(0), out.stride(0), _stream()), "gemm_tn_simt")
 
 
+
+# ---------------------------------------------------------------- skinny gemm
+
+SKINNY_MAX_ROWS = 16
+EPI_BF16, EPI_F32, EPI_ADD_RESIDUAL, EPI_SWIGLU = 0, 1, 2, 3
+_sm_count: Dict[int, int] = {}
+
+
+def sm_count(device: torch.device) -> int:
+    i = device.index if device.index is not None else torch.cuda.current_device()
+    if i not in _sm_count:
+        _sm_count[i] = torch.cuda.get_device_properties(i).multi_processor_count
+    return _sm_count[i]
+
+
+def skinny_ok(rows: int, w: torch.Tensor, x_dtype: torch.dtype) -> bool:
+    """Whether gemm_skinny takes this product: few rows, bfloat16 operands, K a multiple of 8."""
+    return (rows <= SKINNY_MAX_ROWS and w.dtype == torch.bfloat16 and x_dtype == torch.bfloat16
+            and w.shape[1] % 8 == 0 and w.is_contiguous())
+
+
+def gemm_skinny(w: torch.Tensor, y: torch.Tensor, epilogue: int, rows: int, x: Optional[torch.Tensor] = None,
+                residual: Optional[torch.Tensor] = None, norm_w: Optional[torch.Tensor] = None,
+                eps: float = 0.0, rows_idx: Optional[torch.Tensor] = None) -> None:
+    """y = epilogue(x @ w^T) for at most 16 rows on the tensor cores (csrc/gemm_skinny.cu).
+
+    x given: bfloat16 activations [rows, K].  residual + norm_w given instead: x is
+    bfloat16(rmsnorm(residual[rows_idx]) * norm_w) formed inside the kernel.
+    epilogue EPI_BF16 / EPI_F32: store into y; EPI_ADD_RESIDUAL: y (float32 stream) += product;
+    EPI_SWIGLU: w is [2 N, K] (gate rows, then up rows), y = silu(gate) * up, [rows, N]."""
+    _need_cuda(w, y)
+    f = _fn(_lib("gemm_skinny", "gemm_skinny.cu"), "rl_gemm_skinny",
+            [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_float, c_int, c_void_p, c_int,
+             c_int, c_int, c_int, c_int, c_int, c_void_p])
+    K = w.shape[1]
+    N = w.shape[0] // 2 if epilogue == EPI_SWIGLU else w.shape[0]
+    norm = residual is not None
+    if norm:
+        if norm_w is None or residual.dtype != torch.float32 or residual.shape[1] != K or residual.stride(0) != K:
+            raise KernelError("gemm_skinny: the fused norm needs a contiguous float32 residual [*, K] and a weight")
+        ldx = 0
+    else:
+        if x is None or x.dtype != torch.bfloat16 or x.shape[1] != K or x.stride(1) != 1:
+            raise KernelError("gemm_skinny: x must be bfloat16 [rows, K]")
+        ldx = x.stride(0)
+    want = {EPI_BF16: torch.bfloat16, EPI_F32: torch.float32, EPI_ADD_RESIDUAL: torch.float32,
+            EPI_SWIGLU: torch.bfloat16}[epilogue]
+    if y.dtype != want or y.shape[1] != N or y.stride(1) != 1:
+        raise KernelError(f"gemm_skinny: output must be {want} [rows, {N}]")
+    _check(f(_ptr(w), _ptr(x), ldx, _ptr(residual), _ptr(norm_w),
+             1 if (norm_w is not None and norm_w.dtype == torch.float32) else 0, _ptr(rows_idx), float(eps),
+             1 if norm else 0, _ptr(y), y.stride(0), epilogue, rows, N, K, sm_count(w.device), _stream()),
+           "gemm_skinny")
+
 # ------------------------------------------------------------------- attention
 
 MAX_HEAD_DIM = 256
@@ -172,26 +226,36 @@ def _attn(head_dim: int) -> ctypes.CDLL:
     return _lib(f"attention_d{head_dim}", "attention.cu", {"RL_HEAD_DIM": head_dim})
 
 
-DECODE_PARTITION = 256
+DECODE_PARTITION = 128
 PREFILL_TILE_ROWS = 32
 
 
 def attn_decode(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcache: torch.Tensor,
-                block_table: torch.Tensor, item_tok: torch.Tensor, seq_of_token: torch.Tensor,
-                positions: torch.Tensor, part_o: torch.Tensor, part_ml: torch.Tensor, max_parts: int,
-                out: torch.Tensor, items: int, num_heads: int, num_kv_heads: int, head_dim: int,
-                page_size: int, window: int, scale: float) -> None:
+                block_table: torch.Tensor, items: torch.Tensor, part_o: torch.Tensor, part_ml: torch.Tensor,
+                max_parts: int, counters: Optional[torch.Tensor], out: torch.Tensor, nitems: int,
+                num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, window: int, scale: float,
+                impl: int = 0) -> None:
+    """One query token per item over the paged cache.
+
+    items     int32 [nitems, 4]: (token index of the query, sequence index, context length, 0)
+    counters  int32 [nitems * num_kv_heads], zero (the tensor-core kernel needs and keeps them zero)
+    impl      0: tensor-core kernel where it applies, else CUDA-core; 1: CUDA-core; 2: tensor-core or error
+    """
     _need_cuda(q, kcache, out)
     f = _fn(_attn(head_dim), "rl_attn_decode",
-            [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
-             c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p])
-    need = items * num_heads * max_parts
+            [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+             c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p])
+    need = nitems * num_heads * max_parts
     if part_o.numel() < need * head_dim or part_ml.numel() < need * 2:
         raise KernelError("attn_decode: partition workspace too small")
+    if counters is not None and counters.numel() < nitems * num_kv_heads:
+        raise KernelError("attn_decode: counter workspace too small")
+    if items.data_ptr() % 16 != 0:
+        raise KernelError("attn_decode: items must be 16-byte aligned")
     _check(f(_code(q.dtype), _ptr(q), q_stride, _ptr(kcache), _ptr(vcache), _ptr(block_table),
-             block_table.shape[1], _ptr(item_tok), _ptr(seq_of_token), _ptr(positions), _ptr(part_o),
-             _ptr(part_ml), max_parts, _ptr(out), out.stride(0), items, num_heads, num_kv_heads, page_size,
-             window, float(scale), _stream()), "attn_decode", 2)
+             block_table.shape[1], _ptr(items), _ptr(part_o), _ptr(part_ml), max_parts, _ptr(counters), _ptr(out),
+             out.stride(0), nitems, num_heads, num_kv_heads, page_size, window, float(scale), impl, _stream()),
+           "attn_decode", 2)
 
 
 def attn_prefill(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcache: torch.Tensor,
@@ -237,6 +301,7 @@ def build_all(head_dims=(64, 128), verbose: bool = True) -> None:
     """Compiles every kernel family (attention for the given head sizes)."""
     build.compile_module("elementwise", "elementwise.cu", verbose=verbose)
     build.compile_module("gemm_simt", "gemm_simt.cu", verbose=verbose)
+    build.compile_module("gemm_skinny", "gemm_skinny.cu", verbose=verbose)
     build.compile_module("sampling", "sampling.cu", verbose=verbose)
     for d in head_dims:
         build.compile_module(f"attention_d{d}", "attention.cu", {"RL_HEAD_DIM": d}, verbose=verbose)

@@ -1,6 +1,8 @@
 """y = x W^T for the linear layers.
 
-* bfloat16 x, bfloat16 W: a library matrix product (cuBLAS through torch), as the
+* bfloat16 x, bfloat16 W, at most 16 rows (a small decode batch): the package's own
+  tensor-core kernel built around the weight stream (csrc/gemm_skinny.cu).
+* bfloat16 x, bfloat16 W, more rows: a library matrix product (cuBLAS through torch), as the
   reference uses cuBLASLt for its half-precision products
   (src/cuda/gemm/cublaslt_gemm.cpp:97-111); float32 output for the logits.
 * anything with a float32 operand: the package's own CUDA-core kernel, which is a
@@ -40,6 +42,10 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     if not x.is_cuda:
         raise kernels.KernelError("linear runs on CUDA tensors only; there is no CPU fallback")
     if x.shape[0] == 0:
+        return out
+    if kernels.skinny_ok(x.shape[0], w, x.dtype) and out.stride(1) == 1 and x.stride(0) % 8 == 0 and x.stride(1) == 1:
+        kernels.gemm_skinny(w, out, kernels.EPI_BF16 if out.dtype == torch.bfloat16 else kernels.EPI_F32,
+                            x.shape[0], x=x)
         return out
     if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
         if out.dtype == torch.bfloat16:

@@ -88,9 +88,41 @@ class GQAttention(Mixer):
     def forward(self, x, ctx, cache: Optional[LayerCache], state=None) -> torch.Tensor:
         p, rt = self.params, self.rt
         T = ctx.T
-        ws = rt.workspace
-        qkv = ws.get("attn.qkv", (rt.max_tokens, self.qkv_size), rt.dtype)[:T]
+        qkv = rt.workspace.get("attn.qkv", (rt.max_tokens, self.qkv_size), rt.dtype)[:T]
         linear(x, self.w_qkv, qkv)
+        attn = self._attend(qkv, ctx, cache)
+        out = rt.workspace.get("mixer.out", (rt.max_tokens, p.hidden_size), rt.dtype)[:T]
+        linear(attn, self.w_o, out)
+        if self.b_o is not None:
+            kernels.add_bias(out, self.b_o)
+        return out
+
+    def forward_into(self, residual, norm, ctx, cache: Optional[LayerCache], state=None) -> bool:
+        rt = self.rt
+        T = ctx.T
+        rms = norm.rms_params()
+        if (rms is None or self.b_o is not None or rt.dtype != torch.bfloat16
+                or not kernels.skinny_ok(T, self.w_qkv, rt.dtype) or not kernels.skinny_ok(T, self.w_o, rt.dtype)):
+            return False
+        qkv = rt.workspace.get("attn.qkv", (rt.max_tokens, self.qkv_size), rt.dtype)[:T]
+        kernels.gemm_skinny(self.w_qkv, qkv, kernels.EPI_BF16, T, residual=residual, norm_w=rms[0], eps=rms[1])
+        attn = self._attend(qkv, ctx, cache)
+        kernels.gemm_skinny(self.w_o, residual, kernels.EPI_ADD_RESIDUAL, T, x=attn)
+        return True
+
+    def _counters(self, max_items: int) -> torch.Tensor:
+        """Arrival counters of the decode kernel's fused merge: zero between launches."""
+        c = getattr(self, "_cnt", None)
+        if c is None or c.numel() < max_items * self.params.num_kv_heads:
+            c = torch.zeros(max_items * self.params.num_kv_heads, dtype=torch.int32, device=self.rt.device)
+            self._cnt = c
+        return c
+
+    def _attend(self, qkv, ctx, cache: LayerCache) -> torch.Tensor:
+        """Bias, position encoding, cache write and attention on the projected [q | k | v]."""
+        p, rt = self.params, self.rt
+        T = ctx.T
+        ws = rt.workspace
         if self.b_qkv is not None:
             kernels.add_bias(qkv, self.b_qkv)
         tables = self.position.rotary_tables()
@@ -106,16 +138,12 @@ class GQAttention(Mixer):
                             torch.float32)
             part_ml = ws.get("attn.part_ml", (ctx.max_items * p.num_heads * ctx.parts_capacity * 2,),
                              torch.float32)
-            kernels.attn_decode(qkv, self.qkv_size, cache.k, cache.v, g.block_table, ctx.decode_tok,
-                                ctx.seq_of_token, ctx.positions, part_o, part_ml, ctx.decode_parts, attn,
+            kernels.attn_decode(qkv, self.qkv_size, cache.k, cache.v, g.block_table, ctx.decode_info,
+                                part_o, part_ml, ctx.decode_parts, self._counters(ctx.max_items), attn,
                                 ctx.num_decode, p.num_heads, p.num_kv_heads, p.head_dim, rt.page_size,
                                 p.window, self.scale)
         if ctx.num_tiles > 0:
             kernels.attn_prefill(qkv, self.qkv_size, cache.k, cache.v, g.block_table, ctx.tile_seq,
                                  ctx.tile_tok, ctx.tile_rows, ctx.positions, attn, ctx.num_tiles, p.num_heads,
                                  p.num_kv_heads, p.head_dim, rt.page_size, p.window, self.scale)
-        out = ws.get("mixer.out", (rt.max_tokens, p.hidden_size), rt.dtype)[:T]
-        linear(attn, self.w_o, out)
-        if self.b_o is not None:
-            kernels.add_bias(out, self.b_o)
-        return out
+        return attn

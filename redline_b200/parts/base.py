@@ -127,6 +127,11 @@ class Norm(Part):
         those rows are produced and residual is not changed."""
         raise NotImplementedError
 
+    def rms_params(self) -> Optional[Tuple[torch.Tensor, float]]:
+        """(weight, eps) if this norm is y = x * rsqrt(mean(x^2) + eps) * weight, which a
+        consumer may then compute itself from the residual stream; None otherwise."""
+        return None
+
 
 class PositionEncoding(Part):
     """How positions enter a mixer.  A rotary encoding exposes ``rotary_tables()``
@@ -154,10 +159,21 @@ class Mixer(Part):
         call's slot pool [slots, *state shape]; ``ctx.state_slot`` maps sequences to slots."""
         raise NotImplementedError
 
+    def forward_into(self, residual: torch.Tensor, norm: Norm, ctx, cache: Optional[LayerCache],
+                     state: Optional[torch.Tensor]) -> bool:
+        """Optional fused form for small batches: residual += mixer(norm(residual)), the norm
+        computed by the mixer's first kernel and the add by its last.  Returns False (and
+        does nothing) when the part does not take this batch that way."""
+        return False
+
 
 class FeedForward(Part):
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         raise NotImplementedError
+
+    def forward_into(self, residual: torch.Tensor, norm: Norm, ctx) -> bool:
+        """Optional fused form: residual += ffn(norm(residual)); see ``Mixer.forward_into``."""
+        return False
 
 
 class Embedding(Part):
@@ -173,6 +189,11 @@ class Head(Part):
     def forward(self, x: torch.Tensor, rows: int, out: torch.Tensor) -> None:
         """x [R, H] -> out [R, V] float32."""
         raise NotImplementedError
+
+    def forward_from(self, residual: torch.Tensor, norm: Norm, rows_idx: torch.Tensor, rows: int,
+                     out: torch.Tensor) -> bool:
+        """Optional fused form: out[:rows] = head(norm(residual[rows_idx])).  False if not taken."""
+        return False
 
 
 class Block:

@@ -66,3 +66,14 @@ class LMHead(Head):
 
     def forward(self, x: torch.Tensor, rows: int, out: torch.Tensor) -> None:
         linear(x[:rows], self.weight, out[:rows])
+
+    def forward_from(self, residual, norm, rows_idx, rows: int, out: torch.Tensor) -> bool:
+        rms = norm.rms_params()
+        # (for a very tall matrix the library product already runs at the bandwidth limit;
+        #  the fused form pays off where the product is short and launches dominate)
+        if (rms is None or self.rt.dtype != torch.bfloat16 or self.weight.shape[0] > 32768
+                or not kernels.skinny_ok(rows, self.weight, self.rt.dtype)):
+            return False
+        kernels.gemm_skinny(self.weight, out, kernels.EPI_F32, rows, residual=residual, norm_w=rms[0], eps=rms[1],
+                            rows_idx=rows_idx)
+        return True

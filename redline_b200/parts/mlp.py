@@ -64,3 +64,15 @@ class SwiGLUMLP(FeedForward):
         if self.b_down is not None:
             kernels.add_bias(out, self.b_down)
         return out
+
+    def forward_into(self, residual, norm, ctx) -> bool:
+        p, rt = self.params, self.rt
+        T = ctx.T
+        rms = norm.rms_params()
+        if (rms is None or self.b_gate_up is not None or self.b_down is not None or rt.dtype != torch.bfloat16
+                or not kernels.skinny_ok(T, self.w_gate_up, rt.dtype) or not kernels.skinny_ok(T, self.w_down, rt.dtype)):
+            return False
+        act = rt.workspace.get("ffn.act", (rt.max_tokens, p.intermediate_size), rt.dtype)[:T]
+        kernels.gemm_skinny(self.w_gate_up, act, kernels.EPI_SWIGLU, T, residual=residual, norm_w=rms[0], eps=rms[1])
+        kernels.gemm_skinny(self.w_down, residual, kernels.EPI_ADD_RESIDUAL, T, x=act)
+        return True

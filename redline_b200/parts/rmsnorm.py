@@ -33,3 +33,6 @@ class RMSNorm(Norm):
 
     def add_norm(self, residual, delta, out, rows_idx=None, rows=None) -> None:
         kernels.add_rmsnorm(residual, delta, self.weight, out, self.params.eps, rows_idx, rows)
+
+    def rms_params(self):
+        return self.weight, self.params.eps

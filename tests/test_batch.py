@@ -39,7 +39,7 @@ def test_mixed_batch_layout():
     slots = g.slots.tolist()
     assert slots[:40] == [16 + i for i in range(40)]          # pages 1, 2, 3 are consecutive
     assert slots[40] == 5 * 16 + 4 and slots[41:] == [10 * 16, 10 * 16 + 1, 10 * 16 + 2]
-    assert ctx.decode_tok.tolist()[:1] == [40] and ctx.decode_parts == 1
+    assert ctx.decode_info.tolist()[0] == [40, 1, 21, 0] and ctx.decode_parts == 1
     assert ctx.tile_seq.tolist() == [0, 0, 2] and ctx.tile_tok.tolist() == [0, 32, 41]
     assert ctx.tile_rows.tolist() == [32, 8, 3]
     assert ctx.logit_rows.tolist() == [39, 40, 41, 43]
@@ -60,7 +60,8 @@ def test_padding_of_a_decode_batch_and_device_fed_tokens():
     assert ctx.token_src.tolist() == [-1, 1, -1, -1] and ctx.positions.tolist() == [70, 5, 0, 0]
     assert ctx.groups[0].slots.tolist()[2:] == [0, 0]           # dummy rows write page 0
     assert ctx.groups[0].block_table[2].tolist() == [0] * 8
-    assert ctx.decode_tok.tolist() == [0, 1, 2, 3] and ctx.logit_rows.tolist() == [0, 1, 2, 3]
+    assert ctx.decode_info.tolist() == [[0, 0, 71, 0], [1, 1, 6, 0], [2, 2, 1, 0], [3, 3, 1, 0]]
+    assert ctx.logit_rows.tolist() == [0, 1, 2, 3]
     assert ctx.decode_parts == ctx.parts_capacity == 1
     with pytest.raises(ValueError, match="single tokens"):
         b.build([Segment(x, [1, 2], 71, want=(1,))], pad_to=4)

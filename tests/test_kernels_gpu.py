@@ -150,7 +150,7 @@ def reference_attention(seqs, Hq, Hkv, D, cos, sin, scale, window, dtype):
 
 
 def run_attention(dtype, Hq, Hkv, D, lens_past, lens_new, page_size=16, window=0, seed=0, sharp=None,
-                  poison=True):
+                  poison=True, decode_impl=0):
     """Writes the past through rope_kv_write, then runs the new tokens (decode kernel for
     single tokens, prefill kernel for portions) and compares with the reference."""
     from redline_b200.config.model_config import RopeScaling
@@ -194,11 +194,14 @@ def run_attention(dtype, Hq, Hkv, D, lens_past, lens_new, page_size=16, window=0
         kernels.rope_kv_write(qkv, pos_d, slot_d, cosd, sind, kc, vc, Hq, Hkv, D, page_size, status)
         out = torch.full((t, Hq * D), float("nan"), device=DEV, dtype=DT[dtype])
         if dec:
-            parts = (max(total) + 255) // 256
-            po = torch.empty(len(dec) * Hq * parts * D, device=DEV)
-            pm = torch.empty(len(dec) * Hq * parts * 2, device=DEV)
-            kernels.attn_decode(qkv, qkv.shape[1], kc, vc, bt, i32(dec), seq_d, pos_d, po, pm, parts, out,
-                                len(dec), Hq, Hkv, D, page_size, window, scale)
+            parts = (max(total) + kernels.DECODE_PARTITION - 1) // kernels.DECODE_PARTITION
+            po = torch.full((len(dec) * Hq * parts * D,), float("nan"), device=DEV)
+            pm = torch.full((len(dec) * Hq * parts * 2,), float("nan"), device=DEV)
+            items = i32([[tk, seq_of[tk], pos[tk] + 1, 0] for tk in dec])
+            counters = torch.zeros(len(dec) * Hkv, dtype=torch.int32, device=DEV)
+            kernels.attn_decode(qkv, qkv.shape[1], kc, vc, bt, items, po, pm, parts, counters, out,
+                                len(dec), Hq, Hkv, D, page_size, window, scale, decode_impl)
+            assert int(counters.abs().max()) == 0, "the merge counters must be left at zero"
         if tiles:
             kernels.attn_prefill(qkv, qkv.shape[1], kc, vc, bt, i32([x[0] for x in tiles]),
                                  i32([x[1] for x in tiles]), i32([x[2] for x in tiles]), pos_d, out, len(tiles),
@@ -229,8 +232,22 @@ def test_attention_prefill_whole_and_with_a_cached_past(dtype, Hq, Hkv, D):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("Hq,Hkv,D", ATTN_SHAPES)
 def test_attention_decode_lengths_across_pages_and_partitions(dtype, Hq, Hkv, D):
-    run_attention(dtype, Hq, Hkv, D, [0, 4, 15, 16, 128], [1, 1, 1, 1, 1], seed=3)
-    run_attention(dtype, Hq, Hkv, D, [255, 256, 257, 699], [1, 1, 1, 1], seed=4)
+    # impl 1: the CUDA-core kernel; 0: the tensor-core kernel where it applies (bfloat16, D 64 / 128)
+    for impl in (0, 1):
+        run_attention(dtype, Hq, Hkv, D, [0, 4, 15, 16, 128], [1, 1, 1, 1, 1], seed=3, decode_impl=impl)
+        run_attention(dtype, Hq, Hkv, D, [255, 256, 257, 699], [1, 1, 1, 1], seed=4, decode_impl=impl)
+
+
+@pytest.mark.parametrize("Hq,Hkv,D", [(4, 2, 64), (32, 8, 64), (3, 1, 128), (16, 1, 64), (24, 8, 128), (7, 7, 64)])
+@pytest.mark.parametrize("page_size", [16, 32, 64])
+def test_attention_decode_tensor_core_kernel(Hq, Hkv, D, page_size):
+    """impl 2 insists on the tensor-core kernel: group sizes 1 to 16, both head sizes, every page size,
+    lengths around the 32-key rounds, the 64-key warps and the 256-key partitions, and windows."""
+    run_attention("bfloat16", Hq, Hkv, D, [0, 31, 32, 33, 63, 64, 65], [1] * 7, page_size=page_size, seed=11, decode_impl=2)
+    run_attention("bfloat16", Hq, Hkv, D, [255, 256, 300, 511, 512, 1030], [1] * 6, page_size=page_size, seed=12, decode_impl=2)
+    for window in (1, 20, 100, 300):
+        run_attention("bfloat16", Hq, Hkv, D, [5, 99, 290, 700], [1] * 4, page_size=page_size, window=window, seed=13,
+                      decode_impl=2)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -267,6 +284,7 @@ def test_a_far_key_is_found_among_hundreds(dtype):
             for h in range(Hkv):
                 x[far, (Hq + h) * D:(Hq + h + 1) * D] = unrotate(u, cos[far], sin[far])
         run_attention(dtype, Hq, Hkv, D, [total - 1], [1], seed=9, sharp=sharp)     # decode kernel
+        run_attention(dtype, Hq, Hkv, D, [total - 1], [1], seed=9, sharp=sharp, decode_impl=1)
         run_attention(dtype, Hq, Hkv, D, [total - 40], [40], seed=9, sharp=sharp)   # prefill kernel
 
 
@@ -326,3 +344,79 @@ def test_resolve_ids_and_bias_and_residual():
     want = r + d.float()
     kernels.add_residual(r, d)
     assert torch.equal(r, want)
+
+
+SKINNY_SHAPES = [(1, 3072, 2048), (8, 2048, 8192), (3, 331, 200), (9, 1000, 384), (16, 64, 328), (13, 704, 256),
+                 (16, 2048, 2048), (5, 16, 8), (8, 5000, 264), (16, 300, 8192)]
+
+
+@pytest.mark.parametrize("M,N,K", SKINNY_SHAPES)
+def test_gemm_skinny_plain_epilogues(M, N, K):
+    g = torch.Generator(device="cuda").manual_seed(M * N + K)
+    x = torch.randn(M + 3, K, device=DEV, generator=g).to(torch.bfloat16)[:M]
+    w = (torch.randn(N, K, device=DEV, generator=g) * 0.05).to(torch.bfloat16)
+    ref = x.double() @ w.double().T
+    y = torch.full((M, N), float("nan"), device=DEV, dtype=torch.bfloat16)
+    kernels.gemm_skinny(w, y, kernels.EPI_BF16, M, x=x)
+    close(y, ref, 1.2e-2)
+    yf = torch.full((M, N), float("nan"), device=DEV)
+    kernels.gemm_skinny(w, yf, kernels.EPI_F32, M, x=x)
+    close(yf, ref, 2e-5)
+    res = torch.randn(M, N, device=DEV, generator=g)
+    want = res.double() + ref.to(torch.bfloat16).double()
+    kernels.gemm_skinny(w, res, kernels.EPI_ADD_RESIDUAL, M, x=x)
+    close(res, want, 1e-2)
+    if M > 1:       # a row does not depend on its neighbours, bit for bit, nor on the padding it gets
+        y1 = torch.empty(1, N, device=DEV)
+        kernels.gemm_skinny(w, y1, kernels.EPI_F32, 1, x=x[M // 2:M // 2 + 1])
+        assert torch.equal(y1[0], yf[M // 2])
+    y2 = torch.empty(M, N, device=DEV)
+    kernels.gemm_skinny(w, y2, kernels.EPI_F32, M, x=x)
+    assert torch.equal(y2, yf)      # and not on the run
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 8192, 2048), (8, 704, 256), (7, 328, 200), (12, 1024, 384), (16, 96, 4096)])
+@pytest.mark.parametrize("w32", [False, True])
+def test_gemm_skinny_norm_prologue_and_gated_epilogue(M, N, K, w32):
+    g = torch.Generator(device="cuda").manual_seed(N + K)
+    T = M + 5
+    res = torch.randn(T, K, device=DEV, generator=g) * 2
+    nw = (1 + 0.1 * torch.randn(K, device=DEV, generator=g)).to(torch.float32 if w32 else torch.bfloat16)
+    idx = torch.randperm(T, device=DEV, generator=g)[:M].to(torch.int32)
+    w = (torch.randn(2 * N, K, device=DEV, generator=g) * 0.05).to(torch.bfloat16)
+    eps = 1e-5
+    P.STORE_DTYPE = torch.bfloat16
+    try:
+        xn = P.rmsnorm(res.double().cpu(), nw.cpu(), eps)                 # rounded to bfloat16, as the kernel does
+        xg = P.rmsnorm(res[idx.long()].double().cpu(), nw.cpu(), eps)
+        gate, up = P.linear(xn[:M], w[:N].cpu()), P.linear(xn[:M], w[N:].cpu())
+        want_act = P.swiglu(gate, up)
+    finally:
+        P.STORE_DTYPE = None
+    act = torch.full((M, N), float("nan"), device=DEV, dtype=torch.bfloat16)
+    kernels.gemm_skinny(w, act, kernels.EPI_SWIGLU, M, residual=res, norm_w=nw, eps=eps)
+    close(act, want_act, 2e-2)
+    logits = torch.full((M, 2 * N), float("nan"), device=DEV)
+    kernels.gemm_skinny(w, logits, kernels.EPI_F32, M, residual=res, norm_w=nw, eps=eps, rows_idx=idx)
+    close(logits, xg @ w.double().cpu().T, 1e-2)
+    y = torch.empty(M, 2 * N, device=DEV, dtype=torch.bfloat16)
+    kernels.gemm_skinny(w, y, kernels.EPI_BF16, M, residual=res, norm_w=nw, eps=eps)
+    close(y, xn[:M] @ w.double().cpu().T, 1.5e-2)
+    # the gated product without the fused norm
+    xb = xn[:M].to(torch.bfloat16).to(DEV)
+    act2 = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    kernels.gemm_skinny(w, act2, kernels.EPI_SWIGLU, M, x=xb)
+    close(act2, want_act, 2e-2)
+
+
+def test_gemm_skinny_refuses_what_it_cannot_do():
+    w = torch.zeros(32, 20, device=DEV, dtype=torch.bfloat16)      # K no multiple of 8
+    x = torch.zeros(4, 20, device=DEV, dtype=torch.bfloat16)
+    assert not kernels.skinny_ok(4, w, torch.bfloat16)
+    with pytest.raises(kernels.KernelError):
+        kernels.gemm_skinny(w, torch.zeros(4, 32, device=DEV, dtype=torch.bfloat16), kernels.EPI_BF16, 4, x=x)
+    w = torch.zeros(32, 64, device=DEV, dtype=torch.bfloat16)
+    assert not kernels.skinny_ok(17, w, torch.bfloat16) and kernels.skinny_ok(16, w, torch.bfloat16)
+    with pytest.raises(kernels.KernelError):
+        kernels.gemm_skinny(w, torch.zeros(4, 32, device=DEV), kernels.EPI_BF16, 4,
+                            x=torch.zeros(4, 64, device=DEV, dtype=torch.bfloat16))
