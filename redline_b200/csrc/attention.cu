@@ -759,3 +759,68 @@ int rl_attn_prefill(int dtype, const void* q, int q_stride, const void* kc, cons
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------------------------
+// The entry point that allocates nothing (declared and explained in attention_noalloc.h).
+// ------------------------------------------------------------------------------------
+#include <cstdio>
+
+#include "attention_noalloc.h"
+
+namespace {
+
+// Scratch of rl_attn_decode_noalloc.  In host code this name is only a handle for
+// cudaGetSymbolAddress, never a pointer to pass to a kernel.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[RL_ATTN_NOALLOC_SCRATCH_BYTES];
+
+constexpr int kMaxDevices = 64;
+unsigned char* g_noalloc_ptr[kMaxDevices];   // device address of the array, per device; null until looked up
+
+}  // namespace
+
+extern "C" int rl_attn_decode_noalloc(int dtype, const void* q, int q_stride, const void* kcache,
+                                      const void* vcache, const int32_t* block_table, int max_blocks,
+                                      const int32_t* items, int max_parts, void* out, int out_stride,
+                                      int nitems, int hq, int hkv, int page_size, int window, float scale,
+                                      cudaStream_t stream, char* errbuf, int errbuf_len) {
+  if (errbuf && errbuf_len > 0) errbuf[0] = 0;
+  if (nitems <= 0) return 0;
+  const size_t counter_bytes = (static_cast<size_t>(nitems) * hkv * sizeof(int) + 255) / 256 * 256;
+  const size_t rows = static_cast<size_t>(nitems) * hq * max_parts;
+  const size_t ml_bytes = (rows * 2 * sizeof(float) + 255) / 256 * 256;
+  const size_t need = counter_bytes + ml_bytes + rows * kD * sizeof(float);
+  if (need > RL_ATTN_NOALLOC_SCRATCH_BYTES) {
+    if (errbuf && errbuf_len > 0) {
+      std::snprintf(errbuf, static_cast<size_t>(errbuf_len),
+                    "rl_attn_decode_noalloc: %d items x %d heads x %d partitions x head size %d need %zu bytes "
+                    "of scratch, the built-in array holds %u; use rl_attn_decode with buffers of your own",
+                    nitems, hq, max_parts, kD, need, RL_ATTN_NOALLOC_SCRATCH_BYTES);
+    }
+    return RL_ATTN_NOALLOC_TOO_LARGE;
+  }
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (dev < 0 || dev >= kMaxDevices) return static_cast<int>(cudaErrorInvalidDevice);
+  if (g_noalloc_ptr[dev] == nullptr) {
+    // set-up, once per device, with that device current: the array's address on this device
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    g_noalloc_ptr[dev] = static_cast<unsigned char*>(p);
+  }
+  unsigned char* base = g_noalloc_ptr[dev];
+  int* counters = reinterpret_cast<int*>(base);
+  float* part_ml = reinterpret_cast<float*>(base + counter_bytes);
+  float* part_o = reinterpret_cast<float*>(base + counter_bytes + ml_bytes);
+  // the counters must start at zero whatever an earlier call left behind
+  e = cudaMemsetAsync(counters, 0, counter_bytes, stream);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (dtype == 0)
+    return launch_decode<float>(q, q_stride, kcache, vcache, block_table, max_blocks, items, part_o, part_ml,
+                                max_parts, counters, out, out_stride, nitems, hq, hkv, page_size, window, scale,
+                                0, stream);
+  return launch_decode<bf16>(q, q_stride, kcache, vcache, block_table, max_blocks, items, part_o, part_ml,
+                             max_parts, counters, out, out_stride, nitems, hq, hkv, page_size, window, scale, 0,
+                             stream);
+}
