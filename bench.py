@@ -232,6 +232,42 @@ def decode_run(model: str, batch: int, prompt_len: int, steps: int, warmup: int,
     return out
 
 
+def profile_step(args) -> int:
+    """For profilers: sets the decode batch up as the default run does, then brackets ONE decode
+    step with cudaProfilerStart/Stop (use ``ncu --profile-from-start off``) and prints its time."""
+    import numpy as np
+    import torch
+    from redline_b200.engine.engine import Engine
+    from redline_b200.sampling import SamplingParams
+    tmp = tempfile.mkdtemp(prefix="redline_bench_")
+    try:
+        model = write_model(tmp, args.layers)
+        batch, prompt = args.profile_batch, CONTEXT - 96
+        eng = Engine(model, dtype="bfloat16", max_num_seqs=batch, max_num_batched_tokens=2048, max_seq_len=CONTEXT,
+                     kv_cache_tokens=batch * (prompt + 128), cuda_graphs=not args.profile_eager, async_scheduling=False)
+        rng = np.random.RandomState(0)
+        for i in range(batch):
+            eng.add_request(rng.randint(0, eng.vocab_size, size=prompt).tolist(),
+                            SamplingParams(max_new_tokens=64, ignore_eos=True))
+        eng.record_steps = True
+        while not (eng.records and eng.records[-1].kind == "decode" and eng.records[-1].num_seqs == batch):
+            eng.step()
+        for _ in range(3):
+            eng.step()
+        torch.cuda.synchronize()
+        torch.cuda.profiler.start()
+        eng.step()
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+        for _ in range(3):
+            eng.step()
+        print(json.dumps({"profiled": "one decode step", "batch": batch, "context": prompt + 4,
+                          "gpu_ms_per_step": [round(r.gpu_ms, 4) for r in eng.records[-4:]]}))
+    finally:
+        shutil.rmtree(tmp, ignore_errors=True)
+    return 0
+
+
 def prefill_run(model: str, tokens: int, reps: int = 5, warmup: int = 3) -> Dict[str, Any]:
     import numpy as np
     import torch
@@ -358,10 +394,15 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration has (named in config)")
+    ap.add_argument("--profile-step", action="store_true", help="bracket one decode step with cudaProfilerStart/Stop and exit")
+    ap.add_argument("--profile-batch", type=int, default=BATCH)
+    ap.add_argument("--profile-eager", action="store_true", help="with --profile-step: no CUDA graph")
     args = ap.parse_args()
     if args.gpus != 1:
         print("redline_b200 is a single-GPU engine: bench.py runs at --gpus 1 only")
         return 2
+    if args.profile_step:
+        return profile_step(args)
     args.warmup = max(args.warmup, 3)
     args.steps = max(1, min(args.steps, 1000))
     res = run_reference(args) if args.impl == "reference" else run_ours(args)

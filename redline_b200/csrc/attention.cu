@@ -7,9 +7,11 @@
 //                    and V and leaves (max, sum, unnormalised output); a second
 //                    kernel merges the partitions with w_i = exp(m_i - m).
 //                    Restates src/cuda/kernels/attention.cu:69-209.
-//   rl_attn_prefill  32-query x 32-key tiles with an online softmax; the keys of a
-//                    tile come from the cache, so a prompt portion attends to what
-//                    earlier portions left there (attention.cu:217-359).
+//   rl_attn_prefill  tiles of query rows against tiles of keys with an online softmax; the
+//                    keys of a tile come from the cache, so a prompt portion attends to
+//                    what earlier portions left there (attention.cu:217-359).  A CUDA-core
+//                    kernel (32 x 32 tiles, any head size, both types) and a tensor-core
+//                    kernel (64 x 64 tiles, bfloat16, head size 64 or 128).
 //
 // Scores, the softmax and the P.V sums are float whatever the element type.  A
 // window w > 0 keeps only keys with pos - w < key <= pos.  The cache of a layer is
@@ -512,7 +514,7 @@ struct PrefillArgs {
   int max_blocks;
   const int32_t* tile_seq;    // [tiles] sequence index
   const int32_t* tile_tok;    // [tiles] first token of the tile (tokens of a tile are consecutive)
-  const int32_t* tile_rows;   // [tiles] rows in use (1..32)
+  const int32_t* tile_rows;   // [tiles] rows in use (1..64)
   const int32_t* positions;   // [tokens]
   T* out;
   int out_stride;
@@ -534,8 +536,11 @@ prefill_attn_kernel(const PrefillArgs<T> a) {
   float* Vs = Ks + kBK * LDQ;        // [32][D]
   float* Ps = Vs + kBK * kD;         // [32][33]
 
-  const int tile = blockIdx.x, head = blockIdx.y;
-  const int seq = a.tile_seq[tile], tok0 = a.tile_tok[tile], rows = a.tile_rows[tile];
+  // the tile list holds tiles of up to 64 rows; this kernel takes them as two halves of 32
+  const int tile = blockIdx.x >> 1, half_tile = blockIdx.x & 1, head = blockIdx.y;
+  const int seq = a.tile_seq[tile], tok0 = a.tile_tok[tile] + half_tile * kBQ;
+  const int rows = min(a.tile_rows[tile] - half_tile * kBQ, kBQ);
+  if (rows <= 0) return;
   const int kvh = head / (a.hq / a.hkv);
   const int pos0 = a.positions[tok0];
   const int32_t* bt = a.block_table + static_cast<size_t>(seq) * a.max_blocks;
@@ -626,6 +631,217 @@ prefill_attn_kernel(const PrefillArgs<T> a) {
   }
 }
 
+// ------------------------------------------------- prefill on the tensor cores
+// bfloat16, head size 64 or 128: one CTA of four warps per (64-row tile, query head), each
+// warp 16 query rows; keys in tiles of 64, brought from the paged cache into a two-stage
+// shared-memory ring with cp.async; S = Q K^T and O += P V with mma.sync.m16n8k16, online
+// softmax in float32 in the MMA's accumulator layout.  Fragments are read from shared memory
+// in 16-byte pieces with the same index permutations as the decode kernel (so no ldmatrix
+// and no transposes are needed); a 16-byte-chunk XOR swizzle keeps those reads free of
+// bank conflicts.
+#ifdef RL_HAVE_MMA_DECODE
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool pred) {
+  const uint32_t s = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+  const int bytes = pred ? 16 : 0;   // src-size 0: the 16 bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+constexpr int kMQ = 64, kMK = 64;
+
+__global__ void __launch_bounds__(128)
+prefill_attn_mma_kernel(const PrefillArgs<bf16> a) {
+  constexpr int DB = kD / 32, DG = kD / 64, CPR = kD / 8;   // 16-byte chunks per row
+  constexpr float kLog2e = 1.4426950408889634f;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* Ks = reinterpret_cast<bf16*>(smem_raw);            // [2][64][D], chunk-swizzled
+  bf16* Vs = Ks + 2 * kMK * kD;                            // [2][64][D], chunk-swizzled
+
+  // longest tiles first: a later tile of a sequence attends to more keys
+  const int tile = gridDim.x - 1 - blockIdx.x, head = blockIdx.y;
+  const int seq = a.tile_seq[tile], tok0 = a.tile_tok[tile], rows = a.tile_rows[tile];
+  const int kvh = head / (a.hq / a.hkv);
+  const int pos0 = a.positions[tok0];
+  const int32_t* bt = a.block_table + static_cast<size_t>(seq) * a.max_blocks;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int ps_shift = __ffs(a.page_size) - 1, ps_mask = a.page_size - 1;
+  const size_t head_stride = static_cast<size_t>(a.page_size) * kD;
+  const int k_end = pos0 + rows;                                                      // exclusive
+  const int lo0 = (a.window > 0 && pos0 + 1 > a.window) ? pos0 + 1 - a.window : 0;   // first key any row sees
+  const int k_begin = lo0 / kMK * kMK;
+  const int ntiles = (k_end - k_begin + kMK - 1) / kMK;
+
+  auto load_tile = [&](int it, int stage) {
+    const int k0 = k_begin + it * kMK;
+    bf16* ks = Ks + stage * kMK * kD;
+    bf16* vs = Vs + stage * kMK * kD;
+    for (int i = threadIdx.x; i < kMK * CPR; i += 128) {
+      const int key = i / CPR, c = i - key * CPR;
+      const int j = k0 + key;
+      const bool live = j < k_end && j >= lo0;
+      const size_t page = live ? bt[j >> ps_shift] : 0;
+      const size_t off = (page * a.hkv + kvh) * head_stride + static_cast<size_t>(j & ps_mask) * kD + c * 8;
+      const int ck = c ^ ((key & 1) << 2);              // K: rows g, g+1 of a read go to different halves
+      const int cv = c ^ (((key >> 1) & 3) << 1);       // V: rows t*2 of a read go to different pairs
+      cp_async16(ks + key * kD + ck * 8, a.kcache + off, live);
+      cp_async16(vs + key * kD + cv * 8, a.vcache + off, live);
+    }
+    cp_async_commit();
+  };
+
+  load_tile(0, 0);
+  // Q fragments of this warp's 16 rows (rows past the tile are zero)
+  const int r_lo = warp * 16 + g, r_hi = r_lo + 8;
+  uint4 qlo[DB], qhi[DB];
+#pragma unroll
+  for (int db = 0; db < DB; ++db) {
+    const bf16* qp = a.q + static_cast<size_t>(tok0) * a.q_stride + head * kD + db * 32 + t * 8;
+    qlo[db] = r_lo < rows ? *reinterpret_cast<const uint4*>(qp + static_cast<size_t>(r_lo) * a.q_stride) : make_uint4(0, 0, 0, 0);
+    qhi[db] = r_hi < rows ? *reinterpret_cast<const uint4*>(qp + static_cast<size_t>(r_hi) * a.q_stride) : make_uint4(0, 0, 0, 0);
+  }
+  const int pos_lo = pos0 + r_lo, pos_hi = pos0 + r_hi;
+  const int win_lo = (a.window > 0 && pos_lo + 1 > a.window) ? pos_lo + 1 - a.window : 0;
+  const int win_hi = (a.window > 0 && pos_hi + 1 > a.window) ? pos_hi + 1 - a.window : 0;
+  float o[DG][8][4];
+#pragma unroll
+  for (int dg = 0; dg < DG; ++dg)
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) o[dg][j][e] = 0.f;
+  float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
+  const float sc = a.scale * kLog2e;
+
+  for (int it = 0; it < ntiles; ++it) {
+    const int stage = it & 1;
+    if (it + 1 < ntiles) {
+      load_tile(it + 1, stage ^ 1);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const int k0 = k_begin + it * kMK;
+    const bf16* ks = Ks + stage * kMK * kD;
+    const bf16* vs = Vs + stage * kMK * kD;
+    // a warp whose rows all lie before this tile's keys has nothing to do in it
+    const bool warp_live = (k0 <= pos0 + warp * 16 + 15) && (warp * 16 < rows);
+    if (warp_live) {
+      float s[8][4];
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s[nt][e] = 0.f;
+        const int key = nt * 8 + g;
+#pragma unroll
+        for (int db = 0; db < DB; ++db) {
+          const int c = (db * 4 + t) ^ ((key & 1) << 2);
+          const uint4 kf = *reinterpret_cast<const uint4*>(ks + key * kD + c * 8);
+          mma_16816(s[nt], qlo[db].x, qhi[db].x, qlo[db].y, qhi[db].y, kf.x, kf.y);
+          mma_16816(s[nt], qlo[db].z, qhi[db].z, qlo[db].w, qhi[db].w, kf.z, kf.w);
+        }
+      }
+      float mx_lo = -INFINITY, mx_hi = -INFINITY;
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int kp = k0 + nt * 8 + t * 2 + e;
+          const bool ok_lo = kp <= pos_lo && kp >= win_lo && r_lo < rows;
+          const bool ok_hi = kp <= pos_hi && kp >= win_hi && r_hi < rows;
+          s[nt][e] = ok_lo ? s[nt][e] * sc : -INFINITY;
+          s[nt][2 + e] = ok_hi ? s[nt][2 + e] * sc : -INFINITY;
+          mx_lo = fmaxf(mx_lo, s[nt][e]);
+          mx_hi = fmaxf(mx_hi, s[nt][2 + e]);
+        }
+      mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+      mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+      mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+      mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+      const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
+      const float mu_lo = mn_lo == -INFINITY ? 0.f : mn_lo, mu_hi = mn_hi == -INFINITY ? 0.f : mn_hi;
+      const float al_lo = exp2f(m_lo - mu_lo), al_hi = exp2f(m_hi - mu_hi);   // exp2(-inf) = 0
+      float ps_lo = 0.f, ps_hi = 0.f;
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          s[nt][e] = exp2f(s[nt][e] - mu_lo);
+          s[nt][2 + e] = exp2f(s[nt][2 + e] - mu_hi);
+          ps_lo += s[nt][e];
+          ps_hi += s[nt][2 + e];
+        }
+      ps_lo += __shfl_xor_sync(0xffffffffu, ps_lo, 1);
+      ps_lo += __shfl_xor_sync(0xffffffffu, ps_lo, 2);
+      ps_hi += __shfl_xor_sync(0xffffffffu, ps_hi, 1);
+      ps_hi += __shfl_xor_sync(0xffffffffu, ps_hi, 2);
+      l_lo = l_lo * al_lo + ps_lo;
+      l_hi = l_hi * al_hi + ps_hi;
+      m_lo = mn_lo;
+      m_hi = mn_hi;
+#pragma unroll
+      for (int dg = 0; dg < DG; ++dg)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          o[dg][j][0] *= al_lo;
+          o[dg][j][1] *= al_lo;
+          o[dg][j][2] *= al_hi;
+          o[dg][j][3] *= al_hi;
+        }
+#pragma unroll
+      for (int ks16 = 0; ks16 < 4; ++ks16) {
+        const uint32_t p0 = pack_bf16(s[2 * ks16][0], s[2 * ks16][1]), p1 = pack_bf16(s[2 * ks16][2], s[2 * ks16][3]);
+        const uint32_t p2 = pack_bf16(s[2 * ks16 + 1][0], s[2 * ks16 + 1][1]);
+        const uint32_t p3 = pack_bf16(s[2 * ks16 + 1][2], s[2 * ks16 + 1][3]);
+        const int kr = ks16 * 16 + t * 2;                     // rows kr, kr+1, kr+8, kr+9 of the V tile
+        const int sw = ((kr >> 1) & 3) << 1;                  // the same for all four rows
+#pragma unroll
+        for (int dg = 0; dg < DG; ++dg) {
+          const int c = (dg * 8 + g) ^ sw;
+          const uint4 va4 = *reinterpret_cast<const uint4*>(vs + kr * kD + c * 8);
+          const uint4 vb4 = *reinterpret_cast<const uint4*>(vs + (kr + 1) * kD + c * 8);
+          const uint4 vc4 = *reinterpret_cast<const uint4*>(vs + (kr + 8) * kD + c * 8);
+          const uint4 vd4 = *reinterpret_cast<const uint4*>(vs + (kr + 9) * kD + c * 8);
+          const uint32_t va[4] = {va4.x, va4.y, va4.z, va4.w}, vb[4] = {vb4.x, vb4.y, vb4.z, vb4.w};
+          const uint32_t vc[4] = {vc4.x, vc4.y, vc4.z, vc4.w}, vd[4] = {vd4.x, vd4.y, vd4.z, vd4.w};
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const uint32_t sel = (j & 1) ? 0x7632u : 0x5410u;
+            mma_16816(o[dg][j], p0, p1, p2, p3, __byte_perm(va[j >> 1], vb[j >> 1], sel),
+                      __byte_perm(vc[j >> 1], vd[j >> 1], sel));
+          }
+        }
+      }
+    }
+    __syncthreads();   // all warps are done with this stage before it is loaded again
+  }
+  // ---- normalise and store: through shared memory so that rows go out in 16-byte pieces
+  bf16* os = Ks;       // [64][D], free now
+  const float inv_lo = l_lo > 0.f ? 1.f / l_lo : 0.f, inv_hi = l_hi > 0.f ? 1.f / l_hi : 0.f;
+#pragma unroll
+  for (int dg = 0; dg < DG; ++dg)
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int d = dg * 64 + (t * 2 + e) * 8 + j;
+        os[r_lo * kD + d] = __float2bfloat16_rn(o[dg][j][e] * inv_lo);
+        os[r_hi * kD + d] = __float2bfloat16_rn(o[dg][j][2 + e] * inv_hi);
+      }
+  __syncthreads();
+  for (int i = threadIdx.x; i < kMQ * CPR; i += 128) {
+    const int r = i / CPR, c = i - r * CPR;
+    if (r < rows)
+      *reinterpret_cast<uint4*>(a.out + static_cast<size_t>(tok0 + r) * a.out_stride + head * kD + c * 8) =
+          *reinterpret_cast<const uint4*>(os + r * kD + c * 8);
+  }
+}
+#endif  // tensor-core prefill
+
 }  // namespace rl
 
 using namespace rl;
@@ -681,7 +897,7 @@ template <typename T>
 int launch_prefill(const void* q, int q_stride, const void* kc, const void* vc, const int32_t* bt,
                    int max_blocks, const int32_t* tile_seq, const int32_t* tile_tok,
                    const int32_t* tile_rows, const int32_t* positions, void* out, int out_stride,
-                   int tiles, int hq, int hkv, int page_size, int window, float scale,
+                   int tiles, int hq, int hkv, int page_size, int window, float scale, int impl,
                    cudaStream_t stream) {
   PrefillArgs<T> a;
   a.q = static_cast<const T*>(q);
@@ -701,6 +917,23 @@ int launch_prefill(const void* q, int q_stride, const void* kc, const void* vc, 
   a.page_size = page_size;
   a.window = window;
   a.scale = scale;
+#ifdef RL_HAVE_MMA_DECODE
+  if constexpr (sizeof(T) == 2) {
+    if (impl != 1 && page_size % 16 == 0 && out_stride % 8 == 0 && q_stride % 8 == 0) {
+      const size_t msmem = static_cast<size_t>(4) * kMK * kD * sizeof(bf16);
+      static bool mattr = false;
+      if (!mattr) {
+        cudaError_t e = cudaFuncSetAttribute(prefill_attn_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             static_cast<int>(msmem));
+        if (e != cudaSuccess) return static_cast<int>(e);
+        mattr = true;
+      }
+      prefill_attn_mma_kernel<<<dim3(tiles, hq), 128, msmem, stream>>>(a);
+      return static_cast<int>(cudaGetLastError());
+    }
+  }
+#endif
+  if (impl == 2) return static_cast<int>(cudaErrorInvalidValue);
   const size_t smem = sizeof(float) * (kBQ * (kD + 1) + kBK * (kD + 1) + kBK * kD + kBQ * (kBK + 1));
   static bool attr_set = false;  // per instantiation; the attribute belongs to the device function
   if (!attr_set) {
@@ -710,7 +943,7 @@ int launch_prefill(const void* q, int q_stride, const void* kc, const void* vc, 
     if (e != cudaSuccess) return static_cast<int>(e);
     attr_set = true;
   }
-  prefill_attn_kernel<T><<<dim3(tiles, hq), kPreThreads, smem, stream>>>(a);
+  prefill_attn_kernel<T><<<dim3(tiles * 2, hq), kPreThreads, smem, stream>>>(a);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -720,7 +953,7 @@ extern "C" {
 
 int rl_attn_head_dim() { return kD; }
 int rl_attn_partition() { return kPart; }
-int rl_attn_tile_rows() { return kBQ; }
+int rl_attn_tile_rows() { return 2 * kBQ; }
 
 // dtype: 0 = float32, 1 = bfloat16 (type of q, the cache and out).
 // items: int32 [nitems, 4] = (token index of the query, sequence index, context length, 0).
@@ -747,14 +980,14 @@ int rl_attn_prefill(int dtype, const void* q, int q_stride, const void* kc, cons
                     const int32_t* bt, int max_blocks, const int32_t* tile_seq,
                     const int32_t* tile_tok, const int32_t* tile_rows, const int32_t* positions,
                     void* out, int out_stride, int tiles, int hq, int hkv, int page_size, int window,
-                    float scale, cudaStream_t stream) {
+                    float scale, int impl, cudaStream_t stream) {
   if (tiles <= 0) return 0;
   if (dtype == 0)
     return launch_prefill<float>(q, q_stride, kc, vc, bt, max_blocks, tile_seq, tile_tok, tile_rows,
-                                 positions, out, out_stride, tiles, hq, hkv, page_size, window, scale,
+                                 positions, out, out_stride, tiles, hq, hkv, page_size, window, scale, impl,
                                  stream);
   return launch_prefill<bf16>(q, q_stride, kc, vc, bt, max_blocks, tile_seq, tile_tok, tile_rows,
-                              positions, out, out_stride, tiles, hq, hkv, page_size, window, scale,
+                              positions, out, out_stride, tiles, hq, hkv, page_size, window, scale, impl,
                               stream);
 }
 

@@ -3,7 +3,7 @@ uploads it with one copy, and hands the model typed device views of it.
 
 A segment is (request cache, its next tokens, the position of the first of them,
 which of them want logits).  Segments of one token go to the decode work list,
-longer ones are cut into tiles of 32 query rows for the prefill kernel.  The
+longer ones are cut into tiles of 64 query rows for the prefill kernel.  The
 buffer holds, in this order (sizes in int32 words; T tokens, S segments, R rows,
 G cache groups, B block-table width, L tiles):
 

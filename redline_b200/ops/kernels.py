@@ -227,7 +227,7 @@ def _attn(head_dim: int) -> ctypes.CDLL:
 
 
 DECODE_PARTITION = 128
-PREFILL_TILE_ROWS = 32
+PREFILL_TILE_ROWS = 64
 
 
 def attn_decode(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcache: torch.Tensor,
@@ -262,14 +262,17 @@ def attn_prefill(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcache: t
                  block_table: torch.Tensor, tile_seq: torch.Tensor, tile_tok: torch.Tensor,
                  tile_rows: torch.Tensor, positions: torch.Tensor, out: torch.Tensor, tiles: int,
                  num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, window: int,
-                 scale: float) -> None:
+                 scale: float, impl: int = 0) -> None:
+    """Tiles of up to 64 consecutive query tokens of one sequence (tile_seq, tile_tok, tile_rows) over the
+    paged cache.  impl 0: tensor-core kernel where it applies (bfloat16, head size 64 or 128), else
+    CUDA cores; 1: CUDA cores; 2: tensor cores or an error."""
     _need_cuda(q, kcache, out)
     f = _fn(_attn(head_dim), "rl_attn_prefill",
             [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
-             c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p])
+             c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p])
     _check(f(_code(q.dtype), _ptr(q), q_stride, _ptr(kcache), _ptr(vcache), _ptr(block_table),
              block_table.shape[1], _ptr(tile_seq), _ptr(tile_tok), _ptr(tile_rows), _ptr(positions),
-             _ptr(out), out.stride(0), tiles, num_heads, num_kv_heads, page_size, window, float(scale),
+             _ptr(out), out.stride(0), tiles, num_heads, num_kv_heads, page_size, window, float(scale), impl,
              _stream()), "attn_prefill")
 
 

@@ -27,7 +27,7 @@ def test_mixed_batch_layout():
         Segment(y, [9], 20, want=(0,)),
         Segment(z, list(range(3)), 64, want=(0, 2)),
     ])
-    assert (ctx.T, ctx.S, ctx.R, ctx.num_decode, ctx.num_tiles) == (44, 3, 4, 1, 3)
+    assert (ctx.T, ctx.S, ctx.R, ctx.num_decode, ctx.num_tiles) == (44, 3, 4, 1, 2)
     assert ctx.token_ids.tolist() == list(range(100, 140)) + [9] + [0, 1, 2]
     assert ctx.token_src.tolist() == [-1] * 44
     assert ctx.positions.tolist() == list(range(40)) + [20] + [64, 65, 66]
@@ -40,8 +40,8 @@ def test_mixed_batch_layout():
     assert slots[:40] == [16 + i for i in range(40)]          # pages 1, 2, 3 are consecutive
     assert slots[40] == 5 * 16 + 4 and slots[41:] == [10 * 16, 10 * 16 + 1, 10 * 16 + 2]
     assert ctx.decode_info.tolist()[0] == [40, 1, 21, 0] and ctx.decode_parts == 1
-    assert ctx.tile_seq.tolist() == [0, 0, 2] and ctx.tile_tok.tolist() == [0, 32, 41]
-    assert ctx.tile_rows.tolist() == [32, 8, 3]
+    assert ctx.tile_seq.tolist() == [0, 2] and ctx.tile_tok.tolist() == [0, 41]
+    assert ctx.tile_rows.tolist() == [40, 3]
     assert ctx.logit_rows.tolist() == [39, 40, 41, 43]
     assert ctx.sample_pos.tolist() == [40, 21, 65, 67]        # position of the token that would be drawn
     assert ctx.temperature.tolist() == pytest.approx([0.8, 0, 0, 0]) and ctx.top_k.tolist() == [5, 0, 0, 0]

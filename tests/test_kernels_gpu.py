@@ -150,7 +150,7 @@ def reference_attention(seqs, Hq, Hkv, D, cos, sin, scale, window, dtype):
 
 
 def run_attention(dtype, Hq, Hkv, D, lens_past, lens_new, page_size=16, window=0, seed=0, sharp=None,
-                  poison=True, decode_impl=0):
+                  poison=True, decode_impl=0, prefill_impl=0):
     """Writes the past through rope_kv_write, then runs the new tokens (decode kernel for
     single tokens, prefill kernel for portions) and compares with the reference."""
     from redline_b200.config.model_config import RopeScaling
@@ -185,8 +185,8 @@ def run_attention(dtype, Hq, Hkv, D, lens_past, lens_new, page_size=16, window=0
             if n == 1:
                 dec.append(t)
             else:
-                for r0 in range(0, n, 32):
-                    tiles.append((s, t + r0, min(32, n - r0)))
+                for r0 in range(0, n, kernels.PREFILL_TILE_ROWS):
+                    tiles.append((s, t + r0, min(kernels.PREFILL_TILE_ROWS, n - r0)))
             t += n
         qkv = torch.cat(toks).to(DEV).contiguous()
         i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)  # noqa: E731
@@ -205,7 +205,7 @@ def run_attention(dtype, Hq, Hkv, D, lens_past, lens_new, page_size=16, window=0
         if tiles:
             kernels.attn_prefill(qkv, qkv.shape[1], kc, vc, bt, i32([x[0] for x in tiles]),
                                  i32([x[1] for x in tiles]), i32([x[2] for x in tiles]), pos_d, out, len(tiles),
-                                 Hq, Hkv, D, page_size, window, scale)
+                                 Hq, Hkv, D, page_size, window, scale, prefill_impl)
         return out
 
     if any(lens_past):
@@ -225,8 +225,23 @@ ATTN_SHAPES = [  # Hq, Hkv, D
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("Hq,Hkv,D", ATTN_SHAPES)
 def test_attention_prefill_whole_and_with_a_cached_past(dtype, Hq, Hkv, D):
-    run_attention(dtype, Hq, Hkv, D, [0, 0, 0], [1 + 4, 33, 129], seed=1)
-    run_attention(dtype, Hq, Hkv, D, [17, 64, 5], [40, 2, 70], seed=2)
+    # impl 1: the CUDA-core kernel; 0: the tensor-core kernel where it applies (bfloat16, D 64 / 128)
+    for impl in (0, 1):
+        run_attention(dtype, Hq, Hkv, D, [0, 0, 0], [1 + 4, 33, 129], seed=1, prefill_impl=impl)
+        run_attention(dtype, Hq, Hkv, D, [17, 64, 5], [40, 2, 70], seed=2, prefill_impl=impl)
+
+
+@pytest.mark.parametrize("Hq,Hkv,D", [(4, 2, 64), (32, 8, 64), (3, 1, 128), (5, 5, 64), (24, 8, 128)])
+@pytest.mark.parametrize("page_size", [16, 32, 64])
+def test_attention_prefill_tensor_core_kernel(Hq, Hkv, D, page_size):
+    """impl 2 insists on the tensor-core kernel: portions that start and end anywhere relative to its
+    64-row and 64-key tiles, pasts of every alignment, every page size, and windows."""
+    run_attention("bfloat16", Hq, Hkv, D, [0, 0, 0, 0], [2, 63, 64, 65], page_size=page_size, seed=21, prefill_impl=2)
+    run_attention("bfloat16", Hq, Hkv, D, [0, 1, 63, 64, 200], [300, 129, 2, 70, 131], page_size=page_size, seed=22,
+                  prefill_impl=2)
+    for window in (1, 20, 64, 100, 300):
+        run_attention("bfloat16", Hq, Hkv, D, [0, 90, 290], [150, 35, 66], page_size=page_size, window=window, seed=23,
+                      prefill_impl=2)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -286,6 +301,7 @@ def test_a_far_key_is_found_among_hundreds(dtype):
         run_attention(dtype, Hq, Hkv, D, [total - 1], [1], seed=9, sharp=sharp)     # decode kernel
         run_attention(dtype, Hq, Hkv, D, [total - 1], [1], seed=9, sharp=sharp, decode_impl=1)
         run_attention(dtype, Hq, Hkv, D, [total - 40], [40], seed=9, sharp=sharp)   # prefill kernel
+        run_attention(dtype, Hq, Hkv, D, [total - 40], [40], seed=9, sharp=sharp, prefill_impl=1)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
