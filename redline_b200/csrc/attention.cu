@@ -56,6 +56,8 @@ struct DecodeArgs {
 template <typename T>
 __global__ void __launch_bounds__(kDecThreads)
 decode_attn_kernel(const DecodeArgs<T> a) {
+  pdl_launch();
+  pdl_wait();
   constexpr int VEC = Vec16<T>::N;
   constexpr int CH = kD / VEC;                     // 16-byte chunks per key
   constexpr int CPL = (CH + kLPK - 1) / kLPK;      // chunks per lane
@@ -210,6 +212,8 @@ template <typename T>
 __global__ void decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                     const int4* __restrict__ items, T* __restrict__ out,
                                     int out_stride, int hq, int max_parts, int window) {
+  pdl_launch();
+  pdl_wait();
   const int item = blockIdx.x, head = blockIdx.y;
   const int4 info = items[item];
   const int tok = info.x, ctx = info.z;
@@ -258,6 +262,8 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 
 __global__ void __launch_bounds__(128)
 decode_attn_mma_kernel(const DecodeArgs<bf16> a) {
+  pdl_launch();
+  pdl_wait();
   constexpr int DB = kD / 32;   // 32-wide blocks of d for Q.K^T
   constexpr int DG = kD / 64;   // 64-wide groups of d for P.V
   constexpr float kLog2e = 1.4426950408889634f, kLn2 = 0.6931471805599453f;
@@ -527,6 +533,8 @@ struct PrefillArgs {
 template <typename T>
 __global__ void __launch_bounds__(kPreThreads)
 prefill_attn_kernel(const PrefillArgs<T> a) {
+  pdl_launch();
+  pdl_wait();
   constexpr int VEC = Vec16<T>::N;
   constexpr int CH = kD / VEC;
   constexpr int LDQ = kD + 1;
@@ -654,6 +662,8 @@ constexpr int kMQ = 64, kMK = 64;
 
 __global__ void __launch_bounds__(128)
 prefill_attn_mma_kernel(const PrefillArgs<bf16> a) {
+  pdl_launch();
+  pdl_wait();
   constexpr int DB = kD / 32, DG = kD / 64, CPR = kD / 8;   // 16-byte chunks per row
   constexpr float kLog2e = 1.4426950408889634f;
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -877,18 +887,18 @@ int launch_decode(const void* q, int q_stride, const void* kc, const void* vc, c
   if constexpr (sizeof(T) == 2) {
     // tensor-core kernel: groups of up to 16 heads, pages that hold whole 16-key steps
     if (impl != 1 && hq / hkv <= 16 && page_size % 16 == 0 && counters != nullptr && max_parts <= kMaxMergeParts) {
-      decode_attn_mma_kernel<<<grid, 128, 0, stream>>>(a);
+      launch_kernel(decode_attn_mma_kernel, dim3(grid), dim3(128), 0, stream, a);
       return static_cast<int>(cudaGetLastError());
     }
   }
 #endif
   if (impl == 2) return static_cast<int>(cudaErrorInvalidValue);
-  decode_attn_kernel<T><<<grid, kDecThreads, 0, stream>>>(a);
+  launch_kernel(decode_attn_kernel<T>, dim3(grid), dim3(kDecThreads), 0, stream, a);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return static_cast<int>(e);
   int th = 32;
   while (th < kD) th <<= 1;
-  decode_merge_kernel<T><<<dim3(nitems, hq), th, 0, stream>>>(
+  launch_kernel(decode_merge_kernel<T>, dim3(dim3(nitems, hq)), dim3(th), 0, stream, 
       part_o, part_ml, a.items, static_cast<T*>(out), out_stride, hq, max_parts, window);
   return static_cast<int>(cudaGetLastError());
 }
@@ -928,7 +938,7 @@ int launch_prefill(const void* q, int q_stride, const void* kc, const void* vc, 
         if (e != cudaSuccess) return static_cast<int>(e);
         mattr = true;
       }
-      prefill_attn_mma_kernel<<<dim3(tiles, hq), 128, msmem, stream>>>(a);
+      launch_kernel(prefill_attn_mma_kernel, dim3(dim3(tiles, hq)), dim3(128), msmem, stream, a);
       return static_cast<int>(cudaGetLastError());
     }
   }
@@ -943,7 +953,7 @@ int launch_prefill(const void* q, int q_stride, const void* kc, const void* vc, 
     if (e != cudaSuccess) return static_cast<int>(e);
     attr_set = true;
   }
-  prefill_attn_kernel<T><<<dim3(tiles * 2, hq), kPreThreads, smem, stream>>>(a);
+  launch_kernel(prefill_attn_kernel<T>, dim3(dim3(tiles * 2, hq)), dim3(kPreThreads), smem, stream, a);
   return static_cast<int>(cudaGetLastError());
 }
 

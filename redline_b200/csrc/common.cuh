@@ -91,6 +91,48 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
   return r;
 }
 
+// ---- programmatic dependent launch ----------------------------------------------------
+// Kernels of a step form a chain in one stream.  Launched with the programmatic
+// stream-serialization attribute, a kernel may begin (be scheduled, run its prologue, ask
+// for weights that no earlier kernel writes) while its predecessor is still draining; it
+// calls pdl_wait() before it touches anything an earlier kernel of the chain wrote, which
+// returns once the predecessor has completed and its writes are visible.  pdl_launch()
+// tells the scheduler that the successor may be brought in.  Without the attribute both
+// are no-ops.  REDLINE_PDL=0 in the environment turns the attribute off.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+}  // namespace rl
+
+#include <cstdlib>
+#include <utility>
+
+namespace rl {
+
+inline bool pdl_enabled() {
+  static const bool on = [] {
+    const char* e = std::getenv("REDLINE_PDL");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                 cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+
 }  // namespace rl
 
 #define RL_LAUNCH_END() return static_cast<int>(cudaGetLastError())

@@ -17,6 +17,8 @@ namespace rl {
 // taken from that step's output (reference: elementwise.cu:12-16).
 __global__ void resolve_ids_kernel(int32_t* __restrict__ ids, const int32_t* __restrict__ src,
                                    const int32_t* __restrict__ sampled, int n) {
+  pdl_launch();
+  pdl_wait();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n && src[i] >= 0) ids[i] = sampled[src[i]];
 }
@@ -27,6 +29,8 @@ __global__ void resolve_ids_kernel(int32_t* __restrict__ ids, const int32_t* __r
 template <typename TW>
 __global__ void embedding_kernel(const int32_t* __restrict__ ids, const TW* __restrict__ table,
                                  float* __restrict__ out, int hidden, int vocab, int* status) {
+  pdl_launch();
+  pdl_wait();
   const int t = blockIdx.x;
   const int id = ids[t];
   float* o = out + static_cast<size_t>(t) * hidden;
@@ -49,6 +53,8 @@ template <typename TA, typename TD, typename TW>
 __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __restrict__ delta,
                                    const TW* __restrict__ weight, TA* __restrict__ out,
                                    const int32_t* __restrict__ rows_idx, int hidden, float eps) {
+  pdl_launch();
+  pdl_wait();
   __shared__ float scratch[32];
   const int r = blockIdx.x;
   const int src = rows_idx ? rows_idx[r] : r;
@@ -76,6 +82,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __res
 template <typename TD>
 __global__ void add_residual_kernel(float* __restrict__ residual, const TD* __restrict__ delta,
                                     size_t n) {
+  pdl_launch();
+  pdl_wait();
   const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i < n) residual[i] += to_float(delta[i]);
 }
@@ -85,6 +93,8 @@ __global__ void add_residual_kernel(float* __restrict__ residual, const TD* __re
 // (elementwise.cu:66-82), computed in float and rounded once.
 template <typename TA>
 __global__ void swiglu_kernel(const TA* __restrict__ gu, TA* __restrict__ out, int inter) {
+  pdl_launch();
+  pdl_wait();
   const int t = blockIdx.y;
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= inter) return;
@@ -97,6 +107,8 @@ __global__ void swiglu_kernel(const TA* __restrict__ gu, TA* __restrict__ out, i
 // ------------------------------------------------------------- add bias
 template <typename TA, typename TW>
 __global__ void add_bias_kernel(TA* __restrict__ x, const TW* __restrict__ bias, int n, size_t total) {
+  pdl_launch();
+  pdl_wait();
   const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i < total) x[i] = from_float<TA>(to_float(x[i]) + to_float(bias[i % n]));
 }
@@ -114,6 +126,8 @@ __global__ void rope_kv_write_kernel(TA* __restrict__ qkv, const int32_t* __rest
                                      const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                                      TA* __restrict__ kcache, TA* __restrict__ vcache, int hq, int hkv,
                                      int d, int page_size, int max_pos, int* status) {
+  pdl_launch();
+  pdl_wait();
   const int t = blockIdx.x;
   const int half = d >> 1;
   const int pos = positions[t];
@@ -174,7 +188,7 @@ extern "C" {
 
 int rl_resolve_ids(int32_t* ids, const int32_t* src, const int32_t* sampled, int n, cudaStream_t stream) {
   if (n <= 0) return 0;
-  resolve_ids_kernel<<<(n + 255) / 256, 256, 0, stream>>>(ids, src, sampled, n);
+  launch_kernel(resolve_ids_kernel, dim3((n + 255) / 256), dim3(256), 0, stream, ids, src, sampled, n);
   RL_LAUNCH_END();
 }
 
@@ -183,10 +197,10 @@ int rl_embedding(const int32_t* ids, const void* table, int table_dtype, float* 
   if (tokens <= 0) return 0;
   const int th = row_threads(hidden);
   if (table_dtype == RL_F32) {
-    embedding_kernel<float><<<tokens, th, 0, stream>>>(ids, static_cast<const float*>(table), out,
+    launch_kernel(embedding_kernel<float>, dim3(tokens), dim3(th), 0, stream, ids, static_cast<const float*>(table), out,
                                                        hidden, vocab, status);
   } else {
-    embedding_kernel<bf16><<<tokens, th, 0, stream>>>(ids, static_cast<const bf16*>(table), out,
+    launch_kernel(embedding_kernel<bf16>, dim3(tokens), dim3(th), 0, stream, ids, static_cast<const bf16*>(table), out,
                                                       hidden, vocab, status);
   }
   RL_LAUNCH_END();
@@ -199,7 +213,7 @@ int rl_add_rmsnorm(float* residual, const void* delta, const void* weight, int w
   if (rows <= 0) return 0;
   const int th = row_threads(hidden);
 #define RL_NORM_CASE(TA, TW)                                                                 \
-  add_rmsnorm_kernel<TA, TA, TW><<<rows, th, 0, stream>>>(                                   \
+  launch_kernel(add_rmsnorm_kernel<TA, TA, TW>, dim3(rows), dim3(th), 0, stream,                                    \
       residual, static_cast<const TA*>(delta), static_cast<const TW*>(weight),               \
       static_cast<TA*>(out), rows_idx, hidden, eps)
   if (act_dtype == RL_F32 && w_dtype == RL_F32) RL_NORM_CASE(float, float);
@@ -216,9 +230,9 @@ int rl_add_residual(float* residual, const void* delta, int act_dtype, long long
   const int th = 256;
   const unsigned blocks = static_cast<unsigned>((n + th - 1) / th);
   if (act_dtype == RL_F32)
-    add_residual_kernel<float><<<blocks, th, 0, stream>>>(residual, static_cast<const float*>(delta), n);
+    launch_kernel(add_residual_kernel<float>, dim3(blocks), dim3(th), 0, stream, residual, static_cast<const float*>(delta), n);
   else
-    add_residual_kernel<bf16><<<blocks, th, 0, stream>>>(residual, static_cast<const bf16*>(delta), n);
+    launch_kernel(add_residual_kernel<bf16>, dim3(blocks), dim3(th), 0, stream, residual, static_cast<const bf16*>(delta), n);
   RL_LAUNCH_END();
 }
 
@@ -227,9 +241,9 @@ int rl_swiglu(const void* gu, void* out, int act_dtype, int tokens, int inter, c
   const int th = 256;
   dim3 grid((inter + th - 1) / th, tokens);
   if (act_dtype == RL_F32)
-    swiglu_kernel<float><<<grid, th, 0, stream>>>(static_cast<const float*>(gu), static_cast<float*>(out), inter);
+    launch_kernel(swiglu_kernel<float>, dim3(grid), dim3(th), 0, stream, static_cast<const float*>(gu), static_cast<float*>(out), inter);
   else
-    swiglu_kernel<bf16><<<grid, th, 0, stream>>>(static_cast<const bf16*>(gu), static_cast<bf16*>(out), inter);
+    launch_kernel(swiglu_kernel<bf16>, dim3(grid), dim3(th), 0, stream, static_cast<const bf16*>(gu), static_cast<bf16*>(out), inter);
   RL_LAUNCH_END();
 }
 
@@ -240,7 +254,7 @@ int rl_add_bias(void* x, int act_dtype, const void* bias, int b_dtype, int rows,
   const int th = 256;
   const unsigned blocks = static_cast<unsigned>((total + th - 1) / th);
 #define RL_BIAS_CASE(TA, TW)                                                               \
-  add_bias_kernel<TA, TW><<<blocks, th, 0, stream>>>(static_cast<TA*>(x),                  \
+  launch_kernel(add_bias_kernel<TA, TW>, dim3(blocks), dim3(th), 0, stream, static_cast<TA*>(x),                  \
                                                      static_cast<const TW*>(bias), n, total)
   if (act_dtype == RL_F32 && b_dtype == RL_F32) RL_BIAS_CASE(float, float);
   else if (act_dtype == RL_F32) RL_BIAS_CASE(float, bf16);
@@ -257,11 +271,11 @@ int rl_rope_kv_write(void* qkv, int act_dtype, const int32_t* positions, const i
   if (tokens <= 0) return 0;
   const int th = 256;
   if (act_dtype == RL_F32)
-    rope_kv_write_kernel<float><<<tokens, th, 0, stream>>>(
+    launch_kernel(rope_kv_write_kernel<float>, dim3(tokens), dim3(th), 0, stream, 
         static_cast<float*>(qkv), positions, slots, cos_t, sin_t, static_cast<float*>(kcache),
         static_cast<float*>(vcache), hq, hkv, d, page_size, max_pos, status);
   else
-    rope_kv_write_kernel<bf16><<<tokens, th, 0, stream>>>(
+    launch_kernel(rope_kv_write_kernel<bf16>, dim3(tokens), dim3(th), 0, stream, 
         static_cast<bf16*>(qkv), positions, slots, cos_t, sin_t, static_cast<bf16*>(kcache),
         static_cast<bf16*>(vcache), hq, hkv, d, page_size, max_pos, status);
   RL_LAUNCH_END();

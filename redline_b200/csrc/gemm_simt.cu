@@ -16,6 +16,8 @@ template <typename TA, typename TW, typename TC>
 __global__ void __launch_bounds__(256)
 gemm_tn_simt_kernel(const TA* __restrict__ x, const TW* __restrict__ w, TC* __restrict__ y, int M,
                     int N, int K, int ldx, int ldy) {
+  pdl_launch();
+  pdl_wait();
   __shared__ float xs[kTK][kTM + 4];
   __shared__ float ws[kTK][kTN + 4];
   const int m0 = blockIdx.y * kTM, n0 = blockIdx.x * kTN;
@@ -66,7 +68,7 @@ template <typename TA, typename TW, typename TC>
 int launch(const void* x, const void* w, void* y, int M, int N, int K, int ldx, int ldy,
            cudaStream_t stream) {
   dim3 grid((N + kTN - 1) / kTN, (M + kTM - 1) / kTM);
-  gemm_tn_simt_kernel<TA, TW, TC><<<grid, 256, 0, stream>>>(
+  launch_kernel(gemm_tn_simt_kernel<TA, TW, TC>, dim3(grid), dim3(256), 0, stream, 
       static_cast<const TA*>(x), static_cast<const TW*>(w), static_cast<TC*>(y), M, N, K, ldx, ldy);
   return static_cast<int>(cudaGetLastError());
 }

@@ -19,13 +19,9 @@
 // mma.sync.m16n8k16 is used rather than tcgen05: with at most 16 rows the product is
 // bound by the weight stream, a 128-row UMMA tile would be 1/16 full, and mma.sync can
 // take its weight fragments from registers without a shared-memory round trip.
-#include <cuda_bf16.h>
-#include <cuda_runtime.h>
-#include <stdint.h>
+#include "common.cuh"
 
 namespace rl {
-
-typedef __nv_bfloat16 bf16;
 
 enum Epilogue { kStoreBf16 = 0, kStoreF32 = 1, kAddResidual = 2, kSwiglu = 3 };
 
@@ -78,14 +74,18 @@ __device__ __forceinline__ void load_wfrag(WFrag& f, const bf16* w_lo, const bf1
 }
 
 // MT: token rows padded to 8 or 16; WARPS: warps per CTA; EPI: epilogue; NORM: fused norm.
-template <int MT, int WARPS, int EPI, bool NORM>
+// MT: token rows padded to 8 or 16; WARPS: warps per CTA; KW: warps that split the K of one
+// 16-row weight stream; EPI: epilogue; NORM: fused norm.  The CTA's WARPS / KW groups of warps
+// take different streams at the same time: 16-row tiles next to each other and, for the gated
+// product, the gate rows and the up rows of a tile.
+template <int MT, int WARPS, int KW, int EPI, bool NORM>
 __global__ void __launch_bounds__(WARPS * 32)
 gemm_skinny_kernel(const SkinnyArgs a, int kc) {
   constexpr bool GATED = (EPI == kSwiglu);
-  constexpr int NG = MT / 8;           // 8-token groups
-  // the gated product has two weight streams (gate rows, up rows): the first half of the
-  // warps takes one, the second half the other, and each half splits K among its KW warps
-  constexpr int KW = GATED ? WARPS / 2 : WARPS;
+  constexpr int NG = MT / 8;                    // 8-token groups
+  constexpr int STREAMS = GATED ? 2 : 1;        // weight streams per tile (gate rows, up rows)
+  constexpr int TPC = WARPS / KW / STREAMS;     // tiles a CTA works on at the same time
+  static_assert(TPC >= 1 && TPC * KW * STREAMS == WARPS, "bad warp split");
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int lds = kc + 32;             // row stride of the staged activations (elements): 64 B off a
                                        // multiple of 128 B, so the 16-byte fragment reads do not collide
@@ -96,7 +96,8 @@ gemm_skinny_kernel(const SkinnyArgs a, int kc) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
   const int M = a.M, K = a.K;
-  const int kw = warp % KW, stream = warp / KW;
+  const int kw = warp % KW, grp = warp / KW;
+  const int stream = grp % STREAMS, tile_in_cta = grp / STREAMS;
   const int nsb = (K + kSB - 1) / kSB;       // super-blocks in K; warp kw takes kw, kw + KW, ...
 
   // The first weights are asked for before anything else: they do not depend on the
@@ -108,9 +109,11 @@ gemm_skinny_kernel(const SkinnyArgs a, int kc) {
     w_lo = a.w + static_cast<size_t>(stream * a.N + r_lo) * K;
     w_hi = a.w + static_cast<size_t>(stream * a.N + r_hi) * K;
   };
-  const int tile0 = blockIdx.x * a.row_tiles;
+  const int tile0 = blockIdx.x * a.row_tiles * TPC + tile_in_cta;   // then tile0 + TPC, ... (row_tiles rounds)
   set_rows(tile0 * 16);
+  pdl_launch();
   load_wfrag(cur, w_lo, w_hi, kw * kSB + t * 8, K);
+  pdl_wait();   // everything below reads what earlier kernels of the step wrote
 
   if (NORM) {
     for (int m = warp; m < MT; m += WARPS) {
@@ -130,9 +133,10 @@ gemm_skinny_kernel(const SkinnyArgs a, int kc) {
   }
 
   for (int rt = 0; rt < a.row_tiles; ++rt) {
-    const int n0 = (tile0 + rt) * 16;
-    if (n0 >= a.N) break;
-    const bool more_tiles = (rt + 1 < a.row_tiles) && (n0 + 16 < a.N);
+    const int n0 = (tile0 + rt * TPC) * 16;                           // this warp's tile (may lie past N)
+    const int cta_n0 = (blockIdx.x * a.row_tiles + rt) * TPC * 16;   // first feature of the CTA's round
+    if (cta_n0 >= a.N) break;
+    const bool more_tiles = (rt + 1 < a.row_tiles) && (cta_n0 + TPC * 16 < a.N);
     float acc[NG][4];
 #pragma unroll
     for (int j = 0; j < NG; ++j)
@@ -188,8 +192,8 @@ gemm_skinny_kernel(const SkinnyArgs a, int kc) {
         const int sbn = sb + KW;
         if (sbn < nsb) {
           load_wfrag(nxt, w_lo, w_hi, sbn * kSB + t * 8, K);
-        } else if (more_tiles) {         // this tile's stream is done: start the next tile's
-          set_rows(n0 + 16);
+        } else if (more_tiles) {         // this tile's stream is done: start the next round's
+          set_rows(n0 + TPC * 16);
           load_wfrag(nxt, w_lo, w_hi, kw * kSB + t * 8, K);
         }
         const int kb = sb * kSB - k0;    // within the staged chunk
@@ -208,7 +212,7 @@ gemm_skinny_kernel(const SkinnyArgs a, int kc) {
     // a warp that had no super-block in this tile (K shorter than WARPS super-blocks) still holds the
     // tile's first fragment in `cur`: fetch the next tile's instead
     if (kw >= nsb && more_tiles) {
-      set_rows(n0 + 16);
+      set_rows(n0 + TPC * 16);
       load_wfrag(cur, w_lo, w_hi, kw * kSB + t * 8, K);
     }
     // ---- partial sums of the warps meet in shared memory: red[warp][16][MT]
@@ -223,16 +227,18 @@ gemm_skinny_kernel(const SkinnyArgs a, int kc) {
       r[(g + 8) * MT + col + 1] = acc[j][3];
     }
     __syncthreads();
-    for (int i = tid; i < 16 * MT; i += WARPS * 32) {
+    for (int i = tid; i < TPC * 16 * MT; i += WARPS * 32) {
       // consecutive threads take consecutive features of one token: coalesced stores
-      const int m = i / 16, f = i - m * 16;
-      const int n = n0 + f;
+      const int m = i / (TPC * 16), ft = i - m * (TPC * 16);
+      const int tl = ft >> 4, f = ft & 15;             // tile of the CTA's round, feature in the tile
+      const int n = cta_n0 + ft;
       if (m >= M || n >= a.N) continue;
+      const int w0 = (tl * STREAMS) * KW;              // first warp of the tile's (first) stream
       float v = 0.f, u = 0.f;
 #pragma unroll
       for (int w = 0; w < KW; ++w) {
-        v += red[(w * 16 + f) * MT + m];
-        if (GATED) u += red[((KW + w) * 16 + f) * MT + m];
+        v += red[((w0 + w) * 16 + f) * MT + m];
+        if (GATED) u += red[((w0 + KW + w) * 16 + f) * MT + m];
       }
       const size_t o = static_cast<size_t>(m) * a.ldy + n;
       if (EPI == kStoreBf16) {
@@ -250,12 +256,23 @@ gemm_skinny_kernel(const SkinnyArgs a, int kc) {
   }
 }
 
-template <int MT, int WARPS, int EPI, bool NORM>
-int launch_one(const SkinnyArgs& a, int ctas, cudaStream_t stream) {
-  // K is staged in equal chunks that are multiples of 64 * WARPS, so that warp w always
-  // takes the global 128-wide super-blocks w, w + WARPS, ...: the order of a row's sums does not
+template <int MT, int WARPS, int KW, int EPI, bool NORM>
+int launch_one(const SkinnyArgs& a0, int sm_count, cudaStream_t stream) {
+  constexpr int STREAMS = (EPI == kSwiglu) ? 2 : 1;
+  constexpr int TPC = WARPS / KW / STREAMS;
+  SkinnyArgs a = a0;
+  const int tiles = (a.N + 15) / 16;
+  const int rounds = (tiles + TPC - 1) / TPC;       // CTA-rounds of TPC tiles
+  // at most about two CTAs per SM, all resident at once: a second, nearly empty wave would cost
+  // as much as the first
+  int rt = (rounds + 2 * sm_count - 1) / (2 * sm_count);
+  if (rt > 16) rt = 16;
+  a.row_tiles = rt;
+  const int ctas = (rounds + rt - 1) / rt;
+  // K is staged in equal chunks that are multiples of 128 * KW, so that warp kw of a stream always
+  // takes the global 128-wide super-blocks kw, kw + KW, ...: the order of a row's sums does not
   // depend on the chunking, hence not on how many rows the batch has.
-  constexpr int kUnit = kSB * (EPI == kSwiglu ? WARPS / 2 : WARPS);
+  constexpr int kUnit = kSB * KW;
   const int kunits = (a.K + kUnit - 1) / kUnit;
   int max_units = (98304 / (MT * 2) - 32) / kUnit;
   if (max_units < 1) max_units = 1;
@@ -266,19 +283,49 @@ int launch_one(const SkinnyArgs& a, int ctas, cudaStream_t stream) {
   const size_t smem = xbytes > rbytes ? xbytes : rbytes;
   static size_t set_for = 0;
   if (smem > set_for) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_skinny_kernel<MT, WARPS, EPI, NORM>,
+    cudaError_t e = cudaFuncSetAttribute(gemm_skinny_kernel<MT, WARPS, KW, EPI, NORM>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (e != cudaSuccess) return static_cast<int>(e);
     set_for = smem;
   }
-  gemm_skinny_kernel<MT, WARPS, EPI, NORM><<<ctas, WARPS * 32, smem, stream>>>(a, kc);
+  launch_kernel(gemm_skinny_kernel<MT, WARPS, KW, EPI, NORM>, dim3(ctas), dim3(WARPS * 32), smem, stream, a, kc);
   return static_cast<int>(cudaGetLastError());
 }
 
+// How many warps split the K of one stream: the largest power of two that keeps streams x warps
+// at about 16 warps per SM (measured on a B200 over the projection shapes of 1B- to 8B-size
+// models: the best split is the one with 1,500 to 2,100 warps in all), at most one warp per
+// 128-wide super-block.  Depends on the weight's shape and on the GPU only, never on the
+// number of rows.
+inline int choose_kw(int N, int K, int streams, int sm_count) {
+  const int tiles = (N + 15) / 16, nsb = (K + kSB - 1) / kSB;
+  int kw = 1;
+  while (kw < 16 && tiles * streams * (kw * 2) <= sm_count * 16 && kw * 2 <= nsb) kw *= 2;
+  return kw;
+}
+
+template <int MT, int EPI, bool NORM>
+int launch_kw(const SkinnyArgs& a, int sm_count, cudaStream_t stream) {
+  constexpr int STREAMS = (EPI == kSwiglu) ? 2 : 1;
+  int kw = choose_kw(a.N, a.K, STREAMS, sm_count);
+  if (const char* e = std::getenv("REDLINE_SKINNY_KW")) kw = std::atoi(e);   // for tuning runs
+  if (STREAMS == 2 && kw > 4) kw = 4;      // 8 warps hold both streams of a tile
+  switch (kw) {
+    case 1: return launch_one<MT, 8, 1, EPI, NORM>(a, sm_count, stream);
+    case 2: return launch_one<MT, 8, 2, EPI, NORM>(a, sm_count, stream);
+    case 4: return launch_one<MT, 8, 4, EPI, NORM>(a, sm_count, stream);
+    case 8:
+      if constexpr (STREAMS == 1) return launch_one<MT, 8, 8, EPI, NORM>(a, sm_count, stream);
+    default:
+      if constexpr (STREAMS == 1) return launch_one<MT, 16, 16, EPI, NORM>(a, sm_count, stream);
+  }
+  return static_cast<int>(cudaErrorInvalidValue);
+}
+
 template <int EPI, bool NORM>
-int launch_mt(const SkinnyArgs& a, int ctas, bool wide, cudaStream_t stream) {
-  if (a.M <= 8) return wide ? launch_one<8, 16, EPI, NORM>(a, ctas, stream) : launch_one<8, 8, EPI, NORM>(a, ctas, stream);
-  return wide ? launch_one<16, 16, EPI, NORM>(a, ctas, stream) : launch_one<16, 8, EPI, NORM>(a, ctas, stream);
+int launch_mt(const SkinnyArgs& a, int sm_count, cudaStream_t stream) {
+  if (a.M <= 8) return launch_kw<8, EPI, NORM>(a, sm_count, stream);
+  return launch_kw<16, EPI, NORM>(a, sm_count, stream);
 }
 
 }  // namespace rl
@@ -312,31 +359,19 @@ int rl_gemm_skinny(const void* w, const void* x, int ldx, const float* residual,
   a.K = K;
   a.ldx = ldx;
   a.ldy = ldy;
-  const int tiles = (N + 15) / 16;
-  // no more tiles than SMs: one CTA of 16 warps per tile (one CTA fits an SM); more: CTAs of
-  // 8 warps (two fit an SM), several tiles per CTA when there are many so that the prologue
-  // (staging, norm) is shared
-  const bool wide = tiles <= sm_count;
-  int rt = 1;
-  if (!wide) {
-    rt = tiles / (4 * sm_count);
-    if (rt < 1) rt = 1;
-    if (rt > 8) rt = 8;
-  }
-  a.row_tiles = rt;
-  const int ctas = (tiles + rt - 1) / rt;
+  a.row_tiles = 1;
   if (norm) {
     switch (epilogue) {
-      case kStoreBf16: return launch_mt<kStoreBf16, true>(a, ctas, wide, stream);
-      case kStoreF32: return launch_mt<kStoreF32, true>(a, ctas, wide, stream);
-      case kSwiglu: return launch_mt<kSwiglu, true>(a, ctas, wide, stream);
+      case kStoreBf16: return launch_mt<kStoreBf16, true>(a, sm_count, stream);
+      case kStoreF32: return launch_mt<kStoreF32, true>(a, sm_count, stream);
+      case kSwiglu: return launch_mt<kSwiglu, true>(a, sm_count, stream);
     }
   } else {
     switch (epilogue) {
-      case kStoreBf16: return launch_mt<kStoreBf16, false>(a, ctas, wide, stream);
-      case kStoreF32: return launch_mt<kStoreF32, false>(a, ctas, wide, stream);
-      case kAddResidual: return launch_mt<kAddResidual, false>(a, ctas, wide, stream);
-      case kSwiglu: return launch_mt<kSwiglu, false>(a, ctas, wide, stream);
+      case kStoreBf16: return launch_mt<kStoreBf16, false>(a, sm_count, stream);
+      case kStoreF32: return launch_mt<kStoreF32, false>(a, sm_count, stream);
+      case kAddResidual: return launch_mt<kAddResidual, false>(a, sm_count, stream);
+      case kSwiglu: return launch_mt<kSwiglu, false>(a, sm_count, stream);
     }
   }
   return static_cast<int>(cudaErrorInvalidValue);

@@ -165,15 +165,75 @@ __device__ uint32_t select_top_p(const float* l, int vocab, float mx, float inv_
   return prefix;
 }
 
+// First stage for greedy rows: the row is cut into kSampleChunks pieces, one CTA each, which
+// leave (max, arg max, sum of exp(l - max)) of their piece.  sample_kernel combines them.
+constexpr int kSampleChunks = 64;
+
+struct ChunkStat {
+  float mx;
+  int idx;
+  float sumexp;
+  float pad;
+};
+
+__global__ void __launch_bounds__(256)
+sample_partial_kernel(const float* __restrict__ logits, int vocab, int ld, ChunkStat* __restrict__ stats) {
+  pdl_launch();
+  pdl_wait();
+  __shared__ Best bscratch[32];
+  __shared__ float fscratch[32];
+  const int row = blockIdx.x, chunk = blockIdx.y;
+  const int per = (vocab + kSampleChunks - 1) / kSampleChunks;
+  const int lo = chunk * per, hi = min(vocab, lo + per);
+  const float* l = logits + static_cast<size_t>(row) * ld;
+  Best b{-FLT_MAX, 0x7fffffff};
+  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) b = better(b, Best{l[i], i});
+  b = block_best(b, bscratch);
+  float s = 0.f;
+  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) s += expf(l[i] - b.v);
+  s = block_sum(s, fscratch);
+  if (threadIdx.x == 0) stats[row * kSampleChunks + chunk] = ChunkStat{b.v, b.i, s, 0.f};
+}
+
 __global__ void __launch_bounds__(kSampleThreads)
 sample_kernel(const float* __restrict__ logits, int vocab, int ld, const float* __restrict__ temperature,
               const int32_t* __restrict__ top_k, const float* __restrict__ top_p,
               const uint32_t* __restrict__ seed_lo, const uint32_t* __restrict__ seed_hi,
               const int32_t* __restrict__ position, uint32_t stream_id, int32_t* __restrict__ out_token,
-              float* __restrict__ out_logprob) {
+              float* __restrict__ out_logprob, const ChunkStat* __restrict__ stats) {
+  pdl_launch();
+  pdl_wait();
   __shared__ SampleSmem sh;
   const int row = blockIdx.x;
   const float* l = logits + static_cast<size_t>(row) * ld;
+  if (stats != nullptr && temperature[row] <= 0.f) {
+    // greedy row with first-stage statistics: combine the pieces (smaller index wins ties)
+    if (threadIdx.x < 32) {
+      Best b{-FLT_MAX, 0x7fffffff};
+      for (int c = threadIdx.x; c < kSampleChunks; c += 32) {
+        const ChunkStat st = stats[row * kSampleChunks + c];
+        if (st.idx != 0x7fffffff) b = better(b, Best{st.mx, st.idx});
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        Best y;
+        y.v = __shfl_xor_sync(0xffffffffu, b.v, o);
+        y.i = __shfl_xor_sync(0xffffffffu, b.i, o);
+        b = better(b, y);
+      }
+      float sum = 0.f;
+      for (int c = threadIdx.x; c < kSampleChunks; c += 32) {
+        const ChunkStat st = stats[row * kSampleChunks + c];
+        if (st.idx != 0x7fffffff) sum += st.sumexp * expf(st.mx - b.v);
+      }
+      sum = warp_sum(sum);
+      if (threadIdx.x == 0) {
+        out_token[row] = b.i;
+        if (out_logprob) out_logprob[row] = l[b.i] - (b.v + logf(sum));
+      }
+    }
+    return;
+  }
 
   Best b{-FLT_MAX, 0x7fffffff};
   for (int i = threadIdx.x; i < vocab; i += blockDim.x) b = better(b, Best{l[i], i});
@@ -232,6 +292,8 @@ sample_kernel(const float* __restrict__ logits, int vocab, int ld, const float* 
 __global__ void __launch_bounds__(512)
 gather_logprob_kernel(const float* __restrict__ logits, int vocab, int ld,
                       const int32_t* __restrict__ target, float* __restrict__ out) {
+  pdl_launch();
+  pdl_wait();
   __shared__ float scratch[32];
   const float* l = logits + static_cast<size_t>(blockIdx.x) * ld;
   float m = -FLT_MAX;
@@ -249,21 +311,31 @@ using namespace rl;
 
 extern "C" {
 
+int rl_sample_chunks() { return kSampleChunks; }
+
+// scratch: optional [rows * rl_sample_chunks() * 4] floats.  With it, rows whose temperature is <= 0
+// are served by a two-stage arg max that uses the whole GPU instead of one CTA per row.
 int rl_sample(const float* logits, int rows, int vocab, int ld, const float* temperature,
               const int32_t* top_k, const float* top_p, const uint32_t* seed_lo,
               const uint32_t* seed_hi, const int32_t* position, unsigned stream_id,
-              int32_t* out_token, float* out_logprob, cudaStream_t stream) {
+              int32_t* out_token, float* out_logprob, float* scratch, cudaStream_t stream) {
   if (rows <= 0) return 0;
-  sample_kernel<<<rows, kSampleThreads, 0, stream>>>(logits, vocab, ld, temperature, top_k, top_p,
+  ChunkStat* stats = reinterpret_cast<ChunkStat*>(scratch);
+  if (stats != nullptr) {
+    launch_kernel(sample_partial_kernel, dim3(rows, kSampleChunks), dim3(256), 0, stream, logits, vocab, ld, stats);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return static_cast<int>(e);
+  }
+  launch_kernel(sample_kernel, dim3(rows), dim3(kSampleThreads), 0, stream, logits, vocab, ld, temperature, top_k, top_p,
                                                      seed_lo, seed_hi, position, stream_id, out_token,
-                                                     out_logprob);
+                                                     out_logprob, stats);
   RL_LAUNCH_END();
 }
 
 int rl_gather_logprob(const float* logits, int rows, int vocab, int ld, const int32_t* target,
                       float* out, cudaStream_t stream) {
   if (rows <= 0) return 0;
-  gather_logprob_kernel<<<rows, 512, 0, stream>>>(logits, vocab, ld, target, out);
+  launch_kernel(gather_logprob_kernel, dim3(rows), dim3(512), 0, stream, logits, vocab, ld, target, out);
   RL_LAUNCH_END();
 }
 

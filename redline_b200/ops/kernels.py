@@ -278,18 +278,26 @@ def attn_prefill(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcache: t
 
 # -------------------------------------------------------------------- sampling
 
+SAMPLE_CHUNKS = 64
+
+
 def sample(logits: torch.Tensor, rows: int, temperature: torch.Tensor, top_k: torch.Tensor,
            top_p: torch.Tensor, seed_lo: torch.Tensor, seed_hi: torch.Tensor, position: torch.Tensor,
-           out_token: torch.Tensor, out_logprob: Optional[torch.Tensor], stream_id: int = 0) -> None:
+           out_token: torch.Tensor, out_logprob: Optional[torch.Tensor], stream_id: int = 0,
+           scratch: Optional[torch.Tensor] = None) -> None:
+    """One token per row of float32 logits.  ``scratch`` (float32, rows * SAMPLE_CHUNKS * 4) lets greedy
+    rows use a two-stage arg max over the whole GPU."""
     _need_cuda(logits, out_token)
     if logits.dtype != torch.float32:
         raise KernelError("sample: logits must be float32")
     f = _fn(_lib("sampling", "sampling.cu"), "rl_sample",
             [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-             c_uint, c_void_p, c_void_p, c_void_p])
+             c_uint, c_void_p, c_void_p, c_void_p, c_void_p])
+    if scratch is not None and scratch.numel() < rows * SAMPLE_CHUNKS * 4:
+        raise KernelError("sample: scratch too small")
     _check(f(_ptr(logits), rows, logits.shape[1], logits.stride(0), _ptr(temperature), _ptr(top_k),
              _ptr(top_p), _ptr(seed_lo), _ptr(seed_hi), _ptr(position), stream_id, _ptr(out_token),
-             _ptr(out_logprob), _stream()), "sample")
+             _ptr(out_logprob), _ptr(scratch), _stream()), "sample", 2 if scratch is not None else 1)
 
 
 def gather_logprob(logits: torch.Tensor, rows: int, target: torch.Tensor, out: torch.Tensor) -> None:

@@ -13,7 +13,13 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
 
-def run(logits, temperature, top_k, top_p, seeds, positions):
+def run(logits, temperature, top_k, top_p, seeds, positions, two_stage=None):
+    """two_stage None: both ways must agree (greedy rows take the two-stage arg max when scratch is given)."""
+    if two_stage is None:
+        a = run(logits, temperature, top_k, top_p, seeds, positions, two_stage=False)
+        b = run(logits, temperature, top_k, top_p, seeds, positions, two_stage=True)
+        assert np.array_equal(a[0], b[0]) and np.abs(a[1] - b[1]).max() < 1e-4
+        return b
     R = logits.shape[0]
     f = lambda v, dt: torch.tensor(np.broadcast_to(np.asarray(v), (R,)).copy(), dtype=dt, device=DEV)  # noqa: E731
     seeds = np.broadcast_to(np.asarray(seeds, dtype=np.uint64), (R,))
@@ -21,8 +27,9 @@ def run(logits, temperature, top_k, top_p, seeds, positions):
     hi = torch.tensor((seeds >> 32).astype(np.int64), device=DEV).to(torch.int32)
     tok = torch.empty(R, dtype=torch.int32, device=DEV)
     lp = torch.empty(R, dtype=torch.float32, device=DEV)
+    scratch = torch.full((R * kernels.SAMPLE_CHUNKS * 4,), float("nan"), device=DEV) if two_stage else None
     kernels.sample(logits, R, f(temperature, torch.float32), f(top_k, torch.int32), f(top_p, torch.float32),
-                   lo, hi, f(positions, torch.int32), tok, lp)
+                   lo, hi, f(positions, torch.int32), tok, lp, scratch=scratch)
     return tok.cpu().numpy(), lp.cpu().numpy()
 
 
@@ -73,8 +80,14 @@ def test_large_vocabulary_top_k_membership():
     tok, lp = run(l, 1.0, 50, 1.0, [1, 2, 3, 4], [10, 10, 10, 10])
     top = torch.topk(l, 50, dim=-1).indices.cpu().numpy()
     assert all(tok[r] in top[r] for r in range(4)) and np.all(np.isfinite(lp))
-    tok_g, _ = run(l, 0.0, 0, 1.0, 0, 0)
+    tok_g, lp_g = run(l, 0.0, 0, 1.0, 0, 0)
     assert tok_g.tolist() == l.argmax(-1).tolist()
+    want = torch.log_softmax(l.double(), -1).max(-1).values.cpu().numpy()
+    assert np.abs(lp_g - want).max() < 1e-4
+    # greedy and sampled rows in one launch
+    temp = np.array([0.0, 1.0, 0.0, 0.7], dtype=np.float32)
+    tok_m, _ = run(l, temp, 50, 1.0, [1, 2, 3, 4], [10, 10, 10, 10])
+    assert tok_m[0] == tok_g[0] and tok_m[2] == tok_g[2] and tok_m[1] in top[1] and tok_m[3] in top[3]
 
 
 def test_gather_logprob():
