@@ -61,7 +61,67 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __res
   float* res = residual + static_cast<size_t>(src) * hidden;
   const TD* d = delta ? delta + static_cast<size_t>(src) * hidden : nullptr;
   const bool write_back = (d != nullptr) && (rows_idx == nullptr);
+  TA* o = out + static_cast<size_t>(r) * hidden;
   float ss = 0.f;
+  if (hidden % 8 == 0) {
+    // eight columns per thread and step: 16-byte pieces of every operand that is 16 bits wide,
+    // two of every operand that is 32 bits wide
+    for (int c = threadIdx.x * 8; c < hidden; c += blockDim.x * 8) {
+      float v[8];
+      load16(res + c, v);
+      load16(res + c + 4, v + 4);
+      if (d) {
+        float dv[8];
+        if (sizeof(TD) == 2) {
+          load16(d + c, dv);
+        } else {
+          load16(d + c, dv);
+          load16(d + c + 4, dv + 4);
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] += dv[e];
+        if (write_back) {
+          store16(res + c, v);
+          store16(res + c + 4, v + 4);
+        }
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) ss += v[e] * v[e];
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = rsqrtf(ss / static_cast<float>(hidden) + eps);
+    for (int c = threadIdx.x * 8; c < hidden; c += blockDim.x * 8) {
+      float v[8], w[8], y[8];
+      load16(res + c, v);
+      load16(res + c + 4, v + 4);
+      if (d && !write_back) {
+        float dv[8];
+        if (sizeof(TD) == 2) {
+          load16(d + c, dv);
+        } else {
+          load16(d + c, dv);
+          load16(d + c + 4, dv + 4);
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] += dv[e];
+      }
+      if (sizeof(TW) == 2) {
+        load16(weight + c, w);
+      } else {
+        load16(weight + c, w);
+        load16(weight + c + 4, w + 4);
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) y[e] = v[e] * inv * w[e];
+      if (sizeof(TA) == 2) {
+        store16(o + c, y);
+      } else {
+        store16(o + c, y);
+        store16(o + c + 4, y + 4);
+      }
+    }
+    return;
+  }
   for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
     float v = res[c];
     if (d) v += to_float(d[c]);
@@ -70,7 +130,6 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __res
   }
   ss = block_sum(ss, scratch);
   const float inv = rsqrtf(ss / static_cast<float>(hidden) + eps);
-  TA* o = out + static_cast<size_t>(r) * hidden;
   for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
     float v = res[c];
     if (d && !write_back) v += to_float(d[c]);
@@ -95,13 +154,25 @@ template <typename TA>
 __global__ void swiglu_kernel(const TA* __restrict__ gu, TA* __restrict__ out, int inter) {
   pdl_launch();
   pdl_wait();
+  constexpr int VEC = Vec16<TA>::N;
   const int t = blockIdx.y;
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= inter) return;
   const TA* row = gu + static_cast<size_t>(t) * 2 * inter;
-  const float g = to_float(row[i]);
-  const float u = to_float(row[inter + i]);
-  out[static_cast<size_t>(t) * inter + i] = from_float<TA>(g / (1.f + expf(-g)) * u);
+  TA* o = out + static_cast<size_t>(t) * inter;
+  if (inter % VEC == 0) {                       // 16-byte pieces
+    const int i = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
+    if (i >= inter) return;
+    float g[VEC], u[VEC], r[VEC];
+    load16(row + i, g);
+    load16(row + inter + i, u);
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) r[e] = g[e] / (1.f + expf(-g[e])) * u[e];
+    store16(o + i, r);
+  } else {
+    for (int i = (blockIdx.x * blockDim.x + threadIdx.x) * VEC, e = 0; e < VEC && i + e < inter; ++e) {
+      const float g = to_float(row[i + e]), u = to_float(row[inter + i + e]);
+      o[i + e] = from_float<TA>(g / (1.f + expf(-g)) * u);
+    }
+  }
 }
 
 // ------------------------------------------------------------- add bias
@@ -128,6 +199,7 @@ __global__ void rope_kv_write_kernel(TA* __restrict__ qkv, const int32_t* __rest
                                      int d, int page_size, int max_pos, int* status) {
   pdl_launch();
   pdl_wait();
+  constexpr int VEC = Vec16<TA>::N;    // head sizes are multiples of 16, so D / 2 is a multiple of VEC
   const int t = blockIdx.x;
   const int half = d >> 1;
   const int pos = positions[t];
@@ -140,32 +212,38 @@ __global__ void rope_kv_write_kernel(TA* __restrict__ qkv, const int32_t* __rest
   const size_t page = slot >= 0 ? slot / page_size : 0;
   const int off = slot >= 0 ? slot % page_size : 0;
   const int rot_heads = hq + hkv;
-  // one (head, pair) per thread-iteration over q and k heads
-  for (int idx = threadIdx.x; idx < rot_heads * half; idx += blockDim.x) {
-    const int h = idx / half, i = idx - h * half;
+  const int vec_per_head = half / VEC;
+  // one (head, run of VEC pairs (i, i + D/2)) per thread-iteration over q and k heads
+  for (int idx = threadIdx.x; idx < rot_heads * vec_per_head; idx += blockDim.x) {
+    const int h = idx / vec_per_head, i = (idx - h * vec_per_head) * VEC;
     TA* v = row + h * d;
-    float x0 = to_float(v[i]), x1 = to_float(v[i + half]);
+    float x0[VEC], x1[VEC];
+    load16(v + i, x0);
+    load16(v + i + half, x1);
     if (c) {
-      const float cc = c[i], sn = s[i];
-      const float y0 = x0 * cc - x1 * sn;
-      const float y1 = x1 * cc + x0 * sn;
-      x0 = y0;
-      x1 = y1;
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) {
+        const float cc = c[i + e], sn = s[i + e];
+        const float y0 = x0[e] * cc - x1[e] * sn;
+        const float y1 = x1[e] * cc + x0[e] * sn;
+        x0[e] = y0;
+        x1[e] = y1;
+      }
     }
-    const TA r0 = from_float<TA>(x0), r1 = from_float<TA>(x1);
-    v[i] = r0;
-    v[i + half] = r1;
+    store16(v + i, x0);
+    store16(v + i + half, x1);
     if (h >= hq && slot >= 0) {
       TA* dst = kcache + ((page * hkv + (h - hq)) * page_size + off) * d;
-      dst[i] = r0;
-      dst[i + half] = r1;
+      store16(dst + i, x0);
+      store16(dst + i + half, x1);
     }
   }
   if (slot >= 0) {
     const TA* vrow = row + (hq + hkv) * d;
-    for (int idx = threadIdx.x; idx < hkv * d; idx += blockDim.x) {
+    for (int idx = threadIdx.x * VEC; idx < hkv * d; idx += blockDim.x * VEC) {
       const int h = idx / d, i = idx - h * d;
-      vcache[((page * hkv + h) * page_size + off) * d + i] = vrow[idx];
+      *reinterpret_cast<uint4*>(vcache + ((page * hkv + h) * page_size + off) * d + i) =
+          *reinterpret_cast<const uint4*>(vrow + idx);
     }
   }
 }
@@ -239,7 +317,8 @@ int rl_add_residual(float* residual, const void* delta, int act_dtype, long long
 int rl_swiglu(const void* gu, void* out, int act_dtype, int tokens, int inter, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   const int th = 256;
-  dim3 grid((inter + th - 1) / th, tokens);
+  const int per_block = th * (act_dtype == RL_F32 ? 4 : 8);   // a thread takes one 16-byte piece
+  dim3 grid((inter + per_block - 1) / per_block, tokens);
   if (act_dtype == RL_F32)
     launch_kernel(swiglu_kernel<float>, dim3(grid), dim3(th), 0, stream, static_cast<const float*>(gu), static_cast<float*>(out), inter);
   else
