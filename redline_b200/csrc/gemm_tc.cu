@@ -1,0 +1,368 @@
+// y[M, N] = x[M, K] . W[N, K]^T for many rows (prompt portions), bfloat16 operands, on the
+// fifth-generation tensor cores: tcgen05.mma with the accumulator in tensor memory (TMEM),
+// operands brought into shared memory by TMA (cp.async.bulk.tensor, 128-byte swizzle).
+//
+// One CTA computes one 128 x 128 tile of y.  Warp roles:
+//   warp 0     producer: one lane issues the TMA loads of the A (x) and B (W) tiles of every
+//              64-wide k block into a ring of shared-memory stages and arms the stage's
+//              "full" mbarrier with the byte count
+//   warp 1     allocates TMEM; one lane issues the MMAs (four of K = 16 per stage) and commits
+//              them to the stage's "empty" mbarrier, and after the last block to "accumulator
+//              full"
+//   warps 2-5  epilogue: each reads its quarter of the 128 TMEM lanes with tcgen05.ld and
+//              writes bfloat16 or float32 rows (or adds into the float32 residual stream, or
+//              forms silu(gate) * up when the B tile holds 64 gate rows and their 64 up rows)
+// Both operands are K-major (x row-major, W [N, K] row-major), which is how the weights are
+// stored.  No cluster multicast is used anywhere.
+//
+// Every wait on an mbarrier is bounded: after kSpinLimit polls the CTA raises a flag in
+// shared memory, all roles leave their loops, outstanding loads are waited for (again
+// bounded), TMEM is freed, and bit 0 of *status is set for the host to read.  The kernel
+// never traps and never spins without a limit.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace rl {
+
+constexpr int kBM = 128, kBN = 128, kBK = 64, kStages = 5, kUmmaK = 16;
+constexpr int kStageBytesA = kBM * kBK * 2, kStageBytesB = kBN * kBK * 2;
+constexpr int kTcThreads = 192;          // 6 warps
+constexpr int kSpinLimit = 1 << 22;
+constexpr int kTmemCols = 128;
+
+enum TcEpilogue { kTcBf16 = 0, kTcF32 = 1, kTcAddResidual = 2, kTcSwiglu = 3 };
+
+struct TcShared {
+  uint64_t full[kStages];
+  uint64_t empty[kStages];
+  uint64_t acc_full;
+  uint32_t tmem_base;
+  volatile int abort;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Waits for the phase with the given parity; false if the CTA is aborting or the limit ran out.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort) {
+  for (int i = 0; i < kSpinLimit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*abort) return false;
+  }
+  *abort = 1;
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* smem, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 bfloat16),
+// 128-byte swizzled as TMA leaves it: 8-row groups are 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);        // start address
+  d |= static_cast<uint64_t>(1) << 16;                            // leading byte offset (unused for this layout)
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;                    // stride byte offset: 8 rows x 128 B
+  d |= static_cast<uint64_t>(1) << 46;                            // descriptor version of sm_100
+  d |= static_cast<uint64_t>(2) << 61;                            // layout: 128-byte swizzle
+  return d;
+}
+
+// Instruction descriptor of kind::f16: D float32, A and B bfloat16, both K-major, M x N tile.
+__device__ __forceinline__ uint32_t umma_idesc(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) |
+         (static_cast<uint32_t>(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// 16 consecutive float32 columns of this thread's TMEM lane.
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+struct TcArgs {
+  void* y;          // bf16 / float output, or the float32 residual stream
+  int M, N, K, ldy;
+  int n_up;         // kTcSwiglu: row of W where the up rows start (the number of gate rows)
+  int* status;
+};
+
+template <int EPI>
+__global__ void __launch_bounds__(kTcThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const TcArgs a) {
+  extern __shared__ unsigned char smem_raw[];
+  // the stages need 1024-byte alignment for the 128-byte swizzle
+  const uint32_t raw = smem_u32(smem_raw);
+  unsigned char* base = smem_raw + ((1024u - (raw & 1023u)) & 1023u);
+  unsigned char* smem_a = base;
+  unsigned char* smem_b = base + kStages * kStageBytesA;
+  TcShared* sh = reinterpret_cast<TcShared*>(base + kStages * (kStageBytesA + kStageBytesB));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.y * kBM;
+  // plain product: 128 features per tile; gated: 64 gate features and their 64 up features
+  const int n0 = blockIdx.x * (EPI == kTcSwiglu ? kBN / 2 : kBN);
+  const int nkb = (a.K + kBK - 1) / kBK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&sh->full[s], 1);
+      mbar_init(&sh->empty[s], 1);
+    }
+    mbar_init(&sh->acc_full, 1);
+    sh->abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {   // TMEM allocation is a whole-warp operation
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh->tmem_base)),
+                 "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sh->tmem_base;
+  pdl_launch();
+  pdl_wait();        // x is written by earlier kernels of the step
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int issued = 0;
+      for (int kb = 0; kb < nkb; ++kb) {
+        const int s = kb % kStages;
+        const uint32_t parity = ((kb / kStages) & 1) ^ 1;          // a fresh barrier passes a wait on parity 1
+        if (!mbar_wait(&sh->empty[s], parity, &sh->abort)) break;
+        mbar_expect_tx(&sh->full[s], kStageBytesA + kStageBytesB);
+        tma_load_2d(smem_a + s * kStageBytesA, &map_a, &sh->full[s], kb * kBK, m0);
+        if (EPI == kTcSwiglu) {
+          tma_load_2d(smem_b + s * kStageBytesB, &map_b, &sh->full[s], kb * kBK, n0);
+          tma_load_2d(smem_b + s * kStageBytesB + kStageBytesB / 2, &map_b, &sh->full[s], kb * kBK, a.n_up + n0);
+        } else {
+          tma_load_2d(smem_b + s * kStageBytesB, &map_b, &sh->full[s], kb * kBK, n0);
+        }
+        ++issued;
+      }
+      if (sh->abort) {
+        // loads still in flight write shared memory: wait for them (bounded) before the CTA ends
+        for (int kb = max(0, issued - kStages); kb < issued; ++kb) {
+          const int s = kb % kStages;
+          for (int i = 0; i < kSpinLimit && !mbar_try_wait(&sh->full[s], (kb / kStages) & 1); ++i) {
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc(kBM, kBN);
+      bool ok = true;
+      for (int kb = 0; kb < nkb && ok; ++kb) {
+        const int s = kb % kStages;
+        ok = mbar_wait(&sh->full[s], (kb / kStages) & 1, &sh->abort);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t a_addr = smem_u32(smem_a + s * kStageBytesA), b_addr = smem_u32(smem_b + s * kStageBytesB);
+#pragma unroll
+        for (int k = 0; k < kBK / kUmmaK; ++k) {
+          // inside the 128-byte swizzle atom the next 16 k (32 bytes) are 32 bytes further on
+          umma_bf16(tmem, umma_desc(a_addr + k * kUmmaK * 2), umma_desc(b_addr + k * kUmmaK * 2), idesc,
+                    (kb | k) != 0);
+        }
+        umma_commit(&sh->empty[s]);     // the stage is free once these MMAs have read it
+      }
+      if (ok) umma_commit(&sh->acc_full);
+    }
+  } else {
+    // epilogue warps 2..5: warp w may touch TMEM lanes 32 * (w % 4) .. + 32
+    const int q = warp & 3;
+    const bool ok = mbar_wait(&sh->acc_full, 0, &sh->abort);
+    tc_fence_after();
+    const int row = m0 + q * 32 + lane;
+    if (ok) {
+      if (EPI == kTcSwiglu) {
+#pragma unroll 1
+        for (int c = 0; c < kBN / 2; c += 16) {
+          float g[16], u[16];
+          tmem_ld16(tmem + (static_cast<uint32_t>(q * 32) << 16) + c, g);
+          tmem_ld16(tmem + (static_cast<uint32_t>(q * 32) << 16) + kBN / 2 + c, u);
+          if (row < a.M) {
+            bf16* out = static_cast<bf16*>(a.y) + static_cast<size_t>(row) * a.ldy + n0 + c;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              if (n0 + c + i < a.N) {
+                const float gt = __bfloat162float(__float2bfloat16_rn(g[i])), up = __bfloat162float(__float2bfloat16_rn(u[i]));
+                out[i] = __float2bfloat16_rn(gt / (1.f + expf(-gt)) * up);
+              }
+            }
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < kBN; c += 16) {
+          float v[16];
+          tmem_ld16(tmem + (static_cast<uint32_t>(q * 32) << 16) + c, v);
+          if (row < a.M) {
+            const size_t o = static_cast<size_t>(row) * a.ldy + n0 + c;
+            const bool full16 = (n0 + c + 16 <= a.N);
+            if (EPI == kTcBf16) {
+              bf16* out = static_cast<bf16*>(a.y) + o;
+              if (full16 && (a.ldy % 8 == 0)) {
+                store16(out, v);
+                store16(out + 8, v + 8);
+              } else {
+                for (int i = 0; i < 16 && n0 + c + i < a.N; ++i) out[i] = __float2bfloat16_rn(v[i]);
+              }
+            } else if (EPI == kTcF32) {
+              float* out = static_cast<float*>(a.y) + o;
+              for (int i = 0; i < 16 && n0 + c + i < a.N; ++i) out[i] = v[i];
+            } else {
+              float* out = static_cast<float*>(a.y) + o;   // residual += bfloat16(product)
+              for (int i = 0; i < 16 && n0 + c + i < a.N; ++i) out[i] += __bfloat162float(__float2bfloat16_rn(v[i]));
+            }
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+  }
+  if (threadIdx.x == 0 && sh->abort) atomicOr(a.status, 1);
+}
+
+// ---------------------------------------------------------------------------- host side
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+// A [rows, K] bfloat16 matrix with row pitch ld (elements), tiles of box_rows x 64, 128-byte swizzle.
+static bool make_map(CUtensorMap* map, const void* ptr, int rows, int K, int ld, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
+  const cuuint32_t box[2] = {kBK, static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t estr[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int EPI>
+static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcArgs& a, cudaStream_t stream) {
+  const size_t smem = static_cast<size_t>(kStages) * (kStageBytesA + kStageBytesB) + sizeof(TcShared) + 1024;
+  static bool attr = false;
+  if (!attr) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(smem));
+    if (e != cudaSuccess) return static_cast<int>(e);
+    attr = true;
+  }
+  const int tile_n = (EPI == kTcSwiglu) ? kBN / 2 : kBN;
+  dim3 grid((a.N + tile_n - 1) / tile_n, (a.M + kBM - 1) / kBM);
+  launch_kernel(gemm_tc_kernel<EPI>, grid, dim3(kTcThreads), smem, stream, ma, mb, a);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace rl
+
+using namespace rl;
+
+extern "C" {
+
+// epilogue: 0 bf16 store, 1 float32 store, 2 residual (float32) += product, 3 SiLU-gated product
+// (w holds N gate rows then N up rows; y is [M, N] bfloat16).  x [M, K] and w [N or 2N, K] are
+// bfloat16 with K a multiple of 8 and 16-byte aligned rows.  status: device int, bit 0 is set if a
+// wait inside the kernel ran out.  Returns cudaErrorInvalidValue for shapes it does not take.
+int rl_gemm_tc(const void* x, int ldx, const void* w, void* y, int ldy, int epilogue, int M, int N, int K,
+               int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K % 8 != 0 || ldx % 8 != 0 || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15))
+    return static_cast<int>(cudaErrorInvalidValue);
+  CUtensorMap ma, mb;
+  const bool gated = epilogue == kTcSwiglu;
+  if (!make_map(&ma, x, M, K, ldx, kBM)) return static_cast<int>(cudaErrorNotSupported);
+  if (!make_map(&mb, w, gated ? 2 * N : N, K, K, gated ? kBN / 2 : kBN)) return static_cast<int>(cudaErrorNotSupported);
+  TcArgs a;
+  a.y = y;
+  a.M = M;
+  a.N = N;
+  a.K = K;
+  a.ldy = ldy;
+  a.n_up = N;
+  a.status = status;
+  switch (epilogue) {
+    case kTcBf16: return launch_tc<kTcBf16>(ma, mb, a, stream);
+    case kTcF32: return launch_tc<kTcF32>(ma, mb, a, stream);
+    case kTcAddResidual: return launch_tc<kTcAddResidual>(ma, mb, a, stream);
+    case kTcSwiglu: return launch_tc<kTcSwiglu>(ma, mb, a, stream);
+  }
+  return static_cast<int>(cudaErrorInvalidValue);
+}
+
+}  // extern "C"

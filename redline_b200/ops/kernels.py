@@ -214,6 +214,42 @@ def gemm_skinny(w: torch.Tensor, y: torch.Tensor, epilogue: int, rows: int, x: O
              1 if norm else 0, _ptr(y), y.stride(0), epilogue, rows, N, K, sm_count(w.device), _stream()),
            "gemm_skinny")
 
+
+# ------------------------------------------------------------ tcgen05 gemm
+
+_tc_status: Dict[int, torch.Tensor] = {}
+
+
+def tc_status(device: torch.device) -> torch.Tensor:
+    """The device word in which gemm_tc reports a wait that ran out (bit 0)."""
+    i = device.index if device.index is not None else torch.cuda.current_device()
+    if i not in _tc_status:
+        _tc_status[i] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _tc_status[i]
+
+
+def gemm_tc_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether gemm_tc takes this product: bfloat16 operands, K a multiple of 8, 16-byte aligned rows."""
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[1] % 8 == 0 and w.is_contiguous()
+            and x.stride(1) == 1 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_tc(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, epilogue: int = EPI_BF16) -> None:
+    """y = epilogue(x @ w^T) with tcgen05 tensor cores, TMEM accumulators and TMA loads
+    (csrc/gemm_tc.cu): bfloat16 x [M, K], w [N, K] (EPI_SWIGLU: [2 N, K], gate rows then up rows).
+    Epilogues as gemm_skinny's."""
+    _need_cuda(x, w, y)
+    f = _fn(_lib("gemm_tc", "gemm_tc.cu"), "rl_gemm_tc",
+            [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+    M, K = x.shape
+    N = w.shape[0] // 2 if epilogue == EPI_SWIGLU else w.shape[0]
+    want = {EPI_BF16: torch.bfloat16, EPI_F32: torch.float32, EPI_ADD_RESIDUAL: torch.float32,
+            EPI_SWIGLU: torch.bfloat16}[epilogue]
+    if w.shape[1] != K or y.dtype != want or y.shape[1] != N or y.stride(1) != 1 or not gemm_tc_ok(x, w):
+        raise KernelError(f"gemm_tc: shapes x{tuple(x.shape)} w{tuple(w.shape)} y{tuple(y.shape)} {y.dtype}")
+    _check(f(_ptr(x), x.stride(0), _ptr(w), _ptr(y), y.stride(0), epilogue, M, N, K, _ptr(tc_status(x.device)),
+             _stream()), "gemm_tc")
+
 # ------------------------------------------------------------------- attention
 
 MAX_HEAD_DIM = 256
@@ -313,6 +349,7 @@ def build_all(head_dims=(64, 128), verbose: bool = True) -> None:
     build.compile_module("elementwise", "elementwise.cu", verbose=verbose)
     build.compile_module("gemm_simt", "gemm_simt.cu", verbose=verbose)
     build.compile_module("gemm_skinny", "gemm_skinny.cu", verbose=verbose)
+    build.compile_module("gemm_tc", "gemm_tc.cu", verbose=verbose)
     build.compile_module("sampling", "sampling.cu", verbose=verbose)
     for d in head_dims:
         build.compile_module(f"attention_d{d}", "attention.cu", {"RL_HEAD_DIM": d}, verbose=verbose)
