@@ -5,6 +5,7 @@ package, if present).
     python -m redline_b200.apps.kernel_bench attn_decode --batch 8 --ctx 4096
     python -m redline_b200.apps.kernel_bench skinny --rows 8 --n 3072 --k 2048 [--norm] [--epilogue swiglu]
     python -m redline_b200.apps.kernel_bench attn_prefill --tokens 2048
+    python -m redline_b200.apps.kernel_bench gemm_tc --rows 2048 --n 8192 --k 2048 --epilogue swiglu [--library]
 
 Each kernel runs over several distinct copies of its large operands (more than the
 L2 holds), captured in a CUDA graph so that launch overhead of the host is not
@@ -125,6 +126,35 @@ def bench_skinny(args) -> None:
                       "frac_of_measured_hbm": round(nbytes / us / 1e3 / pk["hbm_gbs"], 3), "copies": copies}))
 
 
+def bench_gemm_tc(args) -> None:
+    dev = "cuda"
+    M, N, K = args.rows, args.n, args.k
+    epi = {"bf16": kernels.EPI_BF16, "f32": kernels.EPI_F32, "residual": kernels.EPI_ADD_RESIDUAL,
+           "swiglu": kernels.EPI_SWIGLU}[args.epilogue]
+    wn = 2 * N if epi == kernels.EPI_SWIGLU else N
+    copies = max(2, min(args.copies, int(1e9 // (wn * K * 2))))
+    ws = [(torch.randn(wn, K, device=dev) * 0.02).to(torch.bfloat16) for _ in range(copies)]
+    x = torch.randn(M, K, device=dev).to(torch.bfloat16)
+    ydt = {kernels.EPI_BF16: torch.bfloat16, kernels.EPI_F32: torch.float32, kernels.EPI_ADD_RESIDUAL: torch.float32,
+           kernels.EPI_SWIGLU: torch.bfloat16}[epi]
+    y = torch.zeros(M, N, device=dev, dtype=ydt)
+    yl = torch.empty(M, wn, device=dev, dtype=torch.bfloat16)
+
+    def fn(i):
+        w = ws[i % copies]
+        if args.library:
+            torch.mm(x, w.t(), out=yl)
+        else:
+            kernels.gemm_tc(x, w, y, epi)
+
+    us = graph_time_us(fn, copies, use_graph=not args.no_graph)
+    flops = 2.0 * M * wn * K
+    pk = peaks()
+    print(json.dumps({"kernel": "library_mm" if args.library else "gemm_tc", "rows": M, "n": N, "k": K,
+                      "epilogue": args.epilogue, "us": round(us, 2), "TFLOP/s": round(flops / us / 1e6, 1),
+                      "frac_of_measured_bf16": round(flops / us / 1e6 / pk["bf16_tflops"], 3), "copies": copies}))
+
+
 def bench_attn_prefill(args) -> None:
     dev = "cuda"
     T, Hq, Hkv, D, ps = args.tokens, args.heads, args.kv_heads, args.head_dim, args.page_size
@@ -156,7 +186,7 @@ def bench_attn_prefill(args) -> None:
 def main() -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     sub = ap.add_subparsers(dest="kernel", required=True)
-    for name in ("attn_decode", "attn_prefill", "skinny"):
+    for name in ("attn_decode", "attn_prefill", "skinny", "gemm_tc"):
         p = sub.add_parser(name)
         p.add_argument("--heads", type=int, default=32)
         p.add_argument("--kv-heads", type=int, default=8)
@@ -170,6 +200,12 @@ def main() -> int:
             p.add_argument("--impl", type=int, default=0, help="0 auto, 1 CUDA cores, 2 tensor cores")
         if name == "attn_prefill":
             p.add_argument("--tokens", type=int, default=2048)
+        if name == "gemm_tc":
+            p.add_argument("--rows", type=int, default=2048)
+            p.add_argument("--n", type=int, default=3072)
+            p.add_argument("--k", type=int, default=2048)
+            p.add_argument("--epilogue", default="bf16", choices=["bf16", "f32", "residual", "swiglu"])
+            p.add_argument("--library", action="store_true", help="time the library product instead")
         if name == "skinny":
             p.add_argument("--rows", type=int, default=8)
             p.add_argument("--n", type=int, default=3072)
@@ -181,7 +217,8 @@ def main() -> int:
     if not torch.cuda.is_available():
         print("kernel_bench needs a CUDA device", file=sys.stderr)
         return 1
-    {"attn_decode": bench_attn_decode, "attn_prefill": bench_attn_prefill, "skinny": bench_skinny}[args.kernel](args)
+    {"attn_decode": bench_attn_decode, "attn_prefill": bench_attn_prefill, "skinny": bench_skinny,
+     "gemm_tc": bench_gemm_tc}[args.kernel](args)
     return 0
 
 

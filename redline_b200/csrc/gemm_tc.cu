@@ -2,13 +2,14 @@
 // fifth-generation tensor cores: tcgen05.mma with the accumulator in tensor memory (TMEM),
 // operands brought into shared memory by TMA (cp.async.bulk.tensor, 128-byte swizzle).
 //
-// One CTA computes one 128 x 128 tile of y.  Warp roles:
+// A CTA computes 128 x 128 tiles of y, one after another (persistent: one CTA per SM); the
+// epilogue of a tile overlaps the MMAs of the next.  Warp roles:
 //   warp 0     producer: one lane issues the TMA loads of the A (x) and B (W) tiles of every
 //              64-wide k block into a ring of shared-memory stages and arms the stage's
 //              "full" mbarrier with the byte count
-//   warp 1     allocates TMEM; one lane issues the MMAs (four of K = 16 per stage) and commits
-//              them to the stage's "empty" mbarrier, and after the last block to "accumulator
-//              full"
+//   warp 1     allocates TMEM (two accumulators); one lane issues the MMAs (four of K = 16 per
+//              stage) and commits them to the stage's "empty" mbarrier, and after a tile's last
+//              block to that accumulator's "full" mbarrier
 //   warps 2-5  epilogue: each reads its quarter of the 128 TMEM lanes with tcgen05.ld and
 //              writes bfloat16 or float32 rows (or adds into the float32 residual stream, or
 //              forms silu(gate) * up when the B tile holds 64 gate rows and their 64 up rows)
@@ -29,14 +30,15 @@ constexpr int kBM = 128, kBN = 128, kBK = 64, kStages = 5, kUmmaK = 16;
 constexpr int kStageBytesA = kBM * kBK * 2, kStageBytesB = kBN * kBK * 2;
 constexpr int kTcThreads = 192;          // 6 warps
 constexpr int kSpinLimit = 1 << 22;
-constexpr int kTmemCols = 128;
+constexpr int kTmemCols = 256;          // two accumulators of 128 columns
 
 enum TcEpilogue { kTcBf16 = 0, kTcF32 = 1, kTcAddResidual = 2, kTcSwiglu = 3 };
 
 struct TcShared {
   uint64_t full[kStages];
   uint64_t empty[kStages];
-  uint64_t acc_full;
+  uint64_t acc_full[2];     // the MMAs of a tile are done: the epilogue may read this TMEM buffer
+  uint64_t acc_empty[2];    // the epilogue has read it: the next tile's MMAs may overwrite it
   uint32_t tmem_base;
   volatile int abort;
 };
@@ -49,6 +51,9 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
 }
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
@@ -116,26 +121,35 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
-// 16 consecutive float32 columns of this thread's TMEM lane.
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
-  uint32_t r[16];
+// 32 consecutive float32 columns of this thread's TMEM lane (two loads in flight, one wait).
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
+  uint32_t r[32];
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
       : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
         "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
       : "r"(taddr));
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr + 16));
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
 
 struct TcArgs {
   void* y;          // bf16 / float output, or the float32 residual stream
   int M, N, K, ldy;
   int n_up;         // kTcSwiglu: row of W where the up rows start (the number of gate rows)
+  int tiles_m, tiles_n;
   int* status;
 };
 
+// Persistent: CTA c takes tiles c, c + gridDim.x, ... (features fastest, so CTAs that run together
+// share rows of x and sweep the weights once).  TMEM holds two accumulators: while the epilogue
+// warps drain one tile, the MMAs of the next tile fill the other.
 template <int EPI>
 __global__ void __launch_bounds__(kTcThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const TcArgs a) {
@@ -148,17 +162,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   TcShared* sh = reinterpret_cast<TcShared*>(base + kStages * (kStageBytesA + kStageBytesB));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.y * kBM;
-  // plain product: 128 features per tile; gated: 64 gate features and their 64 up features
-  const int n0 = blockIdx.x * (EPI == kTcSwiglu ? kBN / 2 : kBN);
+  constexpr int kTileN = (EPI == kTcSwiglu) ? kBN / 2 : kBN;   // gated: 64 gate features and their 64 up features
   const int nkb = (a.K + kBK - 1) / kBK;
+  const int ntiles = a.tiles_m * a.tiles_n;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&sh->full[s], 1);
       mbar_init(&sh->empty[s], 1);
     }
-    mbar_init(&sh->acc_full, 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&sh->acc_full[b], 1);
+      mbar_init(&sh->acc_empty[b], 128);    // every epilogue thread arrives
+    }
     sh->abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -177,26 +193,31 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
   if (warp == 0) {
     if (lane == 0) {
-      int issued = 0;
-      for (int kb = 0; kb < nkb; ++kb) {
-        const int s = kb % kStages;
-        const uint32_t parity = ((kb / kStages) & 1) ^ 1;          // a fresh barrier passes a wait on parity 1
-        if (!mbar_wait(&sh->empty[s], parity, &sh->abort)) break;
-        mbar_expect_tx(&sh->full[s], kStageBytesA + kStageBytesB);
-        tma_load_2d(smem_a + s * kStageBytesA, &map_a, &sh->full[s], kb * kBK, m0);
-        if (EPI == kTcSwiglu) {
-          tma_load_2d(smem_b + s * kStageBytesB, &map_b, &sh->full[s], kb * kBK, n0);
-          tma_load_2d(smem_b + s * kStageBytesB + kStageBytesB / 2, &map_b, &sh->full[s], kb * kBK, a.n_up + n0);
-        } else {
-          tma_load_2d(smem_b + s * kStageBytesB, &map_b, &sh->full[s], kb * kBK, n0);
+      int it = 0, issued = 0;      // it: k blocks over all of this CTA's tiles
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+        const int m0 = (tile / a.tiles_n) * kBM, n0 = (tile % a.tiles_n) * kTileN;
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          const int s = it % kStages;
+          const uint32_t parity = ((it / kStages) & 1) ^ 1;        // a fresh barrier passes a wait on parity 1
+          ok = mbar_wait(&sh->empty[s], parity, &sh->abort);
+          if (!ok) break;
+          mbar_expect_tx(&sh->full[s], kStageBytesA + kStageBytesB);
+          tma_load_2d(smem_a + s * kStageBytesA, &map_a, &sh->full[s], kb * kBK, m0);
+          if (EPI == kTcSwiglu) {
+            tma_load_2d(smem_b + s * kStageBytesB, &map_b, &sh->full[s], kb * kBK, n0);
+            tma_load_2d(smem_b + s * kStageBytesB + kStageBytesB / 2, &map_b, &sh->full[s], kb * kBK, a.n_up + n0);
+          } else {
+            tma_load_2d(smem_b + s * kStageBytesB, &map_b, &sh->full[s], kb * kBK, n0);
+          }
+          ++issued;
         }
-        ++issued;
       }
       if (sh->abort) {
         // loads still in flight write shared memory: wait for them (bounded) before the CTA ends
-        for (int kb = max(0, issued - kStages); kb < issued; ++kb) {
-          const int s = kb % kStages;
-          for (int i = 0; i < kSpinLimit && !mbar_try_wait(&sh->full[s], (kb / kStages) & 1); ++i) {
+        for (int i2 = max(0, issued - kStages); i2 < issued; ++i2) {
+          const int s = i2 % kStages;
+          for (int i = 0; i < kSpinLimit && !mbar_try_wait(&sh->full[s], (i2 / kStages) & 1); ++i) {
           }
         }
       }
@@ -205,72 +226,106 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (lane == 0) {
       const uint32_t idesc = umma_idesc(kBM, kBN);
       bool ok = true;
-      for (int kb = 0; kb < nkb && ok; ++kb) {
-        const int s = kb % kStages;
-        ok = mbar_wait(&sh->full[s], (kb / kStages) & 1, &sh->abort);
+      int it = 0, t = 0;
+      for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++t) {
+        const int buf = t & 1;
+        ok = mbar_wait(&sh->acc_empty[buf], ((t >> 1) & 1) ^ 1, &sh->abort);   // fresh: passes at once
         if (!ok) break;
         tc_fence_after();
-        const uint32_t a_addr = smem_u32(smem_a + s * kStageBytesA), b_addr = smem_u32(smem_b + s * kStageBytesB);
+        const uint32_t acc = tmem + buf * kBN;
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          const int s = it % kStages;
+          ok = mbar_wait(&sh->full[s], (it / kStages) & 1, &sh->abort);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smem_a + s * kStageBytesA), b_addr = smem_u32(smem_b + s * kStageBytesB);
 #pragma unroll
-        for (int k = 0; k < kBK / kUmmaK; ++k) {
-          // inside the 128-byte swizzle atom the next 16 k (32 bytes) are 32 bytes further on
-          umma_bf16(tmem, umma_desc(a_addr + k * kUmmaK * 2), umma_desc(b_addr + k * kUmmaK * 2), idesc,
-                    (kb | k) != 0);
+          for (int k = 0; k < kBK / kUmmaK; ++k) {
+            // inside the 128-byte swizzle atom the next 16 k (32 bytes) are 32 bytes further on
+            umma_bf16(acc, umma_desc(a_addr + k * kUmmaK * 2), umma_desc(b_addr + k * kUmmaK * 2), idesc,
+                      (kb | k) != 0);
+          }
+          umma_commit(&sh->empty[s]);     // the stage is free once these MMAs have read it
         }
-        umma_commit(&sh->empty[s]);     // the stage is free once these MMAs have read it
+        if (ok) umma_commit(&sh->acc_full[buf]);
       }
-      if (ok) umma_commit(&sh->acc_full);
     }
   } else {
     // epilogue warps 2..5: warp w may touch TMEM lanes 32 * (w % 4) .. + 32
     const int q = warp & 3;
-    const bool ok = mbar_wait(&sh->acc_full, 0, &sh->abort);
-    tc_fence_after();
-    const int row = m0 + q * 32 + lane;
-    if (ok) {
+    int t = 0;
+    for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++t) {
+      const int buf = t & 1;
+      const int m0 = (tile / a.tiles_n) * kBM, n0 = (tile % a.tiles_n) * kTileN;
+      if (!mbar_wait(&sh->acc_full[buf], (t >> 1) & 1, &sh->abort)) break;
+      tc_fence_after();
+      const int row = m0 + q * 32 + lane;
+      const uint32_t acc = tmem + buf * kBN + (static_cast<uint32_t>(q * 32) << 16);
       if (EPI == kTcSwiglu) {
 #pragma unroll 1
-        for (int c = 0; c < kBN / 2; c += 16) {
-          float g[16], u[16];
-          tmem_ld16(tmem + (static_cast<uint32_t>(q * 32) << 16) + c, g);
-          tmem_ld16(tmem + (static_cast<uint32_t>(q * 32) << 16) + kBN / 2 + c, u);
+        for (int c = 0; c < kBN / 2; c += 32) {
+          float g[32], u[32], r[32];
+          tmem_ld32(acc + c, g);
+          tmem_ld32(acc + kBN / 2 + c, u);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float gt = __bfloat162float(__float2bfloat16_rn(g[i])), up = __bfloat162float(__float2bfloat16_rn(u[i]));
+            r[i] = gt / (1.f + __expf(-gt)) * up;
+          }
           if (row < a.M) {
             bf16* out = static_cast<bf16*>(a.y) + static_cast<size_t>(row) * a.ldy + n0 + c;
+            if (n0 + c + 32 <= a.N && (a.ldy % 8 == 0)) {
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              if (n0 + c + i < a.N) {
-                const float gt = __bfloat162float(__float2bfloat16_rn(g[i])), up = __bfloat162float(__float2bfloat16_rn(u[i]));
-                out[i] = __float2bfloat16_rn(gt / (1.f + expf(-gt)) * up);
-              }
+              for (int i = 0; i < 32; i += 8) store16(out + i, r + i);
+            } else {
+              for (int i = 0; i < 32 && n0 + c + i < a.N; ++i) out[i] = __float2bfloat16_rn(r[i]);
             }
           }
         }
       } else {
 #pragma unroll 1
-        for (int c = 0; c < kBN; c += 16) {
-          float v[16];
-          tmem_ld16(tmem + (static_cast<uint32_t>(q * 32) << 16) + c, v);
+        for (int c = 0; c < kBN; c += 32) {
+          float v[32];
+          tmem_ld32(acc + c, v);
           if (row < a.M) {
             const size_t o = static_cast<size_t>(row) * a.ldy + n0 + c;
-            const bool full16 = (n0 + c + 16 <= a.N);
+            const bool whole = (n0 + c + 32 <= a.N);
             if (EPI == kTcBf16) {
               bf16* out = static_cast<bf16*>(a.y) + o;
-              if (full16 && (a.ldy % 8 == 0)) {
-                store16(out, v);
-                store16(out + 8, v + 8);
+              if (whole && (a.ldy % 8 == 0)) {
+#pragma unroll
+                for (int i = 0; i < 32; i += 8) store16(out + i, v + i);
               } else {
-                for (int i = 0; i < 16 && n0 + c + i < a.N; ++i) out[i] = __float2bfloat16_rn(v[i]);
+                for (int i = 0; i < 32 && n0 + c + i < a.N; ++i) out[i] = __float2bfloat16_rn(v[i]);
               }
             } else if (EPI == kTcF32) {
               float* out = static_cast<float*>(a.y) + o;
-              for (int i = 0; i < 16 && n0 + c + i < a.N; ++i) out[i] = v[i];
+              if (whole && (a.ldy % 4 == 0)) {
+#pragma unroll
+                for (int i = 0; i < 32; i += 4) store16(out + i, v + i);
+              } else {
+                for (int i = 0; i < 32 && n0 + c + i < a.N; ++i) out[i] = v[i];
+              }
             } else {
               float* out = static_cast<float*>(a.y) + o;   // residual += bfloat16(product)
-              for (int i = 0; i < 16 && n0 + c + i < a.N; ++i) out[i] += __bfloat162float(__float2bfloat16_rn(v[i]));
+              if (whole && (a.ldy % 4 == 0)) {
+#pragma unroll
+                for (int i = 0; i < 32; i += 4) {
+                  float r4[4];
+                  load16(out + i, r4);
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) r4[e] += __bfloat162float(__float2bfloat16_rn(v[i + e]));
+                  store16(out + i, r4);
+                }
+              } else {
+                for (int i = 0; i < 32 && n0 + c + i < a.N; ++i) out[i] += __bfloat162float(__float2bfloat16_rn(v[i]));
+              }
             }
           }
         }
       }
+      tc_fence_before();
+      mbar_arrive(&sh->acc_empty[buf]);     // this thread is done with the buffer
     }
   }
   tc_fence_before();
@@ -314,7 +369,7 @@ static bool make_map(CUtensorMap* map, const void* ptr, int rows, int K, int ld,
 }
 
 template <int EPI>
-static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcArgs& a, cudaStream_t stream) {
+static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcArgs& a0, int sm_count, cudaStream_t stream) {
   const size_t smem = static_cast<size_t>(kStages) * (kStageBytesA + kStageBytesB) + sizeof(TcShared) + 1024;
   static bool attr = false;
   if (!attr) {
@@ -324,7 +379,11 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcArgs&
     attr = true;
   }
   const int tile_n = (EPI == kTcSwiglu) ? kBN / 2 : kBN;
-  dim3 grid((a.N + tile_n - 1) / tile_n, (a.M + kBM - 1) / kBM);
+  TcArgs a = a0;
+  a.tiles_n = (a.N + tile_n - 1) / tile_n;
+  a.tiles_m = (a.M + kBM - 1) / kBM;
+  const int tiles = a.tiles_m * a.tiles_n;
+  dim3 grid(tiles < sm_count ? tiles : sm_count);
   launch_kernel(gemm_tc_kernel<EPI>, grid, dim3(kTcThreads), smem, stream, ma, mb, a);
   return static_cast<int>(cudaGetLastError());
 }
@@ -340,7 +399,7 @@ extern "C" {
 // bfloat16 with K a multiple of 8 and 16-byte aligned rows.  status: device int, bit 0 is set if a
 // wait inside the kernel ran out.  Returns cudaErrorInvalidValue for shapes it does not take.
 int rl_gemm_tc(const void* x, int ldx, const void* w, void* y, int ldy, int epilogue, int M, int N, int K,
-               int* status, cudaStream_t stream) {
+               int* status, int sm_count, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K % 8 != 0 || ldx % 8 != 0 || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15))
     return static_cast<int>(cudaErrorInvalidValue);
@@ -357,10 +416,10 @@ int rl_gemm_tc(const void* x, int ldx, const void* w, void* y, int ldy, int epil
   a.n_up = N;
   a.status = status;
   switch (epilogue) {
-    case kTcBf16: return launch_tc<kTcBf16>(ma, mb, a, stream);
-    case kTcF32: return launch_tc<kTcF32>(ma, mb, a, stream);
-    case kTcAddResidual: return launch_tc<kTcAddResidual>(ma, mb, a, stream);
-    case kTcSwiglu: return launch_tc<kTcSwiglu>(ma, mb, a, stream);
+    case kTcBf16: return launch_tc<kTcBf16>(ma, mb, a, sm_count, stream);
+    case kTcF32: return launch_tc<kTcF32>(ma, mb, a, sm_count, stream);
+    case kTcAddResidual: return launch_tc<kTcAddResidual>(ma, mb, a, sm_count, stream);
+    case kTcSwiglu: return launch_tc<kTcSwiglu>(ma, mb, a, sm_count, stream);
   }
   return static_cast<int>(cudaErrorInvalidValue);
 }

@@ -240,7 +240,7 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, epilogue: int = E
     Epilogues as gemm_skinny's."""
     _need_cuda(x, w, y)
     f = _fn(_lib("gemm_tc", "gemm_tc.cu"), "rl_gemm_tc",
-            [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+            [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p])
     M, K = x.shape
     N = w.shape[0] // 2 if epilogue == EPI_SWIGLU else w.shape[0]
     want = {EPI_BF16: torch.bfloat16, EPI_F32: torch.float32, EPI_ADD_RESIDUAL: torch.float32,
@@ -248,7 +248,7 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, epilogue: int = E
     if w.shape[1] != K or y.dtype != want or y.shape[1] != N or y.stride(1) != 1 or not gemm_tc_ok(x, w):
         raise KernelError(f"gemm_tc: shapes x{tuple(x.shape)} w{tuple(w.shape)} y{tuple(y.shape)} {y.dtype}")
     _check(f(_ptr(x), x.stride(0), _ptr(w), _ptr(y), y.stride(0), epilogue, M, N, K, _ptr(tc_status(x.device)),
-             _stream()), "gemm_tc")
+             sm_count(x.device), _stream()), "gemm_tc")
 
 # ------------------------------------------------------------------- attention
 

@@ -436,3 +436,51 @@ def test_gemm_skinny_refuses_what_it_cannot_do():
     with pytest.raises(kernels.KernelError):
         kernels.gemm_skinny(w, torch.zeros(4, 32, device=DEV), kernels.EPI_BF16, 4,
                             x=torch.zeros(4, 64, device=DEV, dtype=torch.bfloat16))
+
+
+TC_SHAPES = [(128, 128, 64), (17, 331, 200), (256, 384, 512), (130, 200, 72), (2048, 3072, 2048), (300, 1000, 384),
+             (1, 128, 8), (640, 2048, 8192)]
+
+
+@pytest.mark.parametrize("M,N,K", TC_SHAPES)
+def test_gemm_tc_epilogues(M, N, K):
+    """The tcgen05 / TMEM / TMA product against float64, every epilogue, edge tiles in M, N and K."""
+    g = torch.Generator(device="cuda").manual_seed(M + N + K)
+    x = torch.randn(M + 2, K, device=DEV, generator=g).to(torch.bfloat16)[:M]
+    w = (torch.randn(2 * N, K, device=DEV, generator=g) * 0.05).to(torch.bfloat16)
+    ref = x.double() @ w.double().T
+    status = kernels.tc_status(x.device)
+    y = torch.full((M, 2 * N), float("nan"), device=DEV, dtype=torch.bfloat16)
+    kernels.gemm_tc(x, w, y, kernels.EPI_BF16)
+    close(y, ref, 1.2e-2)
+    yf = torch.full((M, 2 * N), float("nan"), device=DEV)
+    kernels.gemm_tc(x, w, yf, kernels.EPI_F32)
+    close(yf, ref, 2e-5)
+    res = torch.randn(M, 2 * N, device=DEV, generator=g)
+    want = res.double() + ref.to(torch.bfloat16).double()
+    kernels.gemm_tc(x, w, res, kernels.EPI_ADD_RESIDUAL)
+    close(res, want, 1e-2)
+    act = torch.full((M, N), float("nan"), device=DEV, dtype=torch.bfloat16)
+    kernels.gemm_tc(x, w, act, kernels.EPI_SWIGLU)
+    P.STORE_DTYPE = torch.bfloat16
+    try:
+        want_act = P.swiglu(P.stored(ref[:, :N].cpu()), P.stored(ref[:, N:].cpu()))
+    finally:
+        P.STORE_DTYPE = None
+    close(act, want_act, 2e-2)
+    y2 = torch.empty(M, 2 * N, device=DEV)
+    kernels.gemm_tc(x, w, y2, kernels.EPI_F32)
+    assert torch.equal(y2, yf)                       # the same bits on every run
+    if M > 1:                                        # and a row does not depend on the rows beside it
+        y1 = torch.empty(1, 2 * N, device=DEV)
+        kernels.gemm_tc(x[M // 2:M // 2 + 1], w, y1, kernels.EPI_F32)
+        assert torch.equal(y1[0], yf[M // 2])
+    assert int(status.item()) == 0                   # no wait inside the kernel ran out
+
+
+def test_gemm_tc_refuses_what_it_cannot_do():
+    x = torch.zeros(4, 20, device=DEV, dtype=torch.bfloat16)
+    w = torch.zeros(32, 20, device=DEV, dtype=torch.bfloat16)
+    assert not kernels.gemm_tc_ok(x, w)
+    with pytest.raises(kernels.KernelError):
+        kernels.gemm_tc(x, w, torch.zeros(4, 32, device=DEV, dtype=torch.bfloat16))
