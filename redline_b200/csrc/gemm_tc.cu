@@ -2,7 +2,7 @@
 // fifth-generation tensor cores: tcgen05.mma with the accumulator in tensor memory (TMEM),
 // operands brought into shared memory by TMA (cp.async.bulk.tensor, 128-byte swizzle).
 //
-// A CTA computes 128 x 128 tiles of y, one after another (persistent: one CTA per SM); the
+// A CTA computes 128 x 256 (or 128 x 128) tiles of y, one after another (persistent: one CTA per SM); the
 // epilogue of a tile overlaps the MMAs of the next.  Warp roles:
 //   warp 0     producer: one lane issues the TMA loads of the A (x) and B (W) tiles of every
 //              64-wide k block into a ring of shared-memory stages and arms the stage's
@@ -26,17 +26,27 @@
 
 namespace rl {
 
-constexpr int kBM = 128, kBN = 128, kBK = 64, kStages = 5, kUmmaK = 16;
-constexpr int kStageBytesA = kBM * kBK * 2, kStageBytesB = kBN * kBK * 2;
+constexpr int kBM = 128, kBK = 64, kUmmaK = 16;
+constexpr int kMaxStages = 6;
+constexpr int kStageBytesA = kBM * kBK * 2;
 constexpr int kTcThreads = 192;          // 6 warps
 constexpr int kSpinLimit = 1 << 22;
-constexpr int kTmemCols = 256;          // two accumulators of 128 columns
+// The tile is 128 x BN with BN = 128 or 256.  Per 64-wide k block the tensor core reads both
+// operand tiles from shared memory: 32 KB per 256 clocks at BN = 128, which is all the shared
+// memory delivers (128 B/clock), 48 KB per 512 clocks at BN = 256: the wider tile is the one that
+// is not bound by shared memory.  Two accumulators live in TMEM: 2 x BN of its 512 columns.
+template <int BN>
+struct TileCfg {
+  static constexpr int kStageBytesB = BN * kBK * 2;
+  static constexpr int kStages = BN == 256 ? 4 : 6;
+  static constexpr int kTmemCols = 2 * BN;
+};
 
 enum TcEpilogue { kTcBf16 = 0, kTcF32 = 1, kTcAddResidual = 2, kTcSwiglu = 3 };
 
 struct TcShared {
-  uint64_t full[kStages];
-  uint64_t empty[kStages];
+  uint64_t full[kMaxStages];
+  uint64_t empty[kMaxStages];
   uint64_t acc_full[2];     // the MMAs of a tile are done: the epilogue may read this TMEM buffer
   uint64_t acc_empty[2];    // the epilogue has read it: the next tile's MMAs may overwrite it
   uint32_t tmem_base;
@@ -150,13 +160,15 @@ struct TcArgs {
 // Persistent: CTA c takes tiles c, c + gridDim.x, ... (features fastest, so CTAs that run together
 // share rows of x and sweep the weights once).  TMEM holds two accumulators: while the epilogue
 // warps drain one tile, the MMAs of the next tile fill the other.
-template <int EPI>
+template <int EPI, int kBN>
 __global__ void __launch_bounds__(kTcThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const TcArgs a) {
   extern __shared__ unsigned char smem_raw[];
   // the stages need 1024-byte alignment for the 128-byte swizzle
   const uint32_t raw = smem_u32(smem_raw);
   unsigned char* base = smem_raw + ((1024u - (raw & 1023u)) & 1023u);
+  constexpr int kStages = TileCfg<kBN>::kStages, kStageBytesB = TileCfg<kBN>::kStageBytesB;
+  constexpr int kTmemCols = TileCfg<kBN>::kTmemCols;
   unsigned char* smem_a = base;
   unsigned char* smem_b = base + kStages * kStageBytesA;
   TcShared* sh = reinterpret_cast<TcShared*>(base + kStages * (kStageBytesA + kStageBytesB));
@@ -189,27 +201,45 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem = sh->tmem_base;
   pdl_launch();
-  pdl_wait();        // x is written by earlier kernels of the step
 
   if (warp == 0) {
     if (lane == 0) {
+      auto load_b = [&](int s, int kb, int n0) {
+        if (EPI == kTcSwiglu) {
+          tma_load_2d(smem_b + s * kStageBytesB, &map_b, &sh->full[s], kb * kBK, n0);
+          tma_load_2d(smem_b + s * kStageBytesB + kStageBytesB / 2, &map_b, &sh->full[s], kb * kBK, a.n_up + n0);
+        } else {
+          tma_load_2d(smem_b + s * kStageBytesB, &map_b, &sh->full[s], kb * kBK, n0);
+        }
+      };
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+      // The weights do not depend on earlier kernels of the step: the first stages' weight tiles are
+      // asked for before the wait on those kernels, the activation tiles after it.
+      const int pre = (blockIdx.x < ntiles) ? min(kStages, nkb) : 0;
+      const int pre_n0 = (blockIdx.x % a.tiles_n) * kTileN;
+      for (int kb = 0; kb < pre; ++kb) {
+        mbar_expect_tx(&sh->full[kb], kStageBytesA + kStageBytesB);
+        load_b(kb, kb, pre_n0);
+      }
+      pdl_wait();        // x is written by earlier kernels of the step
       int it = 0, issued = 0;      // it: k blocks over all of this CTA's tiles
       bool ok = true;
       for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
         const int m0 = (tile / a.tiles_n) * kBM, n0 = (tile % a.tiles_n) * kTileN;
         for (int kb = 0; kb < nkb; ++kb, ++it) {
           const int s = it % kStages;
+          if (it < pre) {          // armed above, the weight tile is on its way
+            tma_load_2d(smem_a + s * kStageBytesA, &map_a, &sh->full[s], kb * kBK, m0);
+            ++issued;
+            continue;
+          }
           const uint32_t parity = ((it / kStages) & 1) ^ 1;        // a fresh barrier passes a wait on parity 1
           ok = mbar_wait(&sh->empty[s], parity, &sh->abort);
           if (!ok) break;
           mbar_expect_tx(&sh->full[s], kStageBytesA + kStageBytesB);
           tma_load_2d(smem_a + s * kStageBytesA, &map_a, &sh->full[s], kb * kBK, m0);
-          if (EPI == kTcSwiglu) {
-            tma_load_2d(smem_b + s * kStageBytesB, &map_b, &sh->full[s], kb * kBK, n0);
-            tma_load_2d(smem_b + s * kStageBytesB + kStageBytesB / 2, &map_b, &sh->full[s], kb * kBK, a.n_up + n0);
-          } else {
-            tma_load_2d(smem_b + s * kStageBytesB, &map_b, &sh->full[s], kb * kBK, n0);
-          }
+          load_b(s, kb, n0);
           ++issued;
         }
       }
@@ -254,6 +284,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     // epilogue warps 2..5: warp w may touch TMEM lanes 32 * (w % 4) .. + 32
     const int q = warp & 3;
     int t = 0;
+    pdl_wait();        // y (or the residual stream) may still be in use by earlier kernels
     for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++t) {
       const int buf = t & 1;
       const int m0 = (tile / a.tiles_n) * kBM, n0 = (tile % a.tiles_n) * kTileN;
@@ -356,7 +387,7 @@ static EncodeTiledFn encode_fn() {
 }
 
 // A [rows, K] bfloat16 matrix with row pitch ld (elements), tiles of box_rows x 64, 128-byte swizzle.
-static bool make_map(CUtensorMap* map, const void* ptr, int rows, int K, int ld, int box_rows) {
+static bool make_map(CUtensorMap* map, const void* ptr, int rows, int K, int ld, int box_rows) {   // box_rows <= 256
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
   const cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows)};
@@ -368,24 +399,32 @@ static bool make_map(CUtensorMap* map, const void* ptr, int rows, int K, int ld,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int EPI>
+template <int EPI, int BN>
 static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcArgs& a0, int sm_count, cudaStream_t stream) {
-  const size_t smem = static_cast<size_t>(kStages) * (kStageBytesA + kStageBytesB) + sizeof(TcShared) + 1024;
+  using Cfg = TileCfg<BN>;
+  const size_t smem = static_cast<size_t>(Cfg::kStages) * (kStageBytesA + Cfg::kStageBytesB) + sizeof(TcShared) + 1024;
   static bool attr = false;
   if (!attr) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<EPI, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(smem));
     if (e != cudaSuccess) return static_cast<int>(e);
     attr = true;
   }
-  const int tile_n = (EPI == kTcSwiglu) ? kBN / 2 : kBN;
+  const int tile_n = (EPI == kTcSwiglu) ? BN / 2 : BN;
   TcArgs a = a0;
   a.tiles_n = (a.N + tile_n - 1) / tile_n;
   a.tiles_m = (a.M + kBM - 1) / kBM;
   const int tiles = a.tiles_m * a.tiles_n;
   dim3 grid(tiles < sm_count ? tiles : sm_count);
-  launch_kernel(gemm_tc_kernel<EPI>, grid, dim3(kTcThreads), smem, stream, ma, mb, a);
+  launch_kernel(gemm_tc_kernel<EPI, BN>, grid, dim3(kTcThreads), smem, stream, ma, mb, a);
   return static_cast<int>(cudaGetLastError());
+}
+
+// 256-wide tiles unless they would leave most SMs without a tile.
+static int choose_bn(int M, int N, int epilogue, int sm_count) {
+  const int tile_n = epilogue == kTcSwiglu ? 128 : 256;
+  const int tiles = ((M + kBM - 1) / kBM) * ((N + tile_n - 1) / tile_n);
+  return tiles * 10 >= sm_count * 8 ? 256 : 128;
 }
 
 }  // namespace rl
@@ -397,16 +436,19 @@ extern "C" {
 // epilogue: 0 bf16 store, 1 float32 store, 2 residual (float32) += product, 3 SiLU-gated product
 // (w holds N gate rows then N up rows; y is [M, N] bfloat16).  x [M, K] and w [N or 2N, K] are
 // bfloat16 with K a multiple of 8 and 16-byte aligned rows.  status: device int, bit 0 is set if a
-// wait inside the kernel ran out.  Returns cudaErrorInvalidValue for shapes it does not take.
+// wait inside the kernel ran out.  force_bn: 0 = choose the tile width, 128 or 256 = use that.
+// Returns cudaErrorInvalidValue for shapes it does not take.
 int rl_gemm_tc(const void* x, int ldx, const void* w, void* y, int ldy, int epilogue, int M, int N, int K,
-               int* status, int sm_count, cudaStream_t stream) {
+               int* status, int sm_count, int force_bn, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K % 8 != 0 || ldx % 8 != 0 || (reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15))
     return static_cast<int>(cudaErrorInvalidValue);
   CUtensorMap ma, mb;
   const bool gated = epilogue == kTcSwiglu;
+  const int bn = force_bn > 0 ? force_bn : choose_bn(M, N, epilogue, sm_count);
+  if (bn != 128 && bn != 256) return static_cast<int>(cudaErrorInvalidValue);
   if (!make_map(&ma, x, M, K, ldx, kBM)) return static_cast<int>(cudaErrorNotSupported);
-  if (!make_map(&mb, w, gated ? 2 * N : N, K, K, gated ? kBN / 2 : kBN)) return static_cast<int>(cudaErrorNotSupported);
+  if (!make_map(&mb, w, gated ? 2 * N : N, K, K, gated ? bn / 2 : bn)) return static_cast<int>(cudaErrorNotSupported);
   TcArgs a;
   a.y = y;
   a.M = M;
@@ -415,12 +457,16 @@ int rl_gemm_tc(const void* x, int ldx, const void* w, void* y, int ldy, int epil
   a.ldy = ldy;
   a.n_up = N;
   a.status = status;
+#define RL_TC_CASE(E)                                                                   \
+  case E:                                                                               \
+    return bn == 256 ? launch_tc<E, 256>(ma, mb, a, sm_count, stream) : launch_tc<E, 128>(ma, mb, a, sm_count, stream)
   switch (epilogue) {
-    case kTcBf16: return launch_tc<kTcBf16>(ma, mb, a, sm_count, stream);
-    case kTcF32: return launch_tc<kTcF32>(ma, mb, a, sm_count, stream);
-    case kTcAddResidual: return launch_tc<kTcAddResidual>(ma, mb, a, sm_count, stream);
-    case kTcSwiglu: return launch_tc<kTcSwiglu>(ma, mb, a, sm_count, stream);
+    RL_TC_CASE(kTcBf16);
+    RL_TC_CASE(kTcF32);
+    RL_TC_CASE(kTcAddResidual);
+    RL_TC_CASE(kTcSwiglu);
   }
+#undef RL_TC_CASE
   return static_cast<int>(cudaErrorInvalidValue);
 }
 

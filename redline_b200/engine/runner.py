@@ -177,9 +177,14 @@ class ModelRunner:
     def check_status(self) -> None:
         """Raises if a kernel flagged bad input since the last check (synchronises)."""
         code = int(self.builder.status.item())
-        if code:
+        tc = kernels.tc_status(self.device)
+        tc_code = int(tc.item())
+        if code or tc_code:
             self.builder.status.zero_()
+            tc.zero_()
             what = [m for bit, m in STATUS_MESSAGES.items() if code & bit]
+            if tc_code:
+                what.append("a wait inside the tcgen05 matrix product that ran out")
             raise EngineError("a kernel met " + " and ".join(what))
 
     def memory_report(self) -> Dict[str, int]:

@@ -234,13 +234,13 @@ def gemm_tc_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
             and x.stride(1) == 1 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-def gemm_tc(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, epilogue: int = EPI_BF16) -> None:
+def gemm_tc(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, epilogue: int = EPI_BF16, tile_n: int = 0) -> None:
     """y = epilogue(x @ w^T) with tcgen05 tensor cores, TMEM accumulators and TMA loads
     (csrc/gemm_tc.cu): bfloat16 x [M, K], w [N, K] (EPI_SWIGLU: [2 N, K], gate rows then up rows).
-    Epilogues as gemm_skinny's."""
+    Epilogues as gemm_skinny's.  tile_n: 0 lets the kernel choose its tile width, 128 or 256 forces it."""
     _need_cuda(x, w, y)
     f = _fn(_lib("gemm_tc", "gemm_tc.cu"), "rl_gemm_tc",
-            [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p])
+            [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p])
     M, K = x.shape
     N = w.shape[0] // 2 if epilogue == EPI_SWIGLU else w.shape[0]
     want = {EPI_BF16: torch.bfloat16, EPI_F32: torch.float32, EPI_ADD_RESIDUAL: torch.float32,
@@ -248,7 +248,7 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, epilogue: int = E
     if w.shape[1] != K or y.dtype != want or y.shape[1] != N or y.stride(1) != 1 or not gemm_tc_ok(x, w):
         raise KernelError(f"gemm_tc: shapes x{tuple(x.shape)} w{tuple(w.shape)} y{tuple(y.shape)} {y.dtype}")
     _check(f(_ptr(x), x.stride(0), _ptr(w), _ptr(y), y.stride(0), epilogue, M, N, K, _ptr(tc_status(x.device)),
-             sm_count(x.device), _stream()), "gemm_tc")
+             sm_count(x.device), tile_n, _stream()), "gemm_tc")
 
 # ------------------------------------------------------------------- attention
 

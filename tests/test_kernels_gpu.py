@@ -442,8 +442,9 @@ TC_SHAPES = [(128, 128, 64), (17, 331, 200), (256, 384, 512), (130, 200, 72), (2
              (1, 128, 8), (640, 2048, 8192)]
 
 
+@pytest.mark.parametrize("tile_n", [128, 256])
 @pytest.mark.parametrize("M,N,K", TC_SHAPES)
-def test_gemm_tc_epilogues(M, N, K):
+def test_gemm_tc_epilogues(M, N, K, tile_n):
     """The tcgen05 / TMEM / TMA product against float64, every epilogue, edge tiles in M, N and K."""
     g = torch.Generator(device="cuda").manual_seed(M + N + K)
     x = torch.randn(M + 2, K, device=DEV, generator=g).to(torch.bfloat16)[:M]
@@ -451,17 +452,17 @@ def test_gemm_tc_epilogues(M, N, K):
     ref = x.double() @ w.double().T
     status = kernels.tc_status(x.device)
     y = torch.full((M, 2 * N), float("nan"), device=DEV, dtype=torch.bfloat16)
-    kernels.gemm_tc(x, w, y, kernels.EPI_BF16)
+    kernels.gemm_tc(x, w, y, kernels.EPI_BF16, tile_n)
     close(y, ref, 1.2e-2)
     yf = torch.full((M, 2 * N), float("nan"), device=DEV)
-    kernels.gemm_tc(x, w, yf, kernels.EPI_F32)
+    kernels.gemm_tc(x, w, yf, kernels.EPI_F32, tile_n)
     close(yf, ref, 2e-5)
     res = torch.randn(M, 2 * N, device=DEV, generator=g)
     want = res.double() + ref.to(torch.bfloat16).double()
-    kernels.gemm_tc(x, w, res, kernels.EPI_ADD_RESIDUAL)
+    kernels.gemm_tc(x, w, res, kernels.EPI_ADD_RESIDUAL, tile_n)
     close(res, want, 1e-2)
     act = torch.full((M, N), float("nan"), device=DEV, dtype=torch.bfloat16)
-    kernels.gemm_tc(x, w, act, kernels.EPI_SWIGLU)
+    kernels.gemm_tc(x, w, act, kernels.EPI_SWIGLU, tile_n)
     P.STORE_DTYPE = torch.bfloat16
     try:
         want_act = P.swiglu(P.stored(ref[:, :N].cpu()), P.stored(ref[:, N:].cpu()))
@@ -469,11 +470,11 @@ def test_gemm_tc_epilogues(M, N, K):
         P.STORE_DTYPE = None
     close(act, want_act, 2e-2)
     y2 = torch.empty(M, 2 * N, device=DEV)
-    kernels.gemm_tc(x, w, y2, kernels.EPI_F32)
+    kernels.gemm_tc(x, w, y2, kernels.EPI_F32, tile_n)
     assert torch.equal(y2, yf)                       # the same bits on every run
     if M > 1:                                        # and a row does not depend on the rows beside it
         y1 = torch.empty(1, 2 * N, device=DEV)
-        kernels.gemm_tc(x[M // 2:M // 2 + 1], w, y1, kernels.EPI_F32)
+        kernels.gemm_tc(x[M // 2:M // 2 + 1], w, y1, kernels.EPI_F32, tile_n)
         assert torch.equal(y1[0], yf[M // 2])
     assert int(status.item()) == 0                   # no wait inside the kernel ran out
 
