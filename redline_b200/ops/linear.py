@@ -43,7 +43,9 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         raise kernels.KernelError("linear runs on CUDA tensors only; there is no CPU fallback")
     if x.shape[0] == 0:
         return out
-    if kernels.skinny_ok(x.shape[0], w, x.dtype) and out.stride(1) == 1 and x.stride(0) % 8 == 0 and x.stride(1) == 1:
+    # (a very tall matrix, the head over a large vocabulary, runs at the bandwidth limit in the library)
+    if (kernels.skinny_ok(x.shape[0], w, x.dtype) and w.shape[0] <= 32768 and out.stride(1) == 1
+            and x.stride(0) % 8 == 0 and x.stride(1) == 1):
         kernels.gemm_skinny(w, out, kernels.EPI_BF16 if out.dtype == torch.bfloat16 else kernels.EPI_F32,
                             x.shape[0], x=x)
         return out
