@@ -197,7 +197,7 @@ def main() -> int:
         if name == "attn_decode":
             p.add_argument("--batch", type=int, default=8)
             p.add_argument("--ctx", type=int, default=4096)
-            p.add_argument("--impl", type=int, default=0, help="0 auto, 1 CUDA cores, 2 tensor cores")
+            p.add_argument("--impl", type=int, default=0, help="0 auto, 1 CUDA cores, 2 tensor cores (3 for attn_decode: the streaming kernel)")
         if name == "attn_prefill":
             p.add_argument("--tokens", type=int, default=2048)
         if name == "gemm_tc":

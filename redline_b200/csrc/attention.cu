@@ -505,6 +505,19 @@ decode_attn_mma_kernel(const DecodeArgs<bf16> a) {
     a.out[static_cast<size_t>(tok) * a.out_stride + head * kD + d] = __float2bfloat16_rn(num / sm_w[r][kMaxMergeParts]);
   }
 }
+// 16-byte asynchronous copies into shared memory (zero-filled when pred is false)
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool pred) {
+  const uint32_t s = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+  const int bytes = pred ? 16 : 0;   // src-size 0: the 16 bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+}  // namespace rl
+#include "decode_stream.cuh"
+namespace rl {
 #endif  // head size 64 or 128
 
 // ------------------------------------------------------------------ prefill
@@ -648,15 +661,6 @@ prefill_attn_kernel(const PrefillArgs<T> a) {
 // and no transposes are needed); a 16-byte-chunk XOR swizzle keeps those reads free of
 // bank conflicts.
 #ifdef RL_HAVE_MMA_DECODE
-
-__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool pred) {
-  const uint32_t s = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
-  const int bytes = pred ? 16 : 0;   // src-size 0: the 16 bytes are zero-filled
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(bytes));
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
 
 constexpr int kMQ = 64, kMK = 64;
 
@@ -885,6 +889,44 @@ int launch_decode(const void* q, int q_stride, const void* kc, const void* vc, c
   dim3 grid(max_parts, hkv, nitems);
 #ifdef RL_HAVE_MMA_DECODE
   if constexpr (sizeof(T) == 2) {
+    // streaming kernel: additionally page sizes that divide a partition and 16-byte aligned rows
+    const bool aligned = q_stride % 8 == 0 && out_stride % 8 == 0 &&
+                         ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(out) |
+                           reinterpret_cast<uintptr_t>(kc) | reinterpret_cast<uintptr_t>(vc) |
+                           reinterpret_cast<uintptr_t>(part_o)) & 15) == 0;
+    // (with few units the one-partition kernel, four warps to a partition, has the shorter critical path)
+    static const long long min_units = [] {
+      const char* e = std::getenv("REDLINE_STREAM_MIN_UNITS");     // a tuning knob
+      return e ? std::atoll(e) : static_cast<long long>(kStreamMinUnits);
+    }();
+    const bool many = static_cast<long long>(nitems) * hkv * max_parts >= min_units;
+    if ((impl == 3 || (impl == 0 && many)) && hq / hkv <= 16 && page_size >= 16 && kPart % page_size == 0 &&
+        counters != nullptr && max_parts <= kMaxMergeParts && nitems <= kStreamMaxItems && aligned) {
+      static int sms = 0;
+      static bool sattr = false;
+      if (!sattr) {
+        int dev = 0;
+        cudaError_t e = cudaGetDevice(&dev);
+        if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (e == cudaSuccess)
+          e = cudaFuncSetAttribute(decode_attn_stream_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   static_cast<int>(kStreamSmem));
+        if (e == cudaSuccess)
+          e = cudaFuncSetAttribute(decode_attn_stream_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   static_cast<int>(kStreamSmem));
+        if (e != cudaSuccess) return static_cast<int>(e);
+        sattr = true;
+      }
+      // no more CTAs than the launch can have units
+      const long long most = static_cast<long long>(nitems) * hkv * max_parts;
+      const int ctas = static_cast<int>(most < sms ? most : sms);
+      if (hq / hkv > 8)
+        launch_kernel(decode_attn_stream_kernel<true>, dim3(ctas), dim3(kStreamThreads), kStreamSmem, stream, a, nitems);
+      else
+        launch_kernel(decode_attn_stream_kernel<false>, dim3(ctas), dim3(kStreamThreads), kStreamSmem, stream, a, nitems);
+      return static_cast<int>(cudaGetLastError());
+    }
+    if (impl == 3) return static_cast<int>(cudaErrorInvalidValue);
     // tensor-core kernel: groups of up to 16 heads, pages that hold whole 16-key steps
     if (impl != 1 && hq / hkv <= 16 && page_size % 16 == 0 && counters != nullptr && max_parts <= kMaxMergeParts) {
       launch_kernel(decode_attn_mma_kernel, dim3(grid), dim3(128), 0, stream, a);
@@ -892,7 +934,7 @@ int launch_decode(const void* q, int q_stride, const void* kc, const void* vc, c
     }
   }
 #endif
-  if (impl == 2) return static_cast<int>(cudaErrorInvalidValue);
+  if (impl == 2 || impl == 3) return static_cast<int>(cudaErrorInvalidValue);
   launch_kernel(decode_attn_kernel<T>, dim3(grid), dim3(kDecThreads), 0, stream, a);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return static_cast<int>(e);
@@ -970,8 +1012,10 @@ int rl_attn_tile_rows() { return 2 * kBQ; }
 // max_parts = ceil(longest context this launch may see / 128); the grid has that many
 // partitions per item and CTAs past an item's context return at once.
 // counters: int32 [nitems * hkv], zero before the first launch (the kernel leaves them zero).
-// impl: 0 = the tensor-core kernel where it applies (bfloat16, head size 64 or 128,
-// at most 16 heads per group), 1 = the CUDA-core kernel, 2 = the tensor-core kernel or an error.
+// impl: 0 = the best kernel that applies: the streaming tensor-core kernel (bfloat16, head size
+// 64 or 128, at most 16 heads per group, pages of 16 to 128 keys, at most 512 items), else the
+// one-partition-per-CTA tensor-core kernel, else the CUDA-core kernel; 1 = the CUDA-core kernel;
+// 2 = the one-partition-per-CTA tensor-core kernel or an error; 3 = the streaming kernel or an error.
 int rl_attn_decode(int dtype, const void* q, int q_stride, const void* kc, const void* vc,
                    const int32_t* bt, int max_blocks, const int32_t* items, float* part_o,
                    float* part_ml, int max_parts, int* counters, void* out, int out_stride, int nitems,

@@ -20,9 +20,7 @@
 // shared memory, all roles leave their loops, outstanding loads are waited for (again
 // bounded), TMEM is freed, and bit 0 of *status is set for the host to read.  The kernel
 // never traps and never spins without a limit.
-#include <cuda.h>
-
-#include "common.cuh"
+#include "tma.cuh"
 
 namespace rl {
 
@@ -30,7 +28,6 @@ constexpr int kBM = 128, kBK = 64, kUmmaK = 16;
 constexpr int kMaxStages = 6;
 constexpr int kStageBytesA = kBM * kBK * 2;
 constexpr int kTcThreads = 192;          // 6 warps
-constexpr int kSpinLimit = 1 << 22;
 // The tile is 128 x BN with BN = 128 or 256.  Per 64-wide k block the tensor core reads both
 // operand tiles from shared memory: 32 KB per 256 clocks at BN = 128, which is all the shared
 // memory delivers (128 B/clock), 48 KB per 512 clocks at BN = 256: the wider tile is the one that
@@ -52,48 +49,6 @@ struct TcShared {
   uint32_t tmem_base;
   volatile int abort;
 };
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-      "selp.u32 %0, 1, 0, p;\n"
-      "}\n"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Waits for the phase with the given parity; false if the CTA is aborting or the limit ran out.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort) {
-  for (int i = 0; i < kSpinLimit; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if (*abort) return false;
-  }
-  *abort = 1;
-  return false;
-}
-
-__device__ __forceinline__ void tma_load_2d(void* smem, const CUtensorMap* map, uint64_t* bar, int x, int y) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(smem_u32(smem)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
-      : "memory");
-}
 
 // Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 bfloat16),
 // 128-byte swizzled as TMA leaves it: 8-row groups are 1024 bytes apart.
@@ -369,22 +324,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 }
 
 // ---------------------------------------------------------------------------- host side
-
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = [] {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
-        q != cudaDriverEntryPointSuccess)
-      p = nullptr;
-    return reinterpret_cast<EncodeTiledFn>(p);
-  }();
-  return fn;
-}
 
 // A [rows, K] bfloat16 matrix with row pitch ld (elements), tiles of box_rows x 64, 128-byte swizzle.
 static bool make_map(CUtensorMap* map, const void* ptr, int rows, int K, int ld, int box_rows) {   // box_rows <= 256

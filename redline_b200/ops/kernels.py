@@ -275,7 +275,9 @@ def attn_decode(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcache: to
 
     items     int32 [nitems, 4]: (token index of the query, sequence index, context length, 0)
     counters  int32 [nitems * num_kv_heads], zero (the tensor-core kernel needs and keeps them zero)
-    impl      0: tensor-core kernel where it applies, else CUDA-core; 1: CUDA-core; 2: tensor-core or error
+    impl      0: the best kernel that applies (streaming tensor-core for launches with many partitions,
+              one-partition tensor-core, CUDA-core); 1: CUDA-core; 2: one-partition tensor-core or error;
+              3: streaming tensor-core or error
     """
     _need_cuda(q, kcache, out)
     f = _fn(_attn(head_dim), "rl_attn_decode",

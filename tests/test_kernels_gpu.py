@@ -265,6 +265,73 @@ def test_attention_decode_tensor_core_kernel(Hq, Hkv, D, page_size):
                       decode_impl=2)
 
 
+@pytest.mark.parametrize("Hq,Hkv,D", [(4, 2, 64), (32, 8, 64), (3, 1, 128), (16, 1, 64), (24, 8, 128), (7, 7, 64)])
+@pytest.mark.parametrize("page_size", [16, 32, 64, 128])
+def test_attention_decode_streaming_kernel(Hq, Hkv, D, page_size):
+    """impl 3 insists on the streaming kernel (persistent CTAs, every warp with its own two-stage ring
+    of 32-key sub-blocks): the same cases as the one-partition kernel and a page size of a whole
+    partition."""
+    run_attention("bfloat16", Hq, Hkv, D, [0, 31, 32, 33, 63, 64, 65], [1] * 7, page_size=page_size, seed=11, decode_impl=3)
+    run_attention("bfloat16", Hq, Hkv, D, [255, 256, 300, 511, 512, 1030], [1] * 6, page_size=page_size, seed=12, decode_impl=3)
+    for window in (1, 20, 100, 300):
+        run_attention("bfloat16", Hq, Hkv, D, [5, 99, 290, 700], [1] * 4, page_size=page_size, window=window, seed=13,
+                      decode_impl=3)
+    assert int(kernels.tc_status(torch.device(DEV)).item()) == 0
+
+
+def decode_only_case(Hq, Hkv, D, lens, page_size, window, impl, seed):
+    """Decode attention straight on a random cache (no rotation, no cache write): the reference
+    gathers each item's keys and does the softmax in float64."""
+    g = torch.Generator().manual_seed(seed)
+    B = len(lens)
+    blocks = [(n + page_size - 1) // page_size for n in lens]
+    npages = sum(blocks) + 1
+    perm = (torch.randperm(npages - 1, generator=g) + 1).tolist()
+    bt = torch.zeros(B, max(blocks) + 1, dtype=torch.int32)
+    it = iter(perm)
+    for b in range(B):
+        for i in range(blocks[b]):
+            bt[b, i] = next(it)
+    kc = torch.randn(npages, Hkv, page_size, D, generator=g).to(torch.bfloat16).to(DEV)
+    vc = torch.randn(npages, Hkv, page_size, D, generator=g).to(torch.bfloat16).to(DEV)
+    q = torch.randn(B, Hq * D, generator=g).to(torch.bfloat16).to(DEV)
+    scale = 1.0 / math.sqrt(D)
+    parts = (max(lens) + kernels.DECODE_PARTITION - 1) // kernels.DECODE_PARTITION
+    po = torch.full((B * Hq * parts * D,), float("nan"), device=DEV)
+    pm = torch.full((B * Hq * parts * 2,), float("nan"), device=DEV)
+    items = torch.tensor([[b, b, lens[b], 0] for b in range(B)], dtype=torch.int32, device=DEV)
+    counters = torch.zeros(B * Hkv, dtype=torch.int32, device=DEV)
+    out = torch.full((B, Hq * D), float("nan"), device=DEV, dtype=torch.bfloat16)
+    btd = bt.to(DEV)
+    for _ in range(2):       # twice: the counters and the ring are left ready for the next launch
+        kernels.attn_decode(q, q.shape[1], kc, vc, btd, items, po, pm, parts, counters, out, B, Hq, Hkv, D,
+                            page_size, window, scale, impl)
+    assert int(counters.abs().max()) == 0
+    G = Hq // Hkv
+    for b in range(B):
+        n = lens[b]
+        lo = max(0, n - window) if window > 0 else 0
+        pages = btd[b, :blocks[b]].long()
+        k = kc[pages].permute(1, 0, 2, 3).reshape(Hkv, -1, D)[:, lo:n].double()     # [Hkv, keys, D]
+        v = vc[pages].permute(1, 0, 2, 3).reshape(Hkv, -1, D)[:, lo:n].double()
+        qb = q[b].double().reshape(Hkv, G, D)
+        p = torch.softmax(torch.einsum("hgd,hkd->hgk", qb, k) * scale, dim=-1)
+        want = torch.einsum("hgk,hkd->hgd", p, v).reshape(Hq * D)
+        close(out[b], want, 1.6e-2)
+
+
+def test_attention_decode_streaming_kernel_many_units_per_cta():
+    """Several thousand (item, head, partition) units over at most one CTA per SM: every warp has a run
+    of several partitions, rows of partitions are cut by the ends of runs and merged from their pieces,
+    with contexts of many lengths in one launch."""
+    lens = [2000 + 97 * i for i in range(12)] + [1, 130, 5, 640]
+    decode_only_case(32, 8, 64, lens, 16, 0, 3, seed=31)
+    decode_only_case(32, 8, 64, lens, 64, 1000, 3, seed=32)
+    decode_only_case(16, 8, 128, [1500, 3000, 77, 2047, 2048, 4096, 4097], 32, 0, 3, seed=33)
+    decode_only_case(32, 8, 64, lens, 16, 0, 2, seed=31)
+    assert int(kernels.tc_status(torch.device(DEV)).item()) == 0
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_attention_mixed_launch_and_other_page_sizes(dtype):
     run_attention(dtype, 4, 2, 64, [300, 31, 0, 90], [1, 33, 2, 1], page_size=32, seed=5)
@@ -300,6 +367,8 @@ def test_a_far_key_is_found_among_hundreds(dtype):
                 x[far, (Hq + h) * D:(Hq + h + 1) * D] = unrotate(u, cos[far], sin[far])
         run_attention(dtype, Hq, Hkv, D, [total - 1], [1], seed=9, sharp=sharp)     # decode kernel
         run_attention(dtype, Hq, Hkv, D, [total - 1], [1], seed=9, sharp=sharp, decode_impl=1)
+        if dtype == "bfloat16":
+            run_attention(dtype, Hq, Hkv, D, [total - 1], [1], seed=9, sharp=sharp, decode_impl=2)
         run_attention(dtype, Hq, Hkv, D, [total - 40], [40], seed=9, sharp=sharp)   # prefill kernel
         run_attention(dtype, Hq, Hkv, D, [total - 40], [40], seed=9, sharp=sharp, prefill_impl=1)
 
