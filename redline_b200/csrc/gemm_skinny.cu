@@ -63,16 +63,6 @@ struct WFrag {
   uint4 lo[4], hi[4];
 };
 
-__device__ __forceinline__ void load_wfrag(WFrag& f, const bf16* w_lo, const bf16* w_hi, int k_first, int K) {
-#pragma unroll
-  for (int q = 0; q < 4; ++q) {
-    const int k = k_first + q * 32;
-    const bool ok = k < K;               // K is a multiple of 8: a 16-byte piece is in or out whole
-    f.lo[q] = ok ? ldg_stream(w_lo + k) : make_uint4(0, 0, 0, 0);
-    f.hi[q] = ok ? ldg_stream(w_hi + k) : make_uint4(0, 0, 0, 0);
-  }
-}
-
 // MT: token rows padded to 8 or 16; WARPS: warps per CTA; EPI: epilogue; NORM: fused norm.
 // MT: token rows padded to 8 or 16; WARPS: warps per CTA; KW: warps that split the K of one
 // 16-row weight stream; EPI: epilogue; NORM: fused norm.  The CTA's WARPS / KW groups of warps
@@ -100,9 +90,14 @@ gemm_skinny_kernel(const SkinnyArgs a, int kc) {
   const int stream = grp % STREAMS, tile_in_cta = grp / STREAMS;
   const int nsb = (K + kSB - 1) / kSB;       // super-blocks in K; warp kw takes kw, kw + KW, ...
 
-  // The first weights are asked for before anything else: they do not depend on the
-  // activations, and their latency then hides behind the norm and the staging.
-  WFrag cur, nxt;
+  // The weight stream of a warp is the sequence of its super-blocks over all the tiles of the CTA:
+  // (tile 0: kw, kw + KW, ...), (tile 1: kw, ...), ...  Two super-blocks are held in registers, fa
+  // for the even steps of the sequence and fb for the odd ones; as soon as a 16-byte piece has been
+  // multiplied, the piece in the same place two steps on is asked for into the same registers, so
+  // nearly two super-blocks (8 KB per warp) are in flight all the time.  The first two are asked for
+  // before anything else: they do not depend on the activations, and their latency then hides behind
+  // the wait for the kernels before this one, the norm and the staging.
+  WFrag fa, fb;
   const bf16 *w_lo, *w_hi;
   auto set_rows = [&](int n0) {
     const int r_lo = min(n0 + g, a.N - 1), r_hi = min(n0 + g + 8, a.N - 1);   // clamped; stores are predicated
@@ -110,9 +105,33 @@ gemm_skinny_kernel(const SkinnyArgs a, int kc) {
     w_hi = a.w + static_cast<size_t>(stream * a.N + r_hi) * K;
   };
   const int tile0 = blockIdx.x * a.row_tiles * TPC + tile_in_cta;   // then tile0 + TPC, ... (row_tiles rounds)
+  // the load cursor: round l_rt of the CTA, super-block l_sb; l_ok: there is such a super-block
+  int l_rt = 0, l_sb = kw;
+  bool l_ok = kw < nsb && blockIdx.x * a.row_tiles * TPC * 16 < a.N;
   set_rows(tile0 * 16);
+  auto load_piece = [&](uint4& lo, uint4& hi, int q) {
+    const int k = l_sb * kSB + q * 32 + t * 8;
+    const bool ok = l_ok && k < K;        // K is a multiple of 8: a 16-byte piece is in or out whole
+    lo = ok ? ldg_stream(w_lo + k) : make_uint4(0, 0, 0, 0);
+    hi = ok ? ldg_stream(w_hi + k) : make_uint4(0, 0, 0, 0);
+  };
+  auto load_advance = [&]() {
+    l_sb += KW;
+    if (l_sb >= nsb) {                     // on to the next round of the CTA
+      l_sb = kw;
+      ++l_rt;
+      l_ok = l_ok && l_rt < a.row_tiles && (blockIdx.x * a.row_tiles + l_rt) * TPC * 16 < a.N;
+      if (l_ok) set_rows((tile0 + l_rt * TPC) * 16);
+    }
+  };
   pdl_launch();
-  load_wfrag(cur, w_lo, w_hi, kw * kSB + t * 8, K);
+#pragma unroll
+  for (int q = 0; q < 4; ++q) load_piece(fa.lo[q], fa.hi[q], q);
+  load_advance();
+#pragma unroll
+  for (int q = 0; q < 4; ++q) load_piece(fb.lo[q], fb.hi[q], q);
+  load_advance();
+  int step = 0;       // super-blocks this warp has multiplied
   pdl_wait();   // everything below reads what earlier kernels of the step wrote
 
   if (NORM) {
@@ -136,7 +155,6 @@ gemm_skinny_kernel(const SkinnyArgs a, int kc) {
     const int n0 = (tile0 + rt * TPC) * 16;                           // this warp's tile (may lie past N)
     const int cta_n0 = (blockIdx.x * a.row_tiles + rt) * TPC * 16;   // first feature of the CTA's round
     if (cta_n0 >= a.N) break;
-    const bool more_tiles = (rt + 1 < a.row_tiles) && (cta_n0 + TPC * 16 < a.N);
     float acc[NG][4];
 #pragma unroll
     for (int j = 0; j < NG; ++j)
@@ -185,35 +203,25 @@ gemm_skinny_kernel(const SkinnyArgs a, int kc) {
         *reinterpret_cast<uint4*>(xs + m * lds + c) = v;
       }
       __syncthreads();
-      // ---- the weight stream: warp kw takes super-blocks kw, kw + KW, ... ; the next one is
-      //      in flight while this one is multiplied
+      // ---- the weight stream: warp kw takes super-blocks kw, kw + KW, ...
       const int sb_end = min((k0 + kc) / kSB, nsb);
-      for (int sb = k0 / kSB + kw; sb < sb_end; sb += KW) {
-        const int sbn = sb + KW;
-        if (sbn < nsb) {
-          load_wfrag(nxt, w_lo, w_hi, sbn * kSB + t * 8, K);
-        } else if (more_tiles) {         // this tile's stream is done: start the next round's
-          set_rows(n0 + TPC * 16);
-          load_wfrag(nxt, w_lo, w_hi, kw * kSB + t * 8, K);
-        }
+      for (int sb = k0 / kSB + kw; sb < sb_end; sb += KW, ++step) {
         const int kb = sb * kSB - k0;    // within the staged chunk
+        auto multiply = [&](WFrag& f) {
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
+          for (int q = 0; q < 4; ++q) {
 #pragma unroll
-          for (int j = 0; j < NG; ++j) {
-            const uint4 xv = *reinterpret_cast<const uint4*>(xs + (j * 8 + g) * lds + kb + q * 32 + t * 8);
-            mma_bf16(acc[j], cur.lo[q].x, cur.hi[q].x, cur.lo[q].y, cur.hi[q].y, xv.x, xv.y);
-            mma_bf16(acc[j], cur.lo[q].z, cur.hi[q].z, cur.lo[q].w, cur.hi[q].w, xv.z, xv.w);
+            for (int j = 0; j < NG; ++j) {
+              const uint4 xv = *reinterpret_cast<const uint4*>(xs + (j * 8 + g) * lds + kb + q * 32 + t * 8);
+              mma_bf16(acc[j], f.lo[q].x, f.hi[q].x, f.lo[q].y, f.hi[q].y, xv.x, xv.y);
+              mma_bf16(acc[j], f.lo[q].z, f.hi[q].z, f.lo[q].w, f.hi[q].w, xv.z, xv.w);
+            }
+            load_piece(f.lo[q], f.hi[q], q);     // the same place, two steps on
           }
-        }
-        cur = nxt;
+          load_advance();
+        };
+        if (step & 1) multiply(fb); else multiply(fa);
       }
-    }
-    // a warp that had no super-block in this tile (K shorter than WARPS super-blocks) still holds the
-    // tile's first fragment in `cur`: fetch the next tile's instead
-    if (kw >= nsb && more_tiles) {
-      set_rows(n0 + TPC * 16);
-      load_wfrag(cur, w_lo, w_hi, kw * kSB + t * 8, K);
     }
     // ---- partial sums of the warps meet in shared memory: red[warp][16][MT]
     __syncthreads();
@@ -265,7 +273,11 @@ int launch_one(const SkinnyArgs& a0, int sm_count, cudaStream_t stream) {
   const int rounds = (tiles + TPC - 1) / TPC;       // CTA-rounds of TPC tiles
   // at most about two CTAs per SM, all resident at once: a second, nearly empty wave would cost
   // as much as the first
-  int rt = (rounds + 2 * sm_count - 1) / (2 * sm_count);
+  static const int per_sm = [] {
+    const char* e = std::getenv("REDLINE_SKINNY_CTAS_PER_SM");
+    return e ? std::atoi(e) : 2;
+  }();
+  int rt = (rounds + per_sm * sm_count - 1) / (per_sm * sm_count);
   if (rt > 16) rt = 16;
   a.row_tiles = rt;
   const int ctas = (rounds + rt - 1) / rt;
