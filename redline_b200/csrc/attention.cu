@@ -533,7 +533,7 @@ struct PrefillArgs {
   int max_blocks;
   const int32_t* tile_seq;    // [tiles] sequence index
   const int32_t* tile_tok;    // [tiles] first token of the tile (tokens of a tile are consecutive)
-  const int32_t* tile_rows;   // [tiles] rows in use (1..64)
+  const int32_t* tile_rows;   // [tiles] rows in use (1..128)
   const int32_t* positions;   // [tokens]
   T* out;
   int out_stride;
@@ -557,8 +557,8 @@ prefill_attn_kernel(const PrefillArgs<T> a) {
   float* Vs = Ks + kBK * LDQ;        // [32][D]
   float* Ps = Vs + kBK * kD;         // [32][33]
 
-  // the tile list holds tiles of up to 64 rows; this kernel takes them as two halves of 32
-  const int tile = blockIdx.x >> 1, half_tile = blockIdx.x & 1, head = blockIdx.y;
+  // the tile list holds tiles of up to 128 rows; this kernel takes them as four quarters of 32
+  const int tile = blockIdx.x >> 2, half_tile = blockIdx.x & 3, head = blockIdx.y;
   const int seq = a.tile_seq[tile], tok0 = a.tile_tok[tile] + half_tile * kBQ;
   const int rows = min(a.tile_rows[tile] - half_tile * kBQ, kBQ);
   if (rows <= 0) return;
@@ -653,30 +653,47 @@ prefill_attn_kernel(const PrefillArgs<T> a) {
 }
 
 // ------------------------------------------------- prefill on the tensor cores
-// bfloat16, head size 64 or 128: one CTA of four warps per (64-row tile, query head), each
-// warp 16 query rows; keys in tiles of 64, brought from the paged cache into a two-stage
-// shared-memory ring with cp.async; S = Q K^T and O += P V with mma.sync.m16n8k16, online
-// softmax in float32 in the MMA's accumulator layout.  Fragments are read from shared memory
-// in 16-byte pieces with the same index permutations as the decode kernel (so no ldmatrix
-// and no transposes are needed); a 16-byte-chunk XOR swizzle keeps those reads free of
-// bank conflicts.
+// bfloat16, head size 64 or 128.  A tile of the launch has up to 128 query rows.  One CTA of four
+// warps takes 64 MT rows of it for one query head; each warp takes 16 MT consecutive rows, as MT
+// blocks of 16 that share every K and V fragment it reads from shared memory (MT = 1, two CTAs to
+// a tile, is the default: measured at head size 64, MT = 2 needs 250 registers and is no faster).
+// Keys come in tiles of 64 from the paged cache into a two-stage shared-memory ring with
+// cp.async; S = Q K^T and O += P V with mma.sync.m16n8k16, online softmax in float32 in the MMA's
+// accumulator layout (masks only in the tiles that need them).  Fragments are read from shared
+// memory in 16-byte pieces with the same index permutations as the decode kernel (so no ldmatrix
+// and no transposes are needed); a 16-byte-chunk XOR swizzle keeps those reads free of bank
+// conflicts.
 #ifdef RL_HAVE_MMA_DECODE
 
-constexpr int kMQ = 64, kMK = 64;
+constexpr int kMK = 64;                        // keys per tile
+#ifndef RL_PRE_MT
+#define RL_PRE_MT 1
+#endif
+#ifndef RL_PRE_MINB
+#define RL_PRE_MINB 3
+#endif
+constexpr int kPreMT = RL_PRE_MT;     // 16-row blocks per warp
+constexpr int kPreRows = 64 * kPreMT;          // query rows per CTA
+constexpr int kPreTile = 128;                  // query rows per tile of the launch
 
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, RL_PRE_MINB)
 prefill_attn_mma_kernel(const PrefillArgs<bf16> a) {
   pdl_launch();
   pdl_wait();
+  constexpr int MT = kPreMT;
   constexpr int DB = kD / 32, DG = kD / 64, CPR = kD / 8;   // 16-byte chunks per row
   constexpr float kLog2e = 1.4426950408889634f;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* Ks = reinterpret_cast<bf16*>(smem_raw);            // [2][64][D], chunk-swizzled
   bf16* Vs = Ks + 2 * kMK * kD;                            // [2][64][D], chunk-swizzled
 
-  // longest tiles first: a later tile of a sequence attends to more keys
-  const int tile = gridDim.x - 1 - blockIdx.x, head = blockIdx.y;
-  const int seq = a.tile_seq[tile], tok0 = a.tile_tok[tile], rows = a.tile_rows[tile];
+  // longest first: a later part of a sequence attends to more keys
+  constexpr int kSplit = kPreTile / kPreRows;              // CTAs per tile
+  const int cta = gridDim.x - 1 - blockIdx.x, head = blockIdx.y;
+  const int tile = cta / kSplit, row0 = (cta % kSplit) * kPreRows;
+  const int rows = min(a.tile_rows[tile] - row0, kPreRows);
+  if (rows <= 0) return;
+  const int seq = a.tile_seq[tile], tok0 = a.tile_tok[tile] + row0;
   const int kvh = head / (a.hq / a.hkv);
   const int pos0 = a.positions[tok0];
   const int32_t* bt = a.block_table + static_cast<size_t>(seq) * a.max_blocks;
@@ -708,26 +725,32 @@ prefill_attn_mma_kernel(const PrefillArgs<bf16> a) {
   };
 
   load_tile(0, 0);
-  // Q fragments of this warp's 16 rows (rows past the tile are zero)
-  const int r_lo = warp * 16 + g, r_hi = r_lo + 8;
-  uint4 qlo[DB], qhi[DB];
+  // Q fragments of this warp's 16 MT rows (rows past the tile are zero)
+  const int wrow0 = warp * 16 * MT;                    // the warp's first row
+  uint4 qlo[MT][DB], qhi[MT][DB];
 #pragma unroll
-  for (int db = 0; db < DB; ++db) {
-    const bf16* qp = a.q + static_cast<size_t>(tok0) * a.q_stride + head * kD + db * 32 + t * 8;
-    qlo[db] = r_lo < rows ? *reinterpret_cast<const uint4*>(qp + static_cast<size_t>(r_lo) * a.q_stride) : make_uint4(0, 0, 0, 0);
-    qhi[db] = r_hi < rows ? *reinterpret_cast<const uint4*>(qp + static_cast<size_t>(r_hi) * a.q_stride) : make_uint4(0, 0, 0, 0);
+  for (int mt = 0; mt < MT; ++mt) {
+    const int r_lo = wrow0 + mt * 16 + g, r_hi = r_lo + 8;
+#pragma unroll
+    for (int db = 0; db < DB; ++db) {
+      const bf16* qp = a.q + static_cast<size_t>(tok0) * a.q_stride + head * kD + db * 32 + t * 8;
+      qlo[mt][db] = r_lo < rows ? *reinterpret_cast<const uint4*>(qp + static_cast<size_t>(r_lo) * a.q_stride) : make_uint4(0, 0, 0, 0);
+      qhi[mt][db] = r_hi < rows ? *reinterpret_cast<const uint4*>(qp + static_cast<size_t>(r_hi) * a.q_stride) : make_uint4(0, 0, 0, 0);
+    }
   }
-  const int pos_lo = pos0 + r_lo, pos_hi = pos0 + r_hi;
-  const int win_lo = (a.window > 0 && pos_lo + 1 > a.window) ? pos_lo + 1 - a.window : 0;
-  const int win_hi = (a.window > 0 && pos_hi + 1 > a.window) ? pos_hi + 1 - a.window : 0;
-  float o[DG][8][4];
+  float o[MT][DG][8][4];
+  float m_lo[MT], m_hi[MT], l_lo[MT], l_hi[MT];
 #pragma unroll
-  for (int dg = 0; dg < DG; ++dg)
+  for (int mt = 0; mt < MT; ++mt) {
+    m_lo[mt] = m_hi[mt] = -INFINITY;
+    l_lo[mt] = l_hi[mt] = 0.f;
 #pragma unroll
-    for (int j = 0; j < 8; ++j)
+    for (int dg = 0; dg < DG; ++dg)
 #pragma unroll
-      for (int e = 0; e < 4; ++e) o[dg][j][e] = 0.f;
-  float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
+      for (int j = 0; j < 8; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[mt][dg][j][e] = 0.f;
+  }
   const float sc = a.scale * kLog2e;
 
   for (int it = 0; it < ntiles; ++it) {
@@ -743,74 +766,107 @@ prefill_attn_mma_kernel(const PrefillArgs<bf16> a) {
     const bf16* ks = Ks + stage * kMK * kD;
     const bf16* vs = Vs + stage * kMK * kD;
     // a warp whose rows all lie before this tile's keys has nothing to do in it
-    const bool warp_live = (k0 <= pos0 + warp * 16 + 15) && (warp * 16 < rows);
+    const bool warp_live = (k0 <= pos0 + wrow0 + 16 * MT - 1) && (wrow0 < rows);
     if (warp_live) {
-      float s[8][4];
+      // ---- S = Q K^T: every K fragment serves the warp's MT blocks of rows
+      float s[MT][8][4];
 #pragma unroll
       for (int nt = 0; nt < 8; ++nt) {
 #pragma unroll
-        for (int e = 0; e < 4; ++e) s[nt][e] = 0.f;
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) s[mt][nt][e] = 0.f;
         const int key = nt * 8 + g;
 #pragma unroll
         for (int db = 0; db < DB; ++db) {
           const int c = (db * 4 + t) ^ ((key & 1) << 2);
           const uint4 kf = *reinterpret_cast<const uint4*>(ks + key * kD + c * 8);
-          mma_16816(s[nt], qlo[db].x, qhi[db].x, qlo[db].y, qhi[db].y, kf.x, kf.y);
-          mma_16816(s[nt], qlo[db].z, qhi[db].z, qlo[db].w, qhi[db].w, kf.z, kf.w);
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+            mma_16816(s[mt][nt], qlo[mt][db].x, qhi[mt][db].x, qlo[mt][db].y, qhi[mt][db].y, kf.x, kf.y);
+            mma_16816(s[mt][nt], qlo[mt][db].z, qhi[mt][db].z, qlo[mt][db].w, qhi[mt][db].w, kf.z, kf.w);
+          }
         }
       }
-      float mx_lo = -INFINITY, mx_hi = -INFINITY;
+      // ---- online softmax, block by block; m in units of log2 of the scaled scores
 #pragma unroll
-      for (int nt = 0; nt < 8; ++nt)
+      for (int mt = 0; mt < MT; ++mt) {
+        const int b0 = wrow0 + mt * 16;                       // the block's first row
+        const int r_lo = b0 + g, r_hi = r_lo + 8;
+        // only tiles that reach past the first row's position, before the last row's window or past the
+        // tile's rows need the masks
+        const bool masked = (k0 + kMK - 1 > pos0 + b0) || (a.window > 0 && k0 < pos0 + b0 + 16 - a.window) || (b0 + 16 > rows);
+        if (masked) {
+          const int pos_lo = pos0 + r_lo, pos_hi = pos0 + r_hi;
+          const int win_lo = (a.window > 0 && pos_lo + 1 > a.window) ? pos_lo + 1 - a.window : 0;
+          const int win_hi = (a.window > 0 && pos_hi + 1 > a.window) ? pos_hi + 1 - a.window : 0;
 #pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const int kp = k0 + nt * 8 + t * 2 + e;
-          const bool ok_lo = kp <= pos_lo && kp >= win_lo && r_lo < rows;
-          const bool ok_hi = kp <= pos_hi && kp >= win_hi && r_hi < rows;
-          s[nt][e] = ok_lo ? s[nt][e] * sc : -INFINITY;
-          s[nt][2 + e] = ok_hi ? s[nt][2 + e] * sc : -INFINITY;
-          mx_lo = fmaxf(mx_lo, s[nt][e]);
-          mx_hi = fmaxf(mx_hi, s[nt][2 + e]);
+          for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              const int kp = k0 + nt * 8 + t * 2 + e;
+              const bool ok_lo = kp <= pos_lo && kp >= win_lo && r_lo < rows;
+              const bool ok_hi = kp <= pos_hi && kp >= win_hi && r_hi < rows;
+              if (!ok_lo) s[mt][nt][e] = -INFINITY;
+              if (!ok_hi) s[mt][nt][2 + e] = -INFINITY;
+            }
         }
-      mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
-      mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
-      mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
-      mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
-      const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
-      const float mu_lo = mn_lo == -INFINITY ? 0.f : mn_lo, mu_hi = mn_hi == -INFINITY ? 0.f : mn_hi;
-      const float al_lo = exp2f(m_lo - mu_lo), al_hi = exp2f(m_hi - mu_hi);   // exp2(-inf) = 0
-      float ps_lo = 0.f, ps_hi = 0.f;
+        float mx_lo = -INFINITY, mx_hi = -INFINITY;
 #pragma unroll
-      for (int nt = 0; nt < 8; ++nt)
+        for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          s[nt][e] = exp2f(s[nt][e] - mu_lo);
-          s[nt][2 + e] = exp2f(s[nt][2 + e] - mu_hi);
-          ps_lo += s[nt][e];
-          ps_hi += s[nt][2 + e];
+          for (int e = 0; e < 2; ++e) {
+            mx_lo = fmaxf(mx_lo, s[mt][nt][e]);
+            mx_hi = fmaxf(mx_hi, s[mt][nt][2 + e]);
+          }
+        mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+        mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+        mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+        mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+        // a row without a live key so far keeps m = -inf
+        const float mn_lo = fmaxf(m_lo[mt], mx_lo * sc), mn_hi = fmaxf(m_hi[mt], mx_hi * sc);
+        const float mu_lo = mn_lo == -INFINITY ? 0.f : mn_lo, mu_hi = mn_hi == -INFINITY ? 0.f : mn_hi;
+        const float al_lo = ex2_approx(m_lo[mt] - mu_lo), al_hi = ex2_approx(m_hi[mt] - mu_hi);   // 2^(-inf) = 0
+        float ps_lo = 0.f, ps_hi = 0.f;
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) {
+          s[mt][nt][0] = ex2_approx(fmaf(s[mt][nt][0], sc, -mu_lo));
+          s[mt][nt][1] = ex2_approx(fmaf(s[mt][nt][1], sc, -mu_lo));
+          s[mt][nt][2] = ex2_approx(fmaf(s[mt][nt][2], sc, -mu_hi));
+          s[mt][nt][3] = ex2_approx(fmaf(s[mt][nt][3], sc, -mu_hi));
+          ps_lo += s[mt][nt][0] + s[mt][nt][1];
+          ps_hi += s[mt][nt][2] + s[mt][nt][3];
         }
-      ps_lo += __shfl_xor_sync(0xffffffffu, ps_lo, 1);
-      ps_lo += __shfl_xor_sync(0xffffffffu, ps_lo, 2);
-      ps_hi += __shfl_xor_sync(0xffffffffu, ps_hi, 1);
-      ps_hi += __shfl_xor_sync(0xffffffffu, ps_hi, 2);
-      l_lo = l_lo * al_lo + ps_lo;
-      l_hi = l_hi * al_hi + ps_hi;
-      m_lo = mn_lo;
-      m_hi = mn_hi;
+        ps_lo += __shfl_xor_sync(0xffffffffu, ps_lo, 1);
+        ps_lo += __shfl_xor_sync(0xffffffffu, ps_lo, 2);
+        ps_hi += __shfl_xor_sync(0xffffffffu, ps_hi, 1);
+        ps_hi += __shfl_xor_sync(0xffffffffu, ps_hi, 2);
+        l_lo[mt] = l_lo[mt] * al_lo + ps_lo;
+        l_hi[mt] = l_hi[mt] * al_hi + ps_hi;
+        m_lo[mt] = mn_lo;
+        m_hi[mt] = mn_hi;
 #pragma unroll
-      for (int dg = 0; dg < DG; ++dg)
+        for (int dg = 0; dg < DG; ++dg)
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          o[dg][j][0] *= al_lo;
-          o[dg][j][1] *= al_lo;
-          o[dg][j][2] *= al_hi;
-          o[dg][j][3] *= al_hi;
-        }
+          for (int j = 0; j < 8; ++j) {
+            o[mt][dg][j][0] *= al_lo;
+            o[mt][dg][j][1] *= al_lo;
+            o[mt][dg][j][2] *= al_hi;
+            o[mt][dg][j][3] *= al_hi;
+          }
+      }
+      // ---- O += P V: every V fragment serves the warp's MT blocks of rows
 #pragma unroll
       for (int ks16 = 0; ks16 < 4; ++ks16) {
-        const uint32_t p0 = pack_bf16(s[2 * ks16][0], s[2 * ks16][1]), p1 = pack_bf16(s[2 * ks16][2], s[2 * ks16][3]);
-        const uint32_t p2 = pack_bf16(s[2 * ks16 + 1][0], s[2 * ks16 + 1][1]);
-        const uint32_t p3 = pack_bf16(s[2 * ks16 + 1][2], s[2 * ks16 + 1][3]);
+        // S tiles 2 ks and 2 ks + 1 are the two halves of the 16-key step ks of P V
+        uint32_t pk[MT][4];
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+          pk[mt][0] = pack_bf16(s[mt][2 * ks16][0], s[mt][2 * ks16][1]);
+          pk[mt][1] = pack_bf16(s[mt][2 * ks16][2], s[mt][2 * ks16][3]);
+          pk[mt][2] = pack_bf16(s[mt][2 * ks16 + 1][0], s[mt][2 * ks16 + 1][1]);
+          pk[mt][3] = pack_bf16(s[mt][2 * ks16 + 1][2], s[mt][2 * ks16 + 1][3]);
+        }
         const int kr = ks16 * 16 + t * 2;                     // rows kr, kr+1, kr+8, kr+9 of the V tile
         const int sw = ((kr >> 1) & 3) << 1;                  // the same for all four rows
 #pragma unroll
@@ -825,8 +881,10 @@ prefill_attn_mma_kernel(const PrefillArgs<bf16> a) {
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
             const uint32_t sel = (j & 1) ? 0x7632u : 0x5410u;
-            mma_16816(o[dg][j], p0, p1, p2, p3, __byte_perm(va[j >> 1], vb[j >> 1], sel),
-                      __byte_perm(vc[j >> 1], vd[j >> 1], sel));
+            const uint32_t b0 = __byte_perm(va[j >> 1], vb[j >> 1], sel), b1 = __byte_perm(vc[j >> 1], vd[j >> 1], sel);
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt)
+              mma_16816(o[mt][dg][j], pk[mt][0], pk[mt][1], pk[mt][2], pk[mt][3], b0, b1);
           }
         }
       }
@@ -834,20 +892,24 @@ prefill_attn_mma_kernel(const PrefillArgs<bf16> a) {
     __syncthreads();   // all warps are done with this stage before it is loaded again
   }
   // ---- normalise and store: through shared memory so that rows go out in 16-byte pieces
-  bf16* os = Ks;       // [64][D], free now
-  const float inv_lo = l_lo > 0.f ? 1.f / l_lo : 0.f, inv_hi = l_hi > 0.f ? 1.f / l_hi : 0.f;
+  bf16* os = Ks;       // [64 MT][D], free now (two stages of [64][D])
 #pragma unroll
-  for (int dg = 0; dg < DG; ++dg)
+  for (int mt = 0; mt < MT; ++mt) {
+    const int r_lo = wrow0 + mt * 16 + g, r_hi = r_lo + 8;
+    const float inv_lo = l_lo[mt] > 0.f ? 1.f / l_lo[mt] : 0.f, inv_hi = l_hi[mt] > 0.f ? 1.f / l_hi[mt] : 0.f;
 #pragma unroll
-    for (int j = 0; j < 8; ++j)
+    for (int dg = 0; dg < DG; ++dg)
 #pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const int d = dg * 64 + (t * 2 + e) * 8 + j;
-        os[r_lo * kD + d] = __float2bfloat16_rn(o[dg][j][e] * inv_lo);
-        os[r_hi * kD + d] = __float2bfloat16_rn(o[dg][j][2 + e] * inv_hi);
-      }
+      for (int j = 0; j < 8; ++j)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int d = dg * 64 + (t * 2 + e) * 8 + j;
+          os[r_lo * kD + d] = __float2bfloat16_rn(o[mt][dg][j][e] * inv_lo);
+          os[r_hi * kD + d] = __float2bfloat16_rn(o[mt][dg][j][2 + e] * inv_hi);
+        }
+  }
   __syncthreads();
-  for (int i = threadIdx.x; i < kMQ * CPR; i += 128) {
+  for (int i = threadIdx.x; i < kPreRows * CPR; i += 128) {
     const int r = i / CPR, c = i - r * CPR;
     if (r < rows)
       *reinterpret_cast<uint4*>(a.out + static_cast<size_t>(tok0 + r) * a.out_stride + head * kD + c * 8) =
@@ -980,7 +1042,7 @@ int launch_prefill(const void* q, int q_stride, const void* kc, const void* vc, 
         if (e != cudaSuccess) return static_cast<int>(e);
         mattr = true;
       }
-      launch_kernel(prefill_attn_mma_kernel, dim3(dim3(tiles, hq)), dim3(128), msmem, stream, a);
+      launch_kernel(prefill_attn_mma_kernel, dim3(dim3(tiles * (kPreTile / kPreRows), hq)), dim3(128), msmem, stream, a);
       return static_cast<int>(cudaGetLastError());
     }
   }
@@ -995,7 +1057,7 @@ int launch_prefill(const void* q, int q_stride, const void* kc, const void* vc, 
     if (e != cudaSuccess) return static_cast<int>(e);
     attr_set = true;
   }
-  launch_kernel(prefill_attn_kernel<T>, dim3(dim3(tiles * 2, hq)), dim3(kPreThreads), smem, stream, a);
+  launch_kernel(prefill_attn_kernel<T>, dim3(dim3(tiles * 4, hq)), dim3(kPreThreads), smem, stream, a);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -1005,7 +1067,7 @@ extern "C" {
 
 int rl_attn_head_dim() { return kD; }
 int rl_attn_partition() { return kPart; }
-int rl_attn_tile_rows() { return 2 * kBQ; }
+int rl_attn_tile_rows() { return 4 * kBQ; }
 
 // dtype: 0 = float32, 1 = bfloat16 (type of q, the cache and out).
 // items: int32 [nitems, 4] = (token index of the query, sequence index, context length, 0).

@@ -263,7 +263,7 @@ def _attn(head_dim: int) -> ctypes.CDLL:
 
 
 DECODE_PARTITION = 128
-PREFILL_TILE_ROWS = 64
+PREFILL_TILE_ROWS = 128
 
 
 def attn_decode(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcache: torch.Tensor,
@@ -301,7 +301,7 @@ def attn_prefill(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcache: t
                  tile_rows: torch.Tensor, positions: torch.Tensor, out: torch.Tensor, tiles: int,
                  num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, window: int,
                  scale: float, impl: int = 0) -> None:
-    """Tiles of up to 64 consecutive query tokens of one sequence (tile_seq, tile_tok, tile_rows) over the
+    """Tiles of up to 128 consecutive query tokens of one sequence (tile_seq, tile_tok, tile_rows) over the
     paged cache.  impl 0: tensor-core kernel where it applies (bfloat16, head size 64 or 128), else
     CUDA cores; 1: CUDA cores; 2: tensor cores or an error."""
     _need_cuda(q, kcache, out)
