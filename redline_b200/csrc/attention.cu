@@ -717,7 +717,7 @@ prefill_attn_mma_kernel(const PrefillArgs<bf16> a) {
       const size_t page = live ? bt[j >> ps_shift] : 0;
       const size_t off = (page * a.hkv + kvh) * head_stride + static_cast<size_t>(j & ps_mask) * kD + c * 8;
       const int ck = c ^ ((key & 1) << 2);              // K: rows g, g+1 of a read go to different halves
-      const int cv = c ^ (((key >> 1) & 3) << 1);       // V: rows t*2 of a read go to different pairs
+      const int cv = c ^ (key & 7);                     // V: the eight rows of an ldmatrix tile go to eight chunks
       cp_async16(ks + key * kD + ck * 8, a.kcache + off, live);
       cp_async16(vs + key * kD + cv * 8, a.vcache + off, live);
     }
@@ -867,24 +867,21 @@ prefill_attn_mma_kernel(const PrefillArgs<bf16> a) {
           pk[mt][2] = pack_bf16(s[mt][2 * ks16 + 1][0], s[mt][2 * ks16 + 1][1]);
           pk[mt][3] = pack_bf16(s[mt][2 * ks16 + 1][2], s[mt][2 * ks16 + 1][3]);
         }
-        const int kr = ks16 * 16 + t * 2;                     // rows kr, kr+1, kr+8, kr+9 of the V tile
-        const int sw = ((kr >> 1) & 3) << 1;                  // the same for all four rows
+        // V fragments by ldmatrix.trans: one instruction brings four 8 x 8 tiles, keys (0..7, 8..15) of the
+        // step x two 8-wide blocks of d, as the B fragments of two MMAs; lane l gives the address of row
+        // l % 8 of tile l / 8
+        const int vrow = ks16 * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
 #pragma unroll
-        for (int dg = 0; dg < DG; ++dg) {
-          const int c = (dg * 8 + g) ^ sw;
-          const uint4 va4 = *reinterpret_cast<const uint4*>(vs + kr * kD + c * 8);
-          const uint4 vb4 = *reinterpret_cast<const uint4*>(vs + (kr + 1) * kD + c * 8);
-          const uint4 vc4 = *reinterpret_cast<const uint4*>(vs + (kr + 8) * kD + c * 8);
-          const uint4 vd4 = *reinterpret_cast<const uint4*>(vs + (kr + 9) * kD + c * 8);
-          const uint32_t va[4] = {va4.x, va4.y, va4.z, va4.w}, vb[4] = {vb4.x, vb4.y, vb4.z, vb4.w};
-          const uint32_t vc[4] = {vc4.x, vc4.y, vc4.z, vc4.w}, vd[4] = {vd4.x, vd4.y, vd4.z, vd4.w};
+        for (int jp = 0; jp < kD / 16; ++jp) {                // pairs of 8-wide d blocks
+          const int c = (jp * 2 + (lane >> 4)) ^ (vrow & 7);
+          uint32_t b0, b1, b2, b3;
+          const uint32_t addr = static_cast<uint32_t>(__cvta_generic_to_shared(vs + vrow * kD + c * 8));
+          asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3) : "r"(addr));
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const uint32_t sel = (j & 1) ? 0x7632u : 0x5410u;
-            const uint32_t b0 = __byte_perm(va[j >> 1], vb[j >> 1], sel), b1 = __byte_perm(vc[j >> 1], vd[j >> 1], sel);
-#pragma unroll
-            for (int mt = 0; mt < MT; ++mt)
-              mma_16816(o[mt][dg][j], pk[mt][0], pk[mt][1], pk[mt][2], pk[mt][3], b0, b1);
+          for (int mt = 0; mt < MT; ++mt) {
+            mma_16816(o[mt][jp >> 2][(jp & 3) * 2], pk[mt][0], pk[mt][1], pk[mt][2], pk[mt][3], b0, b1);
+            mma_16816(o[mt][jp >> 2][(jp & 3) * 2 + 1], pk[mt][0], pk[mt][1], pk[mt][2], pk[mt][3], b2, b3);
           }
         }
       }
@@ -903,7 +900,7 @@ prefill_attn_mma_kernel(const PrefillArgs<bf16> a) {
       for (int j = 0; j < 8; ++j)
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
-          const int d = dg * 64 + (t * 2 + e) * 8 + j;
+          const int d = dg * 64 + j * 8 + t * 2 + e;
           os[r_lo * kD + d] = __float2bfloat16_rn(o[mt][dg][j][e] * inv_lo);
           os[r_hi * kD + d] = __float2bfloat16_rn(o[mt][dg][j][2 + e] * inv_hi);
         }
