@@ -173,12 +173,12 @@ def bench_attn_prefill(args) -> None:
 
     def fn(i):
         kernels.attn_prefill(qkv, qkv.shape[1], k, v, bt, tile_seq, tile_tok, tile_rows, pos, out, nt, Hq, Hkv, D, ps,
-                             0, 1.0 / math.sqrt(D))
+                             0, 1.0 / math.sqrt(D), args.impl)
 
     us = graph_time_us(fn, 2, replays=5, use_graph=not args.no_graph)
     flops = Hq * 4.0 * D * (T * (T + 1) / 2.0)
     pk = peaks()
-    print(json.dumps({"kernel": "attn_prefill", "tokens": T, "heads": Hq, "kv_heads": Hkv, "head_dim": D,
+    print(json.dumps({"kernel": "attn_prefill", "impl": args.impl, "tokens": T, "heads": Hq, "kv_heads": Hkv, "head_dim": D,
                       "us": round(us, 1), "TFLOP/s": round(flops / us / 1e6, 1),
                       "frac_of_measured_bf16": round(flops / us / 1e6 / pk["bf16_tflops"], 4)}))
 
@@ -197,9 +197,11 @@ def main() -> int:
         if name == "attn_decode":
             p.add_argument("--batch", type=int, default=8)
             p.add_argument("--ctx", type=int, default=4096)
-            p.add_argument("--impl", type=int, default=0, help="0 auto, 1 CUDA cores, 2 tensor cores (3 for attn_decode: the streaming kernel)")
+            p.add_argument("--impl", type=int, default=0,
+                           help="0 auto, 1 CUDA cores, 2 one-partition mma.sync kernel, 3 streaming kernel")
         if name == "attn_prefill":
             p.add_argument("--tokens", type=int, default=2048)
+            p.add_argument("--impl", type=int, default=0, help="0 auto, 1 CUDA cores, 2 mma.sync kernel, 3 tcgen05 kernel")
         if name == "gemm_tc":
             p.add_argument("--rows", type=int, default=2048)
             p.add_argument("--n", type=int, default=3072)

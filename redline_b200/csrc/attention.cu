@@ -916,6 +916,13 @@ prefill_attn_mma_kernel(const PrefillArgs<bf16> a) {
 #endif  // tensor-core prefill
 
 }  // namespace rl
+#if RL_HEAD_DIM == 64
+#include "prefill_tc.cuh"
+#define RL_HAVE_TC_PREFILL 1
+#endif
+namespace rl {
+
+}  // namespace rl
 
 using namespace rl;
 
@@ -1008,7 +1015,7 @@ template <typename T>
 int launch_prefill(const void* q, int q_stride, const void* kc, const void* vc, const int32_t* bt,
                    int max_blocks, const int32_t* tile_seq, const int32_t* tile_tok,
                    const int32_t* tile_rows, const int32_t* positions, void* out, int out_stride,
-                   int tiles, int hq, int hkv, int page_size, int window, float scale, int impl,
+                   int tiles, int hq, int hkv, int page_size, int window, float scale, int impl, int* status,
                    cudaStream_t stream) {
   PrefillArgs<T> a;
   a.q = static_cast<const T*>(q);
@@ -1028,6 +1035,26 @@ int launch_prefill(const void* q, int q_stride, const void* kc, const void* vc, 
   a.page_size = page_size;
   a.window = window;
   a.scale = scale;
+#ifdef RL_HAVE_TC_PREFILL
+  if constexpr (sizeof(T) == 2) {
+    const bool aligned = q_stride % 8 == 0 && out_stride % 8 == 0 &&
+                         ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(out) |
+                           reinterpret_cast<uintptr_t>(kc) | reinterpret_cast<uintptr_t>(vc)) & 15) == 0;
+    // the tcgen05 kernel: power-of-two pages, 16-byte aligned rows, a status word for its bounded waits
+    if ((impl == 0 || impl == 3) && status != nullptr && aligned && (page_size & (page_size - 1)) == 0) {
+      static bool tattr = false;
+      if (!tattr) {
+        cudaError_t e = cudaFuncSetAttribute(prefill_attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             static_cast<int>(kPrefillTcSmem));
+        if (e != cudaSuccess) return static_cast<int>(e);
+        tattr = true;
+      }
+      launch_kernel(prefill_attn_tc_kernel, dim3(dim3(tiles, hq)), dim3(kTcThreads), kPrefillTcSmem, stream, a, status);
+      return static_cast<int>(cudaGetLastError());
+    }
+  }
+#endif
+  if (impl == 3) return static_cast<int>(cudaErrorInvalidValue);
 #ifdef RL_HAVE_MMA_DECODE
   if constexpr (sizeof(T) == 2) {
     if (impl != 1 && page_size % 16 == 0 && out_stride % 8 == 0 && q_stride % 8 == 0) {
@@ -1093,15 +1120,15 @@ int rl_attn_prefill(int dtype, const void* q, int q_stride, const void* kc, cons
                     const int32_t* bt, int max_blocks, const int32_t* tile_seq,
                     const int32_t* tile_tok, const int32_t* tile_rows, const int32_t* positions,
                     void* out, int out_stride, int tiles, int hq, int hkv, int page_size, int window,
-                    float scale, int impl, cudaStream_t stream) {
+                    float scale, int impl, int* status, cudaStream_t stream) {
   if (tiles <= 0) return 0;
   if (dtype == 0)
     return launch_prefill<float>(q, q_stride, kc, vc, bt, max_blocks, tile_seq, tile_tok, tile_rows,
                                  positions, out, out_stride, tiles, hq, hkv, page_size, window, scale, impl,
-                                 stream);
+                                 status, stream);
   return launch_prefill<bf16>(q, q_stride, kc, vc, bt, max_blocks, tile_seq, tile_tok, tile_rows,
                               positions, out, out_stride, tiles, hq, hkv, page_size, window, scale, impl,
-                              stream);
+                              status, stream);
 }
 
 }  // extern "C"

@@ -183,8 +183,10 @@ class ModelRunner:
             self.builder.status.zero_()
             tc.zero_()
             what = [m for bit, m in STATUS_MESSAGES.items() if code & bit]
-            if tc_code:
+            if tc_code & 1:
                 what.append("a wait inside the tcgen05 matrix product that ran out")
+            if tc_code & 4:
+                what.append("a wait inside the tcgen05 attention that ran out")
             raise EngineError("a kernel met " + " and ".join(what))
 
     def memory_report(self) -> Dict[str, int]:

@@ -221,7 +221,8 @@ _tc_status: Dict[int, torch.Tensor] = {}
 
 
 def tc_status(device: torch.device) -> torch.Tensor:
-    """The device word in which gemm_tc reports a wait that ran out (bit 0)."""
+    """The device word in which the tcgen05 kernels report a wait that ran out (bit 0: gemm_tc,
+    bit 2: prompt-portion attention)."""
     i = device.index if device.index is not None else torch.cuda.current_device()
     if i not in _tc_status:
         _tc_status[i] = torch.zeros(1, dtype=torch.int32, device=device)
@@ -302,16 +303,17 @@ def attn_prefill(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcache: t
                  num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, window: int,
                  scale: float, impl: int = 0) -> None:
     """Tiles of up to 128 consecutive query tokens of one sequence (tile_seq, tile_tok, tile_rows) over the
-    paged cache.  impl 0: tensor-core kernel where it applies (bfloat16, head size 64 or 128), else
-    CUDA cores; 1: CUDA cores; 2: tensor cores or an error."""
+    paged cache.  impl 0: the best kernel that applies (bfloat16: tcgen05 at head size 64, mma.sync at
+    head size 128; else CUDA cores); 1: CUDA cores; 2: the mma.sync kernel or an error; 3: the tcgen05
+    kernel or an error."""
     _need_cuda(q, kcache, out)
     f = _fn(_attn(head_dim), "rl_attn_prefill",
             [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
-             c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p])
+             c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p])
     _check(f(_code(q.dtype), _ptr(q), q_stride, _ptr(kcache), _ptr(vcache), _ptr(block_table),
              block_table.shape[1], _ptr(tile_seq), _ptr(tile_tok), _ptr(tile_rows), _ptr(positions),
              _ptr(out), out.stride(0), tiles, num_heads, num_kv_heads, page_size, window, float(scale), impl,
-             _stream()), "attn_prefill")
+             _ptr(tc_status(q.device)), _stream()), "attn_prefill")
 
 
 # -------------------------------------------------------------------- sampling

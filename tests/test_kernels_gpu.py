@@ -244,6 +244,22 @@ def test_attention_prefill_tensor_core_kernel(Hq, Hkv, D, page_size):
                       prefill_impl=2)
 
 
+@pytest.mark.parametrize("Hq,Hkv", [(4, 2), (32, 8), (5, 5), (3, 1)])
+@pytest.mark.parametrize("page_size", [16, 32, 64])
+def test_attention_prefill_tcgen05_kernel(Hq, Hkv, page_size):
+    """impl 3 insists on the tcgen05 kernel (head size 64): portions that start and end anywhere relative
+    to its 128-row and 128-key tiles, pasts of every alignment, several key tiles per query tile (both S
+    and O buffers and both stages in use again), every page size, and windows."""
+    D = 64
+    run_attention("bfloat16", Hq, Hkv, D, [0, 0, 0, 0], [2, 127, 128, 129], page_size=page_size, seed=41, prefill_impl=3)
+    run_attention("bfloat16", Hq, Hkv, D, [0, 1, 127, 128, 500], [600, 257, 2, 130, 131], page_size=page_size, seed=42,
+                  prefill_impl=3)
+    for window in (1, 20, 128, 200, 600):
+        run_attention("bfloat16", Hq, Hkv, D, [0, 90, 590], [300, 35, 130], page_size=page_size, window=window, seed=43,
+                      prefill_impl=3)
+    assert int(kernels.tc_status(torch.device(DEV)).item()) == 0
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("Hq,Hkv,D", ATTN_SHAPES)
 def test_attention_decode_lengths_across_pages_and_partitions(dtype, Hq, Hkv, D):
@@ -371,6 +387,8 @@ def test_a_far_key_is_found_among_hundreds(dtype):
             run_attention(dtype, Hq, Hkv, D, [total - 1], [1], seed=9, sharp=sharp, decode_impl=2)
         run_attention(dtype, Hq, Hkv, D, [total - 40], [40], seed=9, sharp=sharp)   # prefill kernel
         run_attention(dtype, Hq, Hkv, D, [total - 40], [40], seed=9, sharp=sharp, prefill_impl=1)
+        if dtype == "bfloat16":
+            run_attention(dtype, Hq, Hkv, D, [total - 40], [40], seed=9, sharp=sharp, prefill_impl=2)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
