@@ -31,11 +31,11 @@ constexpr int kTcTmemCols = 512;                     // S0 0.., S1 128.., O0 256
 
 struct PrefillTcShared {
   uint64_t q_full;
-  uint64_t k_full[2], v_full[2];      // the loader's 32 lanes arrive
+  uint64_t k_full[2], v_full[2];      // one arrival by the loader warp (after all its lanes' copies have landed)
   uint64_t qk_done[2], pv_done[2];    // MMA commits: S of the tile is ready / K stage free; O of the tile ready / V, P free
-  uint64_t s_free[2], o_free[2];      // the 256 row threads have read the buffer
-  uint64_t p_ready[2];                // the 256 row threads have written P
-  uint64_t pair[4];                   // the two warps of a quarter of rows exchange a value (64 arrivals a phase)
+  uint64_t s_free[2], o_free[2];      // the 8 row warps have read the buffer
+  uint64_t p_ready[2];                // the 8 row warps have written P
+  uint64_t pair[4];                   // the two warps of a quarter of rows exchange a value (2 arrivals a phase)
   float xchg[2][2][kTcRows];          // [phase parity][half][row]
   uint32_t tmem_base;
   volatile int abort;
@@ -74,17 +74,17 @@ prefill_attn_tc_kernel(const PrefillArgs<bf16> a, int* status) {
   const int kvh = head / (a.hq / a.hkv);
 
   if (threadIdx.x == 0) {
-    mbar_init(&sh->q_full, 32);
+    mbar_init(&sh->q_full, 1);
     for (int b = 0; b < 2; ++b) {
-      mbar_init(&sh->k_full[b], 32);
-      mbar_init(&sh->v_full[b], 32);
+      mbar_init(&sh->k_full[b], 1);
+      mbar_init(&sh->v_full[b], 1);
       mbar_init(&sh->qk_done[b], 1);
       mbar_init(&sh->pv_done[b], 1);
-      mbar_init(&sh->s_free[b], 256);
-      mbar_init(&sh->o_free[b], 256);
-      mbar_init(&sh->p_ready[b], 256);
+      mbar_init(&sh->s_free[b], 8);       // one arrival per row warp (its lanes meet first)
+      mbar_init(&sh->o_free[b], 8);
+      mbar_init(&sh->p_ready[b], 8);
     }
-    for (int qq = 0; qq < 4; ++qq) mbar_init(&sh->pair[qq], 64);
+    for (int qq = 0; qq < 4; ++qq) mbar_init(&sh->pair[qq], 2);
     sh->abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -141,9 +141,12 @@ prefill_attn_tc_kernel(const PrefillArgs<bf16> a, int* status) {
     auto hand_over = [&]() {
       cp_async_wait<0>();
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      if (q_pending) mbar_arrive(&sh->q_full);
+      __syncwarp();
+      if (lane == 0) {
+        if (q_pending) mbar_arrive(&sh->q_full);
+        if (pending >= 0) mbar_arrive(&full[pending & 1]);
+      }
       q_pending = false;
-      if (pending >= 0) mbar_arrive(&full[pending & 1]);
       pending = -1;
     };
     for (int i = 0; i < nt; ++i) {
@@ -188,9 +191,12 @@ prefill_attn_tc_kernel(const PrefillArgs<bf16> a, int* status) {
       if (pending >= 0 || q_pending) {      // the tile before (and Q): landed by now, or nearly
         cp_async_wait<1>();
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        if (q_pending) mbar_arrive(&sh->q_full);
+        __syncwarp();
+        if (lane == 0) {
+          if (q_pending) mbar_arrive(&sh->q_full);
+          if (pending >= 0) mbar_arrive(&full[pending & 1]);
+        }
         q_pending = false;
-        if (pending >= 0) mbar_arrive(&full[pending & 1]);
       }
       pending = i;
     }
@@ -254,7 +260,8 @@ prefill_attn_tc_kernel(const PrefillArgs<bf16> a, int* status) {
     int xphase = 0;                                       // exchanges done so far (parity of the pair's mbarrier)
     auto exchange = [&](float mine) -> float {            // gives the partner's value
       sh->xchg[xphase & 1][h][r] = mine;
-      mbar_arrive(&sh->pair[q]);                          // (release: the value is visible to who sees the phase)
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sh->pair[q]);           // (release: the values are visible to who sees the phase)
       ok = ok && mbar_wait(&sh->pair[q], xphase & 1, &sh->abort);
       const float other = sh->xchg[xphase & 1][h ^ 1][r];
       ++xphase;
@@ -270,7 +277,8 @@ prefill_attn_tc_kernel(const PrefillArgs<bf16> a, int* status) {
 #pragma unroll
       for (int d = 0; d < 32; ++d) acc[d] = fmaf(acc[d], alpha, o[d]);
       tc_fence_before();
-      mbar_arrive(&sh->o_free[b]);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sh->o_free[b]);
     };
     for (int i = 0; i < nt && ok; ++i) {
       const int b = i & 1;
@@ -311,7 +319,8 @@ prefill_attn_tc_kernel(const PrefillArgs<bf16> a, int* status) {
       tmem_ld32(tmem + lane_addr + b * kTcKeys + h * 64, s);
       tmem_ld32(tmem + lane_addr + b * kTcKeys + h * 64 + 32, s + 32);
       tc_fence_before();
-      mbar_arrive(&sh->s_free[b]);                        // S of this tile has been read
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sh->s_free[b]);         // S of this tile has been read
       if (masked) {
 #pragma unroll
         for (int j = 0; j < 64; ++j) {
@@ -362,7 +371,8 @@ prefill_attn_tc_kernel(const PrefillArgs<bf16> a, int* status) {
                      : "memory");
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P is read by the tensor core
-      mbar_arrive(&sh->p_ready[b]);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sh->p_ready[b]);
       // ---- while the O product of this tile runs: add the one of the tile before
       if (i > 0) add_o(i - 1, alpha_prev);
       alpha_prev = alpha;

@@ -37,10 +37,27 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Waits for the phase with the given parity; false if the CTA is aborting or the limit ran out.
+// The same, but the thread may sleep in the instruction for up to about `ns` nanoseconds (it is woken
+// when the phase completes): a waiting warp then hardly takes issue slots from the working ones.
+__device__ __forceinline__ bool mbar_try_wait_sleep(uint64_t* bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
+      : "memory");
+  return ok != 0;
+}
+// Waits for the phase with the given parity; false if the CTA is aborting or the limit ran out.  A
+// poll sleeps for up to a microsecond, so the limit is a matter of seconds.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort) {
+  if (mbar_try_wait(bar, parity)) return true;
   for (int i = 0; i < kSpinLimit; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_try_wait_sleep(bar, parity, 1000u)) return true;
     if (*abort) return false;
   }
   *abort = 1;
