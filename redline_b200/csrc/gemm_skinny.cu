@@ -61,6 +61,7 @@ constexpr int kSB = 128;  // k per warp iteration (a "super-block": two 64-wide 
 // four 16-byte pieces each (k = sb * 128 + q * 32 + t * 8 .. + 8, q = 0..3).
 struct WFrag {
   uint4 lo[4], hi[4];
+  uint4 x[4];     // XG only: the activations of the same k, row g of the batch
 };
 
 // MT: token rows padded to 8 or 16; WARPS: warps per CTA; EPI: epilogue; NORM: fused norm.
@@ -73,6 +74,11 @@ __global__ void __launch_bounds__(WARPS * 32)
 gemm_skinny_kernel(const SkinnyArgs a, int kc) {
   constexpr bool GATED = (EPI == kSwiglu);
   constexpr int NG = MT / 8;                    // 8-token groups
+  // XG: with bfloat16 activations and at most 8 rows the activations are not staged in shared memory
+  // at all: a thread's activation fragment of a super-block (16 bytes per piece, row g of the batch)
+  // comes from global memory (L2) together with the weights of the same k, two steps ahead, and the
+  // k loop has no barriers.  The sums are taken in the same order as with staging.
+  constexpr bool XG = !NORM && MT == 8;
   constexpr int STREAMS = GATED ? 2 : 1;        // weight streams per tile (gate rows, up rows)
   constexpr int TPC = WARPS / KW / STREAMS;     // tiles a CTA works on at the same time
   static_assert(TPC >= 1 && TPC * KW * STREAMS == WARPS, "bad warp split");
@@ -115,6 +121,11 @@ gemm_skinny_kernel(const SkinnyArgs a, int kc) {
     lo = ok ? ldg_stream(w_lo + k) : make_uint4(0, 0, 0, 0);
     hi = ok ? ldg_stream(w_hi + k) : make_uint4(0, 0, 0, 0);
   };
+  auto load_x = [&](uint4& xv, int q) {          // (after the wait on the kernels before: they wrote x)
+    const int k = l_sb * kSB + q * 32 + t * 8;
+    const bool ok = l_ok && k < K && g < M;
+    xv = ok ? *reinterpret_cast<const uint4*>(a.x + static_cast<size_t>(g) * a.ldx + k) : make_uint4(0, 0, 0, 0);
+  };
   auto load_advance = [&]() {
     l_sb += KW;
     if (l_sb >= nsb) {                     // on to the next round of the CTA
@@ -125,14 +136,32 @@ gemm_skinny_kernel(const SkinnyArgs a, int kc) {
     }
   };
   pdl_launch();
+  const int sb0 = l_sb;
+  const bool ok0 = l_ok;
 #pragma unroll
   for (int q = 0; q < 4; ++q) load_piece(fa.lo[q], fa.hi[q], q);
   load_advance();
+  const int sb1 = l_sb;
+  const bool ok1 = l_ok;
 #pragma unroll
   for (int q = 0; q < 4; ++q) load_piece(fb.lo[q], fb.hi[q], q);
   load_advance();
   int step = 0;       // super-blocks this warp has multiplied
   pdl_wait();   // everything below reads what earlier kernels of the step wrote
+  if (XG) {     // the activations of the first two steps (the load cursor is already two steps on)
+    const int sb2 = l_sb;
+    const bool ok2 = l_ok;
+    l_sb = sb0;
+    l_ok = ok0;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) load_x(fa.x[q], q);
+    l_sb = sb1;
+    l_ok = ok1;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) load_x(fb.x[q], q);
+    l_sb = sb2;
+    l_ok = ok2;
+  }
 
   if (NORM) {
     for (int m = warp; m < MT; m += WARPS) {
@@ -163,10 +192,10 @@ gemm_skinny_kernel(const SkinnyArgs a, int kc) {
 
     for (int k0 = 0; k0 < K; k0 += kc) {
       const int kn = min(kc, K - k0);
-      __syncthreads();   // the previous chunk (or the previous tile's reduction) is done with smem
+      if (!XG) __syncthreads();   // the previous chunk (or the previous tile's reduction) is done with smem
       // ---- stage x[:, k0 : k0 + kn] as bfloat16, zero beyond M and beyond kn (to a multiple of 128)
       const int kpad = (kn + kSB - 1) / kSB * kSB;
-      for (int i = tid; i < MT * (kpad / 8); i += WARPS * 32) {
+      for (int i = tid; i < (XG ? 0 : MT * (kpad / 8)); i += WARPS * 32) {
         const int m = i / (kpad / 8), c = (i - m * (kpad / 8)) * 8;
         uint4 v = make_uint4(0, 0, 0, 0);
         if (m < M && c < kn) {
@@ -202,7 +231,7 @@ gemm_skinny_kernel(const SkinnyArgs a, int kc) {
         }
         *reinterpret_cast<uint4*>(xs + m * lds + c) = v;
       }
-      __syncthreads();
+      if (!XG) __syncthreads();
       // ---- the weight stream: warp kw takes super-blocks kw, kw + KW, ...
       const int sb_end = min((k0 + kc) / kSB, nsb);
       for (int sb = k0 / kSB + kw; sb < sb_end; sb += KW, ++step) {
@@ -212,11 +241,12 @@ gemm_skinny_kernel(const SkinnyArgs a, int kc) {
           for (int q = 0; q < 4; ++q) {
 #pragma unroll
             for (int j = 0; j < NG; ++j) {
-              const uint4 xv = *reinterpret_cast<const uint4*>(xs + (j * 8 + g) * lds + kb + q * 32 + t * 8);
+              const uint4 xv = XG ? f.x[q] : *reinterpret_cast<const uint4*>(xs + (j * 8 + g) * lds + kb + q * 32 + t * 8);
               mma_bf16(acc[j], f.lo[q].x, f.hi[q].x, f.lo[q].y, f.hi[q].y, xv.x, xv.y);
               mma_bf16(acc[j], f.lo[q].z, f.hi[q].z, f.lo[q].w, f.hi[q].w, xv.z, xv.w);
             }
             load_piece(f.lo[q], f.hi[q], q);     // the same place, two steps on
+            if (XG) load_x(f.x[q], q);
           }
           load_advance();
         };
@@ -292,7 +322,8 @@ int launch_one(const SkinnyArgs& a0, int sm_count, cudaStream_t stream) {
   const int kc = (kunits + chunks - 1) / chunks * kUnit;
   const size_t xbytes = static_cast<size_t>(MT) * (kc + 32) * 2;
   const size_t rbytes = static_cast<size_t>(WARPS) * 16 * MT * 4;
-  const size_t smem = xbytes > rbytes ? xbytes : rbytes;
+  constexpr bool XG = !NORM && MT == 8;               // no staging of x: only the reduction uses shared memory
+  const size_t smem = (!XG && xbytes > rbytes) ? xbytes : rbytes;
   static size_t set_for = 0;
   if (smem > set_for) {
     cudaError_t e = cudaFuncSetAttribute(gemm_skinny_kernel<MT, WARPS, KW, EPI, NORM>,
