@@ -164,6 +164,7 @@ def gemm_tn_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, rows: Opti
 # ---------------------------------------------------------------- skinny gemm
 
 SKINNY_MAX_ROWS = 16
+SKINNY_UNSTAGED_ROWS = 8    # up to here bfloat16 activations are read from global memory, not staged
 EPI_BF16, EPI_F32, EPI_ADD_RESIDUAL, EPI_SWIGLU = 0, 1, 2, 3
 _sm_count: Dict[int, int] = {}
 

@@ -105,7 +105,13 @@ class GQAttention(Mixer):
                 or not kernels.skinny_ok(T, self.w_qkv, rt.dtype) or not kernels.skinny_ok(T, self.w_o, rt.dtype)):
             return False
         qkv = rt.workspace.get("attn.qkv", (rt.max_tokens, self.qkv_size), rt.dtype)[:T]
-        kernels.gemm_skinny(self.w_qkv, qkv, kernels.EPI_BF16, T, residual=residual, norm_w=rms[0], eps=rms[1])
+        if T <= kernels.SKINNY_UNSTAGED_ROWS:
+            # (see SwiGLUMLP.forward_into: a norm kernel of its own and a product without staging)
+            xn = rt.workspace.get("attn.xn", (kernels.SKINNY_UNSTAGED_ROWS, self.params.hidden_size), rt.dtype)[:T]
+            kernels.add_rmsnorm(residual, None, rms[0], xn, rms[1], rows=T)
+            kernels.gemm_skinny(self.w_qkv, qkv, kernels.EPI_BF16, T, x=xn)
+        else:
+            kernels.gemm_skinny(self.w_qkv, qkv, kernels.EPI_BF16, T, residual=residual, norm_w=rms[0], eps=rms[1])
         attn = self._attend(qkv, ctx, cache)
         kernels.gemm_skinny(self.w_o, residual, kernels.EPI_ADD_RESIDUAL, T, x=attn)
         return True

@@ -82,6 +82,14 @@ class SwiGLUMLP(FeedForward):
                 or not kernels.skinny_ok(T, self.w_gate_up, rt.dtype) or not kernels.skinny_ok(T, self.w_down, rt.dtype)):
             return False
         act = rt.workspace.get("ffn.act", (rt.max_tokens, p.intermediate_size), rt.dtype)[:T]
-        kernels.gemm_skinny(self.w_gate_up, act, kernels.EPI_SWIGLU, T, residual=residual, norm_w=rms[0], eps=rms[1])
+        if T <= kernels.SKINNY_UNSTAGED_ROWS:
+            # up to 8 rows: the product takes bfloat16 activations straight from global memory (no staging,
+            # no barriers in its k loop), which is worth a norm kernel of its own (measured: 2 % of the step)
+            xn = rt.workspace.get("ffn.xn", (kernels.SKINNY_UNSTAGED_ROWS, p.hidden_size), rt.dtype)[:T]
+            kernels.add_rmsnorm(residual, None, rms[0], xn, rms[1], rows=T)
+            kernels.gemm_skinny(self.w_gate_up, act, kernels.EPI_SWIGLU, T, x=xn)
+        else:
+            kernels.gemm_skinny(self.w_gate_up, act, kernels.EPI_SWIGLU, T, residual=residual, norm_w=rms[0],
+                                eps=rms[1])
         kernels.gemm_skinny(self.w_down, residual, kernels.EPI_ADD_RESIDUAL, T, x=act)
         return True
