@@ -147,7 +147,7 @@ __device__ __forceinline__ void cp_async16_s(uint32_t smem, const void* gmem, bo
 // (a warp or the CTA) share the columns, tid being the caller's index among them.  A piece is what
 // one run of the cut left of the row; it lies in the slot of its first partition.  Pieces are taken
 // sixteen at a time, all their loads in flight together, and folded into a running (max,
-// denominator, numerator) in order: the result does not depend on who merges.
+// denominator, numerators) in order: the result does not depend on who merges.
 __device__ __forceinline__ void stream_merge(const DecodeArgs<bf16>& a, const StreamShared* sh, const StreamCut& cut,
                                              int item, int kvh, int tid, int nthreads) {
   const int G = a.hq / a.hkv;
@@ -158,38 +158,40 @@ __device__ __forceinline__ void stream_merge(const DecodeArgs<bf16>& a, const St
   const int row_begin = sh->start[item] + kvh * np;
   const int k_first = cut.run_of(row_begin), k_last = cut.run_of(row_begin + np - 1);
   const int pieces = k_last - k_first + 1;
-  for (int idx = tid; idx < G * kD; idx += nthreads) {
-    const int r = idx / kD, d = idx - r * kD;
+  for (int idx = tid; idx < G * (kD / 2); idx += nthreads) {        // a thread takes two neighbouring columns
+    const int r = idx / (kD / 2), d = (idx - r * (kD / 2)) * 2;
     const int head = kvh * G + r;
     const size_t row0 = (static_cast<size_t>(item) * a.hq + head) * a.max_parts + p_lo;
     const float2* ml = reinterpret_cast<const float2*>(a.part_ml) + row0;
     const float* po = a.part_o + row0 * kD + d;
-    float mrun = -INFINITY, den = 0.f, num = 0.f;
+    float mrun = -INFINITY, den = 0.f, num0 = 0.f, num1 = 0.f;
     for (int i0 = 0; i0 < pieces; i0 += 16) {
-      float2 q[16];
-      float v[16];
+      float2 q[16], v[16];
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
         const bool in = i0 + i < pieces;
         const int slot = in ? max(cut.begin(k_first + i0 + i) - row_begin, 0) : 0;    // the piece's first partition
         q[i] = in ? __ldcg(&ml[slot]) : make_float2(-INFINITY, 0.f);
-        v[i] = in ? __ldcg(po + static_cast<size_t>(slot) * kD) : 0.f;
+        v[i] = in ? __ldcg(reinterpret_cast<const float2*>(po + static_cast<size_t>(slot) * kD)) : make_float2(0.f, 0.f);
       }
       float mc = mrun;
 #pragma unroll
       for (int i = 0; i < 16; ++i) mc = fmaxf(mc, q[i].x);        // finite: every piece has a live key
       const float f = expf(mrun - mc);                            // exp(-inf) = 0 the first time
       den *= f;
-      num *= f;
+      num0 *= f;
+      num1 *= f;
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
         const float wgt = expf(q[i].x - mc);
         den += wgt * q[i].y;
-        num += wgt * v[i];
+        num0 += wgt * v[i].x;
+        num1 += wgt * v[i].y;
       }
       mrun = mc;
     }
-    a.out[static_cast<size_t>(tok) * a.out_stride + head * kD + d] = __float2bfloat16_rn(num / den);
+    const __nv_bfloat162 hh = __floats2bfloat162_rn(num0 / den, num1 / den);
+    *reinterpret_cast<__nv_bfloat162*>(a.out + static_cast<size_t>(tok) * a.out_stride + head * kD + d) = hh;
   }
 }
 
@@ -552,12 +554,17 @@ decode_attn_stream_kernel(const DecodeArgs<bf16> a, int nitems) {
     }
   }
   __syncthreads();
-  __threadfence();
+  // The queued merges, several at a time: a merge takes one thread per pair of output columns (the
+  // pieces are read with ld.cg from L2, where the counting made them visible).
   const int nq = min(sh->queued, kStreamQueue);
-  for (int i = 0; i < nq; ++i) {
-    const int2 e = sh->queue[i];
-    stream_merge(a, sh, cut, e.x, e.y, threadIdx.x, kStreamThreads);
-  }
+  const int pairs = G * (kD / 2);
+  const int per = min(kStreamThreads, (pairs + 31) / 32 * 32), groups = kStreamThreads / per;
+  const int grp = threadIdx.x / per;
+  if (grp < groups)
+    for (int i = grp; i < nq; i += groups) {
+      const int2 e = sh->queue[i];
+      stream_merge(a, sh, cut, e.x, e.y, threadIdx.x - grp * per, per);
+    }
 }
 
 }  // namespace rl
