@@ -1049,7 +1049,16 @@ int launch_prefill(const void* q, int q_stride, const void* kc, const void* vc, 
         if (e != cudaSuccess) return static_cast<int>(e);
         tattr = true;
       }
-      launch_kernel(prefill_attn_tc_kernel, dim3(dim3(tiles, hq)), dim3(kTcThreads), kPrefillTcSmem, stream, a, status);
+      static int tsms = 0;
+      if (tsms == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&tsms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || tsms <= 0)
+          tsms = 1;
+      }
+      const long long items = static_cast<long long>(tiles) * hq;
+      const int ctas = static_cast<int>(items < tsms ? items : tsms);      // persistent: one CTA per SM
+      launch_kernel(prefill_attn_tc_kernel, dim3(ctas), dim3(kTcThreads), kPrefillTcSmem, stream, a, tiles, status);
       return static_cast<int>(cudaGetLastError());
     }
   }
