@@ -242,13 +242,18 @@ def profile_step(args) -> int:
     tmp = tempfile.mkdtemp(prefix="redline_bench_")
     try:
         model = write_model(tmp, args.layers)
-        batch, prompt = args.profile_batch, CONTEXT - 96
+        batch, prompt = args.profile_batch, args.profile_prompt or (CONTEXT - 96)
+        # every request must still be running when the last one has been admitted: one decoded token per
+        # request and step while the others' prompts are being prefilled
+        if prompt + 2 * batch * ((prompt + 2047) // 2048) + 16 > CONTEXT:
+            raise SystemExit("--profile-batch / --profile-prompt: the first requests would reach the context "
+                             "limit before the last one is admitted; use a shorter --profile-prompt")
         eng = Engine(model, dtype="bfloat16", max_num_seqs=batch, max_num_batched_tokens=2048, max_seq_len=CONTEXT,
                      kv_cache_tokens=batch * (prompt + 128), cuda_graphs=not args.profile_eager, async_scheduling=False)
         rng = np.random.RandomState(0)
         for i in range(batch):
             eng.add_request(rng.randint(0, eng.vocab_size, size=prompt).tolist(),
-                            SamplingParams(max_new_tokens=64, ignore_eos=True))
+                            SamplingParams(max_new_tokens=CONTEXT - prompt - 8, ignore_eos=True))
         eng.record_steps = True
         while not (eng.records and eng.records[-1].kind == "decode" and eng.records[-1].num_seqs == batch):
             eng.step()
@@ -396,6 +401,7 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration has (named in config)")
     ap.add_argument("--profile-step", action="store_true", help="bracket one decode step with cudaProfilerStart/Stop and exit")
     ap.add_argument("--profile-batch", type=int, default=BATCH)
+    ap.add_argument("--profile-prompt", type=int, default=0, help="with --profile-step: prompt length (default: context - 96)")
     ap.add_argument("--profile-eager", action="store_true", help="with --profile-step: no CUDA graph")
     args = ap.parse_args()
     if args.gpus != 1:
