@@ -966,8 +966,8 @@ int launch_decode(const void* q, int q_stride, const void* kc, const void* vc, c
       return e ? std::atoll(e) : static_cast<long long>(kStreamMinUnits);
     }();
     const bool many = static_cast<long long>(nitems) * hkv * max_parts >= min_units;
-    if ((impl == 3 || (impl == 0 && many)) && hq / hkv <= 16 && page_size >= 16 && kPart % page_size == 0 &&
-        counters != nullptr && max_parts <= kMaxMergeParts && nitems <= kStreamMaxItems && aligned) {
+    if ((impl == 3 || (impl == 0 && (many || max_parts > kMaxMergeParts))) && hq / hkv <= 16 && page_size >= 16 && kPart % page_size == 0 &&
+        counters != nullptr && nitems <= kStreamMaxItems && aligned) {      // (any number of partitions)
       static int sms = 0;
       static bool sattr = false;
       if (!sattr) {

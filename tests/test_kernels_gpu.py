@@ -348,6 +348,13 @@ def test_attention_decode_streaming_kernel_many_units_per_cta():
     assert int(kernels.tc_status(torch.device(DEV)).item()) == 0
 
 
+def test_attention_decode_beyond_256_partitions():
+    """A context of 40,000 keys has 313 partitions, more than the one-partition kernel can merge: the
+    default choice must take the streaming kernel there (and the CUDA-core kernel must agree)."""
+    decode_only_case(8, 2, 64, [40000, 33000, 7], 16, 0, 0, seed=35)
+    decode_only_case(8, 2, 64, [40000], 16, 0, 1, seed=36)
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_attention_mixed_launch_and_other_page_sizes(dtype):
     run_attention(dtype, 4, 2, 64, [300, 31, 0, 90], [1, 33, 2, 1], page_size=32, seed=5)
