@@ -2,16 +2,20 @@
 // D a multiple of 16 up to 256) and both element types (float, bfloat16).
 //
 //   rl_attn_decode   one query token per item; the keys are cut into absolute
-//                    128-key partitions, one CTA per (partition, kv head, item)
-//                    computes all G query heads of the group from one read of K
-//                    and V and leaves (max, sum, unnormalised output); a second
-//                    kernel merges the partitions with w_i = exp(m_i - m).
-//                    Restates src/cuda/kernels/attention.cu:69-209.
+//                    128-key partitions and all G query heads of a group are computed
+//                    from one read of K and V (restates src/cuda/kernels/attention.cu:69-209).
+//                    Three kernels: a CUDA-core kernel, one CTA per (partition, kv head,
+//                    item), with a second kernel that merges the partitions with
+//                    w_i = exp(m_i - m) (any head size, both types); a tensor-core kernel of
+//                    the same shape with the merge fused (bfloat16, head size 64 or 128);
+//                    and, for launches with many partitions, the streaming kernel of
+//                    decode_stream.cuh (persistent CTAs, cp.async rings).
 //   rl_attn_prefill  tiles of query rows against tiles of keys with an online softmax; the
 //                    keys of a tile come from the cache, so a prompt portion attends to
 //                    what earlier portions left there (attention.cu:217-359).  A CUDA-core
-//                    kernel (32 x 32 tiles, any head size, both types) and a tensor-core
-//                    kernel (64 x 64 tiles, bfloat16, head size 64 or 128).
+//                    kernel (32 x 32 tiles, any head size, both types), an mma.sync kernel
+//                    (64 query rows x 64 keys per CTA, bfloat16, head size 64 or 128) and,
+//                    at head size 64, the tcgen05 kernel of prefill_tc.cuh.
 //
 // Scores, the softmax and the P.V sums are float whatever the element type.  A
 // window w > 0 keeps only keys with pos - w < key <= pos.  The cache of a layer is

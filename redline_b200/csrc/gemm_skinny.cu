@@ -3,12 +3,15 @@
 //
 // A decode step reads every weight once and does little arithmetic, so the kernel is
 // built around the weight stream: the weights are the MMA's 16-row operand and are
-// loaded straight from global memory in 16-byte pieces (no shared-memory stage), the
-// few activation rows are the 8-wide operand and sit in shared memory.  One CTA owns
-// 16 output features (32 for the gated product: 16 gate rows and their 16 up rows) and
-// its warps split K in interleaved 64-wide blocks; partial sums meet in shared memory
-// and are added in warp order, so a row's result does not depend on how many other rows
-// are in the batch, and not on the run.
+// loaded straight from global memory in 16-byte pieces (no shared-memory stage), two
+// 128-wide super-blocks per warp held in registers and refilled in place two steps
+// ahead.  The few activation rows are the 8-wide operand: with bfloat16 activations of up
+// to 8 rows they too come from global memory, with the weights of the same k; otherwise
+// (a fused norm of the float32 stream, or 9 to 16 rows) they are staged in shared memory.
+// One CTA owns 16 output features (32 for the gated product: 16 gate rows and their 16 up
+// rows) and its warps split K in interleaved 128-wide blocks; partial sums meet in shared
+// memory and are added in warp order, so a row's result does not depend on how many other
+// rows are in the batch, and not on the run.
 //
 // Fused around the product:
 //   prologue  NORM: x = bfloat16(rmsnorm(residual[rows]) * norm_weight), computed in the
@@ -303,11 +306,9 @@ int launch_one(const SkinnyArgs& a0, int sm_count, cudaStream_t stream) {
   const int rounds = (tiles + TPC - 1) / TPC;       // CTA-rounds of TPC tiles
   // at most about two CTAs per SM, all resident at once: a second, nearly empty wave would cost
   // as much as the first
-  static const int per_sm = [] {
-    const char* e = std::getenv("REDLINE_SKINNY_CTAS_PER_SM");
-    return e ? std::atoi(e) : 2;
-  }();
-  int rt = (rounds + per_sm * sm_count - 1) / (per_sm * sm_count);
+  // (one CTA per SM, so that the next product's CTAs could move in beside it, was measured: the decode
+  // step is a fifth slower with half the warps streaming)
+  int rt = (rounds + 2 * sm_count - 1) / (2 * sm_count);
   if (rt > 16) rt = 16;
   a.row_tiles = rt;
   const int ctas = (rounds + rt - 1) / rt;
