@@ -13,19 +13,36 @@ and slots of fixed size for per-request state.
 * A request also holds one state slot (an index into per-layer state pools of fixed
   size) from opening to closing, whether or not any layer keeps state.
 
-This module is host code only and holds no tensors; ``storage.py`` owns the memory.
+The state lives in the native host core (``csrc/host_core.cpp``, bound by ``native.py``);
+the classes here are its Python face.  This module is host code only and holds no
+tensors; ``storage.py`` owns the memory.
 """
 
 from __future__ import annotations
 
+import ctypes
+from ctypes import POINTER, byref, c_int, c_int32
 from dataclasses import dataclass, field
-from typing import Dict, List, Optional, Sequence, Tuple
+from typing import Dict, List, Sequence
 
 from ..parts.spec import CacheSpec
+from . import native
 
 
 class CacheError(RuntimeError):
     pass
+
+
+def _i32_array(values: Sequence[int]):
+    return (c_int32 * max(len(values), 1))(*values)
+
+
+def _raise_free_error(code: int, bad: int) -> None:
+    if code == -1:
+        raise CacheError(f"page id {bad} is not a page of this pool")
+    if code == -2:
+        raise CacheError(f"page {bad} freed twice")
+    raise CacheError(f"page pool error {code}")
 
 
 class PageAllocator:
@@ -34,39 +51,40 @@ class PageAllocator:
     def __init__(self, num_pages: int, reserved: int = 1):
         if num_pages <= reserved:
             raise CacheError(f"a pool needs more than {reserved} pages, got {num_pages}")
+        self._lib = native.lib()
+        self._h = self._lib.rl_pool_create(num_pages, reserved)
+        if not self._h:
+            raise CacheError("the page pool could not be created")
         self.num_pages = num_pages
         self.reserved = reserved
-        self._free = list(range(num_pages - 1, reserved - 1, -1))  # pop() gives the lowest id first
-        self._held = [False] * num_pages
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            self._lib.rl_pool_destroy(h)
 
     @property
     def num_usable(self) -> int:
-        return self.num_pages - self.reserved
+        return self._lib.rl_pool_num_usable(self._h)
 
     @property
     def num_free(self) -> int:
-        return len(self._free)
+        return self._lib.rl_pool_num_free(self._h)
 
     def allocate(self) -> int:
         """A page id, or -1 when none is free."""
-        if not self._free:
-            return -1
-        p = self._free.pop()
-        self._held[p] = True
-        return p
+        return self._lib.rl_pool_allocate(self._h)
 
     def free(self, pages: Sequence[int]) -> None:
         """Gives pages back; the first of ``pages`` is the next to be handed out again."""
-        for p in reversed(list(pages)):
-            if p < self.reserved or p >= self.num_pages:
-                raise CacheError(f"page id {p} is not a page of this pool")
-            if not self._held[p]:
-                raise CacheError(f"page {p} freed twice")
-            self._held[p] = False
-            self._free.append(p)
+        pages = list(pages)
+        bad = c_int(0)
+        code = self._lib.rl_pool_free(self._h, _i32_array(pages), len(pages), byref(bad))
+        if code < 0:
+            _raise_free_error(code, bad.value)
 
     def is_held(self, page: int) -> bool:
-        return self._held[page]
+        return bool(self._lib.rl_pool_is_held(self._h, page))
 
 
 @dataclass
@@ -81,15 +99,38 @@ class GroupInfo:
         return self.spec.window if self.spec.kind == "window" else 0
 
 
-@dataclass
 class RequestCache:
-    """What one request holds."""
+    """What one request holds: a state slot and, per group, a block table (page id per block index; 0
+    once released by a window).  The tables live in the native core; ``tables`` copies them out."""
 
-    key: object
-    state_slot: int
-    tables: List[List[int]]          # per group: page id per block index; 0 once released by a window
-    num_tokens: int = 0              # positions for which pages are reserved
-    released_upto: List[int] = field(default_factory=list)  # per group: blocks below this index were released
+    __slots__ = ("key", "rid", "state_slot", "_m")
+
+    def __init__(self, key: object, rid: int, state_slot: int, manager: "CacheManager"):
+        self.key = key
+        self.rid = rid
+        self.state_slot = state_slot
+        self._m = manager
+
+    def table(self, group: int) -> List[int]:
+        ptr = POINTER(c_int32)()
+        n = self._m._lib.rl_hc_table(self._m._h, self.rid, group, byref(ptr))
+        if n < 0:
+            raise CacheError(f"request {self.key!r} is not open")
+        return ptr[:n]
+
+    @property
+    def tables(self) -> List[List[int]]:
+        return [self.table(g) for g in range(len(self._m.groups))]
+
+    @property
+    def num_tokens(self) -> int:
+        """Positions for which pages are reserved."""
+        return self._m._lib.rl_hc_num_tokens(self._m._h, self.rid)
+
+    @property
+    def released_upto(self) -> List[int]:
+        """Per group: blocks below this index were released."""
+        return [self._m._lib.rl_hc_released_upto(self._m._h, self.rid, g) for g in range(len(self._m.groups))]
 
 
 class CacheManager:
@@ -97,21 +138,33 @@ class CacheManager:
                  num_state_slots: int):
         if len(groups) != len(pages_per_group):
             raise CacheError("one page count per group is needed")
+        for n in pages_per_group:
+            if n <= 1:
+                raise CacheError(f"a pool needs more than 1 pages, got {n}")
         self.groups = list(groups)
         self.page_size = page_size
-        self.allocators = [PageAllocator(n) for n in pages_per_group]
-        self._free_slots = list(range(num_state_slots - 1, -1, -1))
         self.num_state_slots = num_state_slots
+        self._lib = native.lib()
+        self._h = self._lib.rl_hc_create(len(self.groups), _i32_array(list(pages_per_group)),
+                                         _i32_array([g.window for g in self.groups]), page_size, num_state_slots)
+        if not self._h:
+            raise CacheError("the cache manager could not be created")
         self._open: Dict[object, RequestCache] = {}
         self.on_open = None   # called with the RequestCache of every newly opened request
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            self._lib.rl_hc_destroy(h)
 
     # ------------------------------------------------------------ requests
     def open(self, key: object) -> RequestCache:
         if key in self._open:
             raise CacheError(f"request {key!r} is already open")
-        if not self._free_slots:
+        rid = self._lib.rl_hc_open(self._h)
+        if rid < 0:
             raise CacheError("no free state slot: too many live requests")
-        rc = RequestCache(key, self._free_slots.pop(), [[] for _ in self.groups], 0, [0] * len(self.groups))
+        rc = RequestCache(key, rid, self._lib.rl_hc_state_slot(self._h, rid), self)
         self._open[key] = rc
         if self.on_open is not None:
             self.on_open(rc)
@@ -131,10 +184,10 @@ class CacheManager:
         rc = self._open.pop(key, None)
         if rc is None:
             raise CacheError(f"request {key!r} is not open")
-        for g, table in enumerate(rc.tables):
-            live = [p for i, p in enumerate(table) if i >= rc.released_upto[g]]
-            self.allocators[g].free(live)
-        self._free_slots.append(rc.state_slot)
+        bad = c_int(0)
+        code = self._lib.rl_hc_close(self._h, rc.rid, byref(bad))
+        if code < 0:
+            _raise_free_error(code, bad.value)
 
     def num_open(self) -> int:
         return len(self._open)
@@ -146,78 +199,45 @@ class CacheManager:
     def pages_needed(self, rc: RequestCache, new_len: int) -> List[int]:
         """Pages each group would have to hand out to hold positions < new_len."""
         need = self.blocks_for(new_len)
-        return [max(0, need - len(t)) for t in rc.tables]
+        ptr = POINTER(c_int32)()
+        return [max(0, need - self._lib.rl_hc_table(self._h, rc.rid, g, byref(ptr))) for g in range(len(self.groups))]
 
     def can_reserve(self, rc: RequestCache, new_len: int, keep_free: int = 0) -> bool:
-        return all(a.num_free - n >= keep_free
-                   for a, n in zip(self.allocators, self.pages_needed(rc, new_len)))
+        return all(self.num_free_pages(g) - n >= keep_free for g, n in enumerate(self.pages_needed(rc, new_len)))
 
     def reserve(self, rc: RequestCache, new_len: int) -> bool:
         """Makes sure pages exist for positions < new_len in every group.  All or
         nothing: on failure what this call took is given back and False is returned."""
-        need = self.blocks_for(new_len)
-        taken: List[Tuple[int, int]] = []
-        for g, table in enumerate(rc.tables):
-            while len(table) < need:
-                p = self.allocators[g].allocate()
-                if p < 0:
-                    for gg, pp in reversed(taken):
-                        rc.tables[gg].pop()
-                        self.allocators[gg].free([pp])
-                    return False
-                table.append(p)
-                taken.append((g, p))
-        rc.num_tokens = max(rc.num_tokens, new_len)
-        return True
+        code = self._lib.rl_hc_reserve(self._h, rc.rid, new_len)
+        if code < 0:
+            raise CacheError(f"request {rc.key!r} is not open")
+        return code == 1
 
     def release_passed(self, rc: RequestCache, num_computed: int) -> int:
         """After ``num_computed`` positions are in the cache: in window groups, frees the
         pages whose keys no later token can see (key j is dead when j <= n - window for
         the next position n).  Returns how many pages were freed."""
-        freed = 0
-        for g, info in enumerate(self.groups):
-            w = info.window
-            if w <= 0:
-                continue
-            dead_keys = num_computed - w + 1          # keys 0 .. dead_keys-1 are dead
-            dead_blocks = max(0, dead_keys) // self.page_size
-            dead_blocks = min(dead_blocks, len(rc.tables[g]))
-            if dead_blocks > rc.released_upto[g]:
-                pages = rc.tables[g][rc.released_upto[g]:dead_blocks]
-                self.allocators[g].free(pages)
-                for i in range(rc.released_upto[g], dead_blocks):
-                    rc.tables[g][i] = 0
-                freed += len(pages)
-                rc.released_upto[g] = dead_blocks
-        return freed
+        n = self._lib.rl_hc_release_passed(self._h, rc.rid, num_computed)
+        if n < 0:
+            raise CacheError(f"request {rc.key!r}: releasing pages failed ({n})")
+        return n
 
     def slot(self, rc: RequestCache, group: int, pos: int) -> int:
         """The cache slot (page * page_size + offset) of position ``pos``."""
-        return rc.tables[group][pos // self.page_size] * self.page_size + pos % self.page_size
+        return rc.table(group)[pos // self.page_size] * self.page_size + pos % self.page_size
 
     # ----------------------------------------------------------- inspection
     def num_free_pages(self, group: int = 0) -> int:
-        return self.allocators[group].num_free
+        return self._lib.rl_hc_num_free(self._h, group)
 
     def num_total_pages(self, group: int = 0) -> int:
-        return self.allocators[group].num_usable
+        return self._lib.rl_hc_num_usable(self._h, group)
 
     def check_invariants(self) -> None:
         """No page lost, none held twice: every usable page is either free or in exactly
         one live table entry.  Raises CacheError otherwise (used by the tests)."""
-        for g, a in enumerate(self.allocators):
-            seen: Dict[int, object] = {}
-            for rc in self._open.values():
-                for i, p in enumerate(rc.tables[g]):
-                    if i < rc.released_upto[g]:
-                        continue
-                    if p in seen:
-                        raise CacheError(f"group {g}: page {p} held by {seen[p]!r} and {rc.key!r}")
-                    if not a.is_held(p):
-                        raise CacheError(f"group {g}: page {p} of {rc.key!r} is on the free list")
-                    seen[p] = rc.key
-            if len(seen) + a.num_free != a.num_usable:
-                raise CacheError(f"group {g}: {a.num_usable - a.num_free - len(seen)} pages lost")
-        slots = [rc.state_slot for rc in self._open.values()]
-        if len(set(slots)) != len(slots) or len(slots) + len(self._free_slots) != self.num_state_slots:
-            raise CacheError("state slots lost or held twice")
+        buf = ctypes.create_string_buffer(256)
+        if self._lib.rl_hc_check(self._h, buf, 256):
+            raise CacheError(buf.value.decode())
+        if self._lib.rl_hc_num_open(self._h) != len(self._open):
+            raise CacheError("open requests of the core and of its Python face differ")

@@ -3,7 +3,8 @@ uploads it with one copy, and hands the model typed device views of it.
 
 A segment is (request cache, its next tokens, the position of the first of them,
 which of them want logits).  Segments of one token go to the decode work list,
-longer ones are cut into tiles of 64 query rows for the prefill kernel.  The
+longer ones are cut into tiles of 128 query rows for the prefill kernels.  The buffer is
+filled by the native host core (csrc/host_core.cpp) from the requests' own block tables.  The
 buffer holds, in this order (sizes in int32 words; T tokens, S segments, R rows,
 G cache groups, B block-table width, L tiles):
 
@@ -20,12 +21,14 @@ time and can be replayed as a CUDA graph.
 
 from __future__ import annotations
 
+import ctypes
 from dataclasses import dataclass, field
 from typing import List, Optional, Sequence
 
 import numpy as np
 import torch
 
+from ..cache import native
 from ..cache.manager import CacheManager, RequestCache
 from ..ops.kernels import DECODE_PARTITION, PREFILL_TILE_ROWS
 
@@ -86,6 +89,18 @@ class Layout:
         self.seed_hi = take(R)
         self.sample_pos = take(R)
         self.words = off
+        self._native = None
+
+    def native(self):
+        """The offsets as the native host core takes them (and, beside, those of the per-group fields)."""
+        if self._native is None:
+            nl = native.RlLayout()
+            for name, _ in native.RlLayout._fields_:
+                setattr(nl, name, getattr(self, name))
+            self._native = nl
+            self.slots_c = (ctypes.c_int32 * max(self.G, 1))(*self.slots)
+            self.tables_c = (ctypes.c_int32 * max(self.G, 1))(*self.block_table)
+        return self._native
 
 
 @dataclass
@@ -157,6 +172,7 @@ class BatchBuilder:
         self.dev_buf = torch.zeros(cap.words, dtype=torch.int32, device=device)
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
         self._turn = 0
+        self._lib = native.lib()
 
     def _views(self, lay: Layout, dev: torch.Tensor, T: int, S: int, R: int, L: int) -> dict:
         def v(off, n):
@@ -206,87 +222,67 @@ class BatchBuilder:
         if self.used[slot] and self.events[slot] is not None:
             self.events[slot].synchronize()
         h = self.host_np[slot]
-        h[:lay.words] = 0
         hb = HostBatch()
+        # ---- the fields are filled by the native host core from the requests' own block tables
+        rows = []
+        tok_parts = []
+        want_flat: List[int] = []
         t = 0
-        r = 0
-        nd = 0
-        li = 0
-        has_src = False
-        any_sampling = False
-        max_ctx = 1
-        for si, s in enumerate(segments):
+        to = 0
+        for s in segments:
             n = len(s.tokens)
-            end = s.start_pos + n
-            if n <= 0:
-                raise ValueError("empty segment")
-            if end > self.max_seq_len:
-                raise ValueError(f"request {s.cache.key!r} would reach position {end}, beyond max_seq_len "
-                                 f"{self.max_seq_len}")
-            if s.src_row >= 0:
-                if n != 1:
-                    raise ValueError("a device-fed segment has exactly one token")
-                h[lay.token_src + t] = s.src_row
-                has_src = True
-            else:
-                h[lay.token_ids + t:lay.token_ids + t + n] = np.asarray(s.tokens, dtype=np.int32)
-                h[lay.token_src + t:lay.token_src + t + n] = -1
-            pos = np.arange(s.start_pos, end, dtype=np.int32)
-            h[lay.positions + t:lay.positions + t + n] = pos
-            h[lay.seq_of_token + t:lay.seq_of_token + t + n] = si
-            for g in range(self.G):
-                table = s.cache.tables[g]
-                if len(table) * ps < end:
-                    raise ValueError(f"request {s.cache.key!r}: pages reserved for {len(table) * ps} positions, "
-                                     f"step needs {end}")
-                tb = np.asarray(table, dtype=np.int32)
-                h[lay.slots[g] + t:lay.slots[g] + t + n] = tb[pos // ps] * ps + pos % ps
-                o = lay.block_table[g] + si * self.B
-                h[o:o + len(tb)] = tb
-            h[lay.state_slot + si] = s.cache.state_slot
-            if n == 1:
-                h[lay.decode_info + 4 * nd:lay.decode_info + 4 * nd + 3] = (t, si, end)
-                nd += 1
-                max_ctx = max(max_ctx, end)
-            else:
-                for r0 in range(0, n, PREFILL_TILE_ROWS):
-                    h[lay.tile_seq + li] = si
-                    h[lay.tile_tok + li] = t + r0
-                    h[lay.tile_rows + li] = min(PREFILL_TILE_ROWS, n - r0)
-                    li += 1
             sp = s.sampling
-            for wi in s.want:
-                if not 0 <= wi < n:
-                    raise ValueError(f"wanted index {wi} outside a segment of {n} tokens")
-                h[lay.logit_rows + r] = t + wi
-                if sp is not None:
-                    any_sampling = True
-                    h[lay.temperature + r:lay.temperature + r + 1].view(np.float32)[0] = sp.temperature
-                    h[lay.top_k + r] = sp.top_k
-                    h[lay.top_p + r:lay.top_p + r + 1].view(np.float32)[0] = sp.top_p
-                    h[lay.seed_lo + r:lay.seed_lo + r + 1].view(np.uint32)[0] = sp.seed & 0xFFFFFFFF
-                    h[lay.seed_hi + r:lay.seed_hi + r + 1].view(np.uint32)[0] = (sp.seed >> 32) & 0xFFFFFFFF
-                else:
-                    h[lay.top_p + r:lay.top_p + r + 1].view(np.float32)[0] = 1.0
-                h[lay.sample_pos + r] = s.start_pos + wi + 1  # position of the token being drawn
-                r += 1
+            fed = s.src_row >= 0
+            if sp is not None:
+                rows.append((s.cache.rid, s.start_pos, n, s.src_row, to, len(want_flat), len(s.want), 1,
+                             sp.temperature, sp.top_p, sp.top_k, sp.seed & 0xFFFFFFFF, (sp.seed >> 32) & 0xFFFFFFFF))
+            else:
+                rows.append((s.cache.rid, s.start_pos, n, s.src_row, to, len(want_flat), len(s.want), 0,
+                             0.0, 1.0, 0, 0, 0))
+            if not fed and n > 0:
+                tok_parts.append(s.tokens)
+                to += n
+            want_flat.extend(s.want)
             hb.q_start.append(t)
             hb.q_len.append(n)
             hb.start_pos.append(s.start_pos)
             hb.state_slot.append(s.cache.state_slot)
             hb.keys.append(s.cache.key)
             t += n
+        segs = np.array(rows, dtype=native.SEGMENT_DTYPE)
+        if len(tok_parts) == 1:
+            tokens = np.asarray(tok_parts[0], dtype=np.int32)
+        elif tok_parts:
+            tokens = np.concatenate([np.asarray(x, dtype=np.int32) for x in tok_parts])
+        else:
+            tokens = np.zeros(1, dtype=np.int32)
+        tokens = np.ascontiguousarray(tokens)
+        want = np.asarray(want_flat if want_flat else [0], dtype=np.int32)
+        nl = lay.native()
+        res = (ctypes.c_int32 * 8)()
+        code = self._lib.rl_hc_build(self.cache._h, h.ctypes.data, ctypes.byref(nl), lay.slots_c, lay.tables_c,
+                                     self.G, self.B, S_real, segs.ctypes.data, tokens.ctypes.data, want.ctypes.data,
+                                     self.max_seq_len, PREFILL_TILE_ROWS, res)
+        if code < 0:
+            s = segments[res[5]]
+            if code == -10:
+                raise ValueError("empty segment")
+            if code == -11:
+                raise ValueError(f"request {s.cache.key!r} would reach position {res[6]}, beyond max_seq_len "
+                                 f"{self.max_seq_len}")
+            if code == -12:
+                raise ValueError("a device-fed segment has exactly one token")
+            if code == -13:
+                raise ValueError(f"request {s.cache.key!r}: pages reserved for {res[6]} positions, "
+                                 f"step needs {s.start_pos + len(s.tokens)}")
+            if code == -14:
+                raise ValueError(f"wanted index {res[6]} outside a segment of {len(s.tokens)} tokens")
+            raise ValueError(f"request {s.cache.key!r} is not open in the cache manager ({code})")
+        nd, li, max_ctx, has_src, any_sampling = res[0], res[1], res[2], bool(res[3]), bool(res[4])
         if pad_to:
             if nd != S_real or R_real != S_real or T_real != S_real:
                 raise ValueError("only steps of single tokens that all want logits can be padded")
-            # dummy rows: token 0 at position 0 of a sequence whose table is all page 0
-            for i in range(S_real, pad_to):
-                h[lay.token_src + i] = -1
-                h[lay.seq_of_token + i] = i
-                h[lay.decode_info + 4 * i:lay.decode_info + 4 * i + 3] = (i, i, 1)
-                h[lay.logit_rows + i] = i
-                h[lay.top_p + i:lay.top_p + i + 1].view(np.float32)[0] = 1.0
-                h[lay.sample_pos + i] = 1
+            self._lib.rl_hc_pad(h.ctypes.data, ctypes.byref(nl), S_real, pad_to)
             nd = pad_to
             decode_parts = self.parts_capacity
         else:

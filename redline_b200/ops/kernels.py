@@ -356,5 +356,6 @@ def build_all(head_dims=(64, 128), verbose: bool = True) -> None:
     build.compile_module("gemm_skinny", "gemm_skinny.cu", verbose=verbose)
     build.compile_module("gemm_tc", "gemm_tc.cu", verbose=verbose)
     build.compile_module("sampling", "sampling.cu", verbose=verbose)
+    build.compile_module("host_core", "host_core.cpp", verbose=verbose)     # host-only: cache manager, batch filler
     for d in head_dims:
         build.compile_module(f"attention_d{d}", "attention.cu", {"RL_HEAD_DIM": d}, verbose=verbose)
