@@ -63,6 +63,47 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __res
   const bool write_back = (d != nullptr) && (rows_idx == nullptr);
   TA* o = out + static_cast<size_t>(r) * hidden;
   float ss = 0.f;
+  if (hidden == static_cast<int>(blockDim.x) * 8) {
+    // the row is exactly eight columns per thread: they stay in registers between the sum and the scaling
+    const int c = threadIdx.x * 8;
+    float v[8], w[8], y[8];
+    load16(res + c, v);
+    load16(res + c + 4, v + 4);
+    if (sizeof(TW) == 2) {
+      load16(weight + c, w);
+    } else {
+      load16(weight + c, w);
+      load16(weight + c + 4, w + 4);
+    }
+    if (d) {
+      float dv[8];
+      if (sizeof(TD) == 2) {
+        load16(d + c, dv);
+      } else {
+        load16(d + c, dv);
+        load16(d + c + 4, dv + 4);
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[e] += dv[e];
+      if (write_back) {
+        store16(res + c, v);
+        store16(res + c + 4, v + 4);
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) ss += v[e] * v[e];
+    ss = block_sum(ss, scratch);
+    const float inv = rsqrtf(ss / static_cast<float>(hidden) + eps);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) y[e] = v[e] * inv * w[e];
+    if (sizeof(TA) == 2) {
+      store16(o + c, y);
+    } else {
+      store16(o + c, y);
+      store16(o + c + 4, y + 4);
+    }
+    return;
+  }
   if (hidden % 8 == 0) {
     // eight columns per thread and step: 16-byte pieces of every operand that is 16 bits wide,
     // two of every operand that is 32 bits wide
@@ -221,9 +262,15 @@ __global__ void rope_kv_write_kernel(TA* __restrict__ qkv, const int32_t* __rest
     load16(v + i, x0);
     load16(v + i + half, x1);
     if (c) {
+      float cv[VEC], sv[VEC];
+#pragma unroll
+      for (int e = 0; e < VEC; e += 4) {          // (half is a multiple of 8: 16-byte aligned pieces)
+        load16(c + i + e, cv + e);
+        load16(s + i + e, sv + e);
+      }
 #pragma unroll
       for (int e = 0; e < VEC; ++e) {
-        const float cc = c[i + e], sn = s[i + e];
+        const float cc = cv[e], sn = sv[e];
         const float y0 = x0[e] * cc - x1[e] * sn;
         const float y1 = x1[e] * cc + x0[e] * sn;
         x0[e] = y0;
@@ -289,7 +336,8 @@ int rl_add_rmsnorm(float* residual, const void* delta, const void* weight, int w
                    int act_dtype, const int32_t* rows_idx, int rows, int hidden, float eps,
                    cudaStream_t stream) {
   if (rows <= 0) return 0;
-  const int th = row_threads(hidden);
+  // eight columns per thread where the row allows it (then, up to 4,096 columns, the row stays in registers)
+  const int th = hidden % 8 == 0 ? row_threads(hidden / 8) : row_threads(hidden);
 #define RL_NORM_CASE(TA, TW)                                                                 \
   launch_kernel(add_rmsnorm_kernel<TA, TA, TW>, dim3(rows), dim3(th), 0, stream,                                    \
       residual, static_cast<const TA*>(delta), static_cast<const TW*>(weight),               \
