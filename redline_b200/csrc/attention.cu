@@ -932,11 +932,43 @@ using namespace rl;
 
 namespace {
 
+// The rotary tables and columns for a launch that also rotates q and k and writes the token's k and v
+// into the cache (streaming kernel only).
+struct StreamRopeHost {
+  const float* cos;
+  const float* sin;
+  int max_pos, k_col, v_col;
+  int* status;
+};
+
+// Whether a bfloat16 launch goes to the streaming kernel (see rl_attn_decode for impl).
+inline bool decode_streams(const void* q, int q_stride, const void* kc, const void* vc, const void* part_o,
+                           const void* counters, const void* out, int out_stride, int max_parts, int nitems, int hq,
+                           int hkv, int page_size, int impl) {
+#ifdef RL_HAVE_MMA_DECODE
+  // page sizes that divide a partition and 16-byte aligned rows
+  const bool aligned = q_stride % 8 == 0 && out_stride % 8 == 0 &&
+                       ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(out) |
+                         reinterpret_cast<uintptr_t>(kc) | reinterpret_cast<uintptr_t>(vc) |
+                         reinterpret_cast<uintptr_t>(part_o)) & 15) == 0;
+  // (with few units the one-partition kernel, four warps to a partition, has the shorter critical path)
+  static const long long min_units = [] {
+    const char* e = std::getenv("REDLINE_STREAM_MIN_UNITS");     // a tuning knob
+    return e ? std::atoll(e) : static_cast<long long>(kStreamMinUnits);
+  }();
+  const bool many = static_cast<long long>(nitems) * hkv * max_parts >= min_units;
+  return (impl == 3 || (impl == 0 && (many || max_parts > kMaxMergeParts))) && hq / hkv <= 16 && page_size >= 16 &&
+         kPart % page_size == 0 && counters != nullptr && nitems <= kStreamMaxItems && aligned;   // (any number of partitions)
+#else
+  return false;
+#endif
+}
+
 template <typename T>
 int launch_decode(const void* q, int q_stride, const void* kc, const void* vc, const int32_t* bt,
                   int max_blocks, const int32_t* items, float* part_o, float* part_ml, int max_parts,
                   int* counters, void* out, int out_stride, int nitems, int hq, int hkv, int page_size,
-                  int window, float scale, int impl, cudaStream_t stream) {
+                  int window, float scale, int impl, const StreamRopeHost* rope, cudaStream_t stream) {
   DecodeArgs<T> a;
   a.q = static_cast<const T*>(q);
   a.q_stride = q_stride;
@@ -959,19 +991,8 @@ int launch_decode(const void* q, int q_stride, const void* kc, const void* vc, c
   dim3 grid(max_parts, hkv, nitems);
 #ifdef RL_HAVE_MMA_DECODE
   if constexpr (sizeof(T) == 2) {
-    // streaming kernel: additionally page sizes that divide a partition and 16-byte aligned rows
-    const bool aligned = q_stride % 8 == 0 && out_stride % 8 == 0 &&
-                         ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(out) |
-                           reinterpret_cast<uintptr_t>(kc) | reinterpret_cast<uintptr_t>(vc) |
-                           reinterpret_cast<uintptr_t>(part_o)) & 15) == 0;
-    // (with few units the one-partition kernel, four warps to a partition, has the shorter critical path)
-    static const long long min_units = [] {
-      const char* e = std::getenv("REDLINE_STREAM_MIN_UNITS");     // a tuning knob
-      return e ? std::atoll(e) : static_cast<long long>(kStreamMinUnits);
-    }();
-    const bool many = static_cast<long long>(nitems) * hkv * max_parts >= min_units;
-    if ((impl == 3 || (impl == 0 && (many || max_parts > kMaxMergeParts))) && hq / hkv <= 16 && page_size >= 16 && kPart % page_size == 0 &&
-        counters != nullptr && nitems <= kStreamMaxItems && aligned) {      // (any number of partitions)
+    if (decode_streams(q, q_stride, kc, vc, part_o, counters, out, out_stride, max_parts, nitems, hq, hkv, page_size,
+                       impl)) {
       static int sms = 0;
       static bool sattr = false;
       if (!sattr) {
@@ -990,13 +1011,25 @@ int launch_decode(const void* q, int q_stride, const void* kc, const void* vc, c
       // no more CTAs than the launch can have units
       const long long most = static_cast<long long>(nitems) * hkv * max_parts;
       const int ctas = static_cast<int>(most < sms ? most : sms);
+      StreamRope sr = {};
+      if (rope != nullptr && rope->cos != nullptr) {
+        sr.cos = rope->cos;
+        sr.sin = rope->sin;
+        sr.max_pos = rope->max_pos;
+        sr.k_col = rope->k_col;
+        sr.v_col = rope->v_col;
+        sr.kcache = const_cast<bf16*>(a.kcache);
+        sr.vcache = const_cast<bf16*>(a.vcache);
+        sr.status = rope->status;
+      }
       if (hq / hkv > 8)
-        launch_kernel(decode_attn_stream_kernel<true>, dim3(ctas), dim3(kStreamThreads), kStreamSmem, stream, a, nitems);
+        launch_kernel(decode_attn_stream_kernel<true>, dim3(ctas), dim3(kStreamThreads), kStreamSmem, stream, a, nitems, sr);
       else
-        launch_kernel(decode_attn_stream_kernel<false>, dim3(ctas), dim3(kStreamThreads), kStreamSmem, stream, a, nitems);
+        launch_kernel(decode_attn_stream_kernel<false>, dim3(ctas), dim3(kStreamThreads), kStreamSmem, stream, a, nitems, sr);
       return static_cast<int>(cudaGetLastError());
     }
     if (impl == 3) return static_cast<int>(cudaErrorInvalidValue);
+    if (rope != nullptr && rope->cos != nullptr) return static_cast<int>(cudaErrorInvalidValue);   // only that kernel rotates
     // tensor-core kernel: groups of up to 16 heads, pages that hold whole 16-key steps
     if (impl != 1 && hq / hkv <= 16 && page_size % 16 == 0 && counters != nullptr && max_parts <= kMaxMergeParts) {
       launch_kernel(decode_attn_mma_kernel, dim3(grid), dim3(128), 0, stream, a);
@@ -1005,6 +1038,7 @@ int launch_decode(const void* q, int q_stride, const void* kc, const void* vc, c
   }
 #endif
   if (impl == 2 || impl == 3) return static_cast<int>(cudaErrorInvalidValue);
+  if (rope != nullptr && rope->cos != nullptr) return static_cast<int>(cudaErrorInvalidValue);
   launch_kernel(decode_attn_kernel<T>, dim3(grid), dim3(kDecThreads), 0, stream, a);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return static_cast<int>(e);
@@ -1123,10 +1157,38 @@ int rl_attn_decode(int dtype, const void* q, int q_stride, const void* kc, const
   if (dtype == 0)
     return launch_decode<float>(q, q_stride, kc, vc, bt, max_blocks, items, part_o, part_ml, max_parts,
                                 counters, out, out_stride, nitems, hq, hkv, page_size, window, scale, impl,
-                                stream);
+                                nullptr, stream);
   return launch_decode<bf16>(q, q_stride, kc, vc, bt, max_blocks, items, part_o, part_ml, max_parts,
                              counters, out, out_stride, nitems, hq, hkv, page_size, window, scale, impl,
-                             stream);
+                             nullptr, stream);
+}
+
+// 1 if rl_attn_decode with these arguments runs the streaming kernel (bfloat16 only), else 0.
+int rl_attn_decode_streams(int dtype, const void* q, int q_stride, const void* kc, const void* vc, const void* part_o,
+                           const void* counters, const void* out, int out_stride, int max_parts, int nitems, int hq,
+                           int hkv, int page_size, int impl) {
+  if (dtype == 0 || nitems <= 0) return 0;
+  return decode_streams(q, q_stride, kc, vc, part_o, counters, out, out_stride, max_parts, nitems, hq, hkv, page_size,
+                        impl) ? 1 : 0;
+}
+
+// rl_attn_decode for launches that the streaming kernel takes (rl_attn_decode_streams), with the rotary
+// position encoding and the cache write of the query tokens done in the kernel: q points at rows of
+// UNROTATED [q | ... k at k_col ... | ... v at v_col ...]; cos / sin are float [max_pos, D / 2] tables; a
+// token's position is its context length - 1; its rotated k and its v are written into kc and vc at that
+// position (through the block table).  status: device int, bit 1 is set for a position outside the
+// tables.  Returns cudaErrorInvalidValue where the streaming kernel does not apply.
+int rl_attn_decode_rope(const void* q, int q_stride, void* kc, void* vc, const int32_t* bt, int max_blocks,
+                        const int32_t* items, float* part_o, float* part_ml, int max_parts, int* counters, void* out,
+                        int out_stride, int nitems, int hq, int hkv, int page_size, int window, float scale,
+                        const float* cos_t, const float* sin_t, int max_pos, int k_col, int v_col, int* status,
+                        cudaStream_t stream) {
+  if (nitems <= 0) return 0;
+  if (cos_t == nullptr || sin_t == nullptr || status == nullptr || k_col % 8 != 0 || v_col % 8 != 0)
+    return static_cast<int>(cudaErrorInvalidValue);
+  StreamRopeHost r = {cos_t, sin_t, max_pos, k_col, v_col, status};
+  return launch_decode<bf16>(q, q_stride, kc, vc, bt, max_blocks, items, part_o, part_ml, max_parts, counters, out,
+                             out_stride, nitems, hq, hkv, page_size, window, scale, 0, &r, stream);
 }
 
 int rl_attn_prefill(int dtype, const void* q, int q_stride, const void* kc, const void* vc,
@@ -1205,8 +1267,8 @@ extern "C" int rl_attn_decode_noalloc(int dtype, const void* q, int q_stride, co
   if (dtype == 0)
     return launch_decode<float>(q, q_stride, kcache, vcache, block_table, max_blocks, items, part_o, part_ml,
                                 max_parts, counters, out, out_stride, nitems, hq, hkv, page_size, window, scale,
-                                0, stream);
+                                0, nullptr, stream);
   return launch_decode<bf16>(q, q_stride, kcache, vcache, block_table, max_blocks, items, part_o, part_ml,
                              max_parts, counters, out, out_stride, nitems, hq, hkv, page_size, window, scale, 0,
-                             stream);
+                             nullptr, stream);
 }

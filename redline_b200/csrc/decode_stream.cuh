@@ -123,6 +123,51 @@ __device__ __forceinline__ float ex2_approx(float x) {      // 2^x; -inf gives 0
   return y;
 }
 
+// The rotary position encoding and the cache write of the query token, done in this kernel instead of
+// in a kernel of their own before it (cos == nullptr: not done here).  The token's unrotated q, k and v
+// lie in one row (q at column 0, k at k_col, v at v_col).  A warp rotates the q rows it loads; the one
+// warp that takes the sub-block with the token's own key rotates k, writes k and v into the cache for
+// later steps and into its shared-memory stage for this one.
+struct StreamRope {
+  const float* cos;        // [max_pos, D / 2]
+  const float* sin;
+  int max_pos;
+  int k_col, v_col;
+  bf16* kcache;            // writable views of the caches
+  bf16* vcache;
+  int* status;             // bit 1 is set for a position outside the tables
+};
+
+// Rotates the pairs (x0[e], x1[e]) of eight packed bfloat16 each by the angles whose cosines and sines
+// start at c and s: y0 = x0 c - x1 s, y1 = x1 c + x0 s in float32, rounded once.
+__device__ __forceinline__ void rope_rotate8(uint4& x0, uint4& x1, const float* c, const float* s) {
+  float a[8], b[8], cc[8], ss[8];
+  const uint32_t w0[4] = {x0.x, x0.y, x0.z, x0.w}, w1[4] = {x1.x, x1.y, x1.z, x1.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    a[2 * i] = __uint_as_float(w0[i] << 16);
+    a[2 * i + 1] = __uint_as_float(w0[i] & 0xFFFF0000u);
+    b[2 * i] = __uint_as_float(w1[i] << 16);
+    b[2 * i + 1] = __uint_as_float(w1[i] & 0xFFFF0000u);
+  }
+  load16(c, cc);
+  load16(c + 4, cc + 4);
+  load16(s, ss);
+  load16(s + 4, ss + 4);
+  uint32_t o0[4], o1[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float y00 = a[2 * i] * cc[2 * i] - b[2 * i] * ss[2 * i];
+    const float y01 = a[2 * i + 1] * cc[2 * i + 1] - b[2 * i + 1] * ss[2 * i + 1];
+    const float y10 = b[2 * i] * cc[2 * i] + a[2 * i] * ss[2 * i];
+    const float y11 = b[2 * i + 1] * cc[2 * i + 1] + a[2 * i + 1] * ss[2 * i + 1];
+    o0[i] = pack_bf16(y00, y01);
+    o1[i] = pack_bf16(y10, y11);
+  }
+  x0 = make_uint4(o0[0], o0[1], o0[2], o0[3]);
+  x1 = make_uint4(o1[0], o1[1], o1[2], o1[3]);
+}
+
 __device__ __forceinline__ int atomic_add_acq_rel(int* p, int v) {
   int old;
   asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], %2;" : "=r"(old) : "l"(p), "r"(v) : "memory");
@@ -198,7 +243,7 @@ __device__ __forceinline__ void stream_merge(const DecodeArgs<bf16>& a, const St
 // HI: groups of more than 8 heads (rows g + 8 of the MMA tile are in use).
 template <bool HI>
 __global__ void __launch_bounds__(kStreamThreads, 1)
-decode_attn_stream_kernel(const DecodeArgs<bf16> a, int nitems) {
+decode_attn_stream_kernel(const DecodeArgs<bf16> a, int nitems, const StreamRope rope) {
   constexpr int DB = kD / 32, DG = kD / 64;
   constexpr float kLog2e = 1.4426950408889634f, kLn2 = 0.6931471805599453f;
   constexpr int CPR = kD / 8;            // 16-byte chunks per row
@@ -350,6 +395,20 @@ decode_attn_stream_kernel(const DecodeArgs<bf16> a, int nitems) {
         qlo[db] = g < G ? *reinterpret_cast<const uint4*>(qp + g * kD) : make_uint4(0, 0, 0, 0);
         qhi[db] = (HI && g + 8 < G) ? *reinterpret_cast<const uint4*>(qp + (g + 8) * kD) : make_uint4(0, 0, 0, 0);
       }
+      if (rope.cos != nullptr) {     // rotate: the piece db pairs with the piece db + DB / 2 (the same d + D / 2)
+        int pos = cc.w.ctx - 1;
+        if (pos >= rope.max_pos) {
+          if (lane == 0) atomicOr(rope.status, 2);
+          pos = 0;
+        }
+#pragma unroll
+        for (int db = 0; db < DB / 2; ++db) {
+          const float* c = rope.cos + static_cast<size_t>(pos) * (kD / 2) + db * 32 + t * 8;
+          const float* sn = rope.sin + static_cast<size_t>(pos) * (kD / 2) + db * 32 + t * 8;
+          rope_rotate8(qlo[db], qlo[db + DB / 2], c, sn);
+          if (HI) rope_rotate8(qhi[db], qhi[db + DB / 2], c, sn);
+        }
+      }
 #pragma unroll
       for (int dg = 0; dg < DG; ++dg)
 #pragma unroll
@@ -364,6 +423,36 @@ decode_attn_stream_kernel(const DecodeArgs<bf16> a, int nitems) {
     const uint32_t Ks = stages + st * kStreamStageBytes;
     const uint32_t Vs = Ks + kStreamKBytes;
     const int k0 = cc.w.part * kPart + cc.sb * kSub;
+    if (rope.cos != nullptr && k0 <= cc.w.ctx - 1 && cc.w.ctx - 1 < k0 + kSub) {
+      // the token's own key lies in this sub-block: its k (rotated) and v go from the token's row into the
+      // cache and over what the copy brought from the cache's not yet written slot
+      const int pos_raw = cc.w.ctx - 1, row = pos_raw - k0;
+      const int pos = pos_raw < rope.max_pos ? pos_raw : 0;
+      const bf16* trow = a.q + static_cast<size_t>(cc.w.tok) * a.q_stride;
+      const int32_t page = a.block_table[static_cast<size_t>(cc.w.seq) * a.max_blocks + (pos_raw >> ps_shift)];
+      const size_t crow = ((static_cast<size_t>(page) * a.hkv + cc.w.kvh) * ps + (pos_raw & (ps - 1))) * kD;
+      constexpr int HC = CPR / 2;                       // chunks in half a row
+      if (lane < HC) {
+        const bf16* kp = trow + rope.k_col + cc.w.kvh * kD;
+        uint4 x0 = *reinterpret_cast<const uint4*>(kp + lane * 8), x1 = *reinterpret_cast<const uint4*>(kp + (lane + HC) * 8);
+        rope_rotate8(x0, x1, rope.cos + static_cast<size_t>(pos) * (kD / 2) + lane * 8,
+                     rope.sin + static_cast<size_t>(pos) * (kD / 2) + lane * 8);
+        *reinterpret_cast<uint4*>(rope.kcache + crow + lane * 8) = x0;
+        *reinterpret_cast<uint4*>(rope.kcache + crow + (lane + HC) * 8) = x1;
+        const uint32_t kr = Ks + row * (kD * 2);
+        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(kr + ((lane ^ ((row & 1) << 2)) << 4)), "r"(x0.x),
+                     "r"(x0.y), "r"(x0.z), "r"(x0.w) : "memory");
+        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(kr + (((lane + HC) ^ ((row & 1) << 2)) << 4)), "r"(x1.x),
+                     "r"(x1.y), "r"(x1.z), "r"(x1.w) : "memory");
+      } else if (lane < HC + CPR) {
+        const int c = lane - HC;
+        const uint4 x = *reinterpret_cast<const uint4*>(trow + rope.v_col + cc.w.kvh * kD + c * 8);
+        *reinterpret_cast<uint4*>(rope.vcache + crow + c * 8) = x;
+        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(Vs + row * (kD * 2) + ((c ^ (((row >> 1) & 3) << 1)) << 4)),
+                     "r"(x.x), "r"(x.y), "r"(x.z), "r"(x.w) : "memory");
+      }
+      __syncwarp();
+    }
     const bool whole = k0 >= cc.w.lo && k0 + kSub <= cc.w.ctx;     // no key of the sub-block is masked
     constexpr int kdb = kD * 2;                                    // bytes per row
 

@@ -298,6 +298,48 @@ def attn_decode(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcache: to
            "attn_decode", 2)
 
 
+def attn_decode_streams(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcache: torch.Tensor,
+                        part_o: torch.Tensor, counters: Optional[torch.Tensor], out: torch.Tensor, max_parts: int,
+                        nitems: int, num_heads: int, num_kv_heads: int, head_dim: int, page_size: int,
+                        impl: int = 0) -> bool:
+    """Whether ``attn_decode`` with these arguments runs the streaming kernel (which can also do the rotary
+    encoding and the cache write of the query tokens: ``attn_decode_rope``)."""
+    if not q.is_cuda or q.dtype != torch.bfloat16 or head_dim not in (64, 128):
+        return False
+    f = _fn(_attn(head_dim), "rl_attn_decode_streams",
+            [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+             c_int, c_int, c_int])
+    return bool(f(_code(q.dtype), _ptr(q), q_stride, _ptr(kcache), _ptr(vcache), _ptr(part_o), _ptr(counters),
+                  _ptr(out), out.stride(0), max_parts, nitems, num_heads, num_kv_heads, page_size, impl))
+
+
+def attn_decode_rope(qkv: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcache: torch.Tensor,
+                     block_table: torch.Tensor, items: torch.Tensor, part_o: torch.Tensor, part_ml: torch.Tensor,
+                     max_parts: int, counters: torch.Tensor, out: torch.Tensor, nitems: int, num_heads: int,
+                     num_kv_heads: int, head_dim: int, page_size: int, window: int, scale: float,
+                     cos: torch.Tensor, sin: torch.Tensor, k_col: int, v_col: int, status: torch.Tensor) -> None:
+    """``attn_decode`` by the streaming kernel with the rotary encoding and the cache write done in the
+    kernel: ``qkv`` holds the UNROTATED rows [q | k | v] of the query tokens (k at column ``k_col``, v at
+    ``v_col``); a token's position is its context length - 1; its rotated k and its v are written into the
+    cache there.  Only where ``attn_decode_streams`` says so."""
+    _need_cuda(qkv, kcache, out)
+    f = _fn(_attn(head_dim), "rl_attn_decode_rope",
+            [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+             c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_int, c_int, c_int,
+             c_void_p, c_void_p])
+    need = nitems * num_heads * max_parts
+    if part_o.numel() < need * head_dim or part_ml.numel() < need * 2:
+        raise KernelError("attn_decode_rope: partition workspace too small")
+    if counters.numel() < nitems * num_kv_heads:
+        raise KernelError("attn_decode_rope: counter workspace too small")
+    if cos.dtype != torch.float32 or cos.shape[1] != head_dim // 2 or not cos.is_contiguous() or not sin.is_contiguous():
+        raise KernelError("attn_decode_rope: cos / sin must be contiguous float32 [positions, head_dim / 2]")
+    _check(f(_ptr(qkv), q_stride, _ptr(kcache), _ptr(vcache), _ptr(block_table), block_table.shape[1], _ptr(items),
+             _ptr(part_o), _ptr(part_ml), max_parts, _ptr(counters), _ptr(out), out.stride(0), nitems, num_heads,
+             num_kv_heads, page_size, window, float(scale), _ptr(cos), _ptr(sin), cos.shape[0], k_col, v_col,
+             _ptr(status), _stream()), "attn_decode_rope")
+
+
 def attn_prefill(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcache: torch.Tensor,
                  block_table: torch.Tensor, tile_seq: torch.Tensor, tile_tok: torch.Tensor,
                  tile_rows: torch.Tensor, positions: torch.Tensor, out: torch.Tensor, tiles: int,

@@ -132,18 +132,33 @@ class GQAttention(Mixer):
         if self.b_qkv is not None:
             kernels.add_bias(qkv, self.b_qkv)
         tables = self.position.rotary_tables()
-        if tables is None:
-            self.position.apply(qkv, p.num_heads, p.num_kv_heads, p.head_dim, ctx)
-        cos, sin = tables if tables is not None else (None, None)
         g = ctx.groups[cache.group]
-        kernels.rope_kv_write(qkv, ctx.positions, g.slots if cache.write else None, cos, sin, cache.k, cache.v,
-                              p.num_heads, p.num_kv_heads, p.head_dim, rt.page_size, ctx.status, tokens=T)
         attn = ws.get("attn.out", (rt.max_tokens, self.q_size), rt.dtype)[:T]
+        part_o = part_ml = None
         if ctx.num_decode > 0:
             part_o = ws.get("attn.part_o", (ctx.max_items * p.num_heads * ctx.parts_capacity * p.head_dim,),
                             torch.float32)
             part_ml = ws.get("attn.part_ml", (ctx.max_items * p.num_heads * ctx.parts_capacity * 2,),
                              torch.float32)
+            # a step of single tokens only, on the streaming kernel: that kernel rotates q and k itself and
+            # writes the tokens' k and v into the cache, which saves the kernel that does so otherwise
+            if (tables is not None and cache.write and ctx.num_decode == T and ctx.num_tiles == 0
+                    and kernels.attn_decode_streams(qkv, self.qkv_size, cache.k, cache.v, part_o,
+                                                    self._counters(ctx.max_items), attn, ctx.decode_parts,
+                                                    ctx.num_decode, p.num_heads, p.num_kv_heads, p.head_dim,
+                                                    rt.page_size)):
+                kernels.attn_decode_rope(qkv, self.qkv_size, cache.k, cache.v, g.block_table, ctx.decode_info,
+                                         part_o, part_ml, ctx.decode_parts, self._counters(ctx.max_items), attn,
+                                         ctx.num_decode, p.num_heads, p.num_kv_heads, p.head_dim, rt.page_size,
+                                         p.window, self.scale, tables[0], tables[1], self.q_size,
+                                         self.q_size + self.kv_size, ctx.status)
+                return attn
+        if tables is None:
+            self.position.apply(qkv, p.num_heads, p.num_kv_heads, p.head_dim, ctx)
+        cos, sin = tables if tables is not None else (None, None)
+        kernels.rope_kv_write(qkv, ctx.positions, g.slots if cache.write else None, cos, sin, cache.k, cache.v,
+                              p.num_heads, p.num_kv_heads, p.head_dim, rt.page_size, ctx.status, tokens=T)
+        if ctx.num_decode > 0:
             kernels.attn_decode(qkv, self.qkv_size, cache.k, cache.v, g.block_table, ctx.decode_info,
                                 part_o, part_ml, ctx.decode_parts, self._counters(ctx.max_items), attn,
                                 ctx.num_decode, p.num_heads, p.num_kv_heads, p.head_dim, rt.page_size,

@@ -348,6 +348,69 @@ def test_attention_decode_streaming_kernel_many_units_per_cta():
     assert int(kernels.tc_status(torch.device(DEV)).item()) == 0
 
 
+@pytest.mark.parametrize("Hq,Hkv,D", [(32, 8, 64), (16, 2, 128), (4, 4, 64)])
+@pytest.mark.parametrize("page_size,window", [(16, 0), (64, 0), (16, 300)])
+def test_attention_decode_with_rotation_and_cache_write_in_the_kernel(Hq, Hkv, D, page_size, window):
+    """attn_decode_rope against rope_kv_write followed by attn_decode: the same outputs, and the same k and
+    v rows written into the cache at the tokens' own positions (and nowhere else)."""
+    from redline_b200.config.model_config import RopeScaling
+    from redline_b200.parts.rope import RotaryParams, rope_tables
+    g = torch.Generator().manual_seed(51)
+    lens = [700, 1, 129, 2048, 33, 1500, 260, 2047] * 4      # context lengths including the new token
+    B = len(lens)
+    cos, sin = rope_tables(RotaryParams(D, 10000.0, RopeScaling(), 4096), 2200)
+    cos, sin = cos.to(DEV).contiguous(), sin.to(DEV).contiguous()
+    blocks = [(n + page_size - 1) // page_size for n in lens]
+    npages = sum(blocks) + 1
+    perm = (torch.randperm(npages - 1, generator=g) + 1).tolist()
+    bt = torch.zeros(B, max(blocks) + 1, dtype=torch.int32)
+    it = iter(perm)
+    for b in range(B):
+        for i in range(blocks[b]):
+            bt[b, i] = next(it)
+    btd = bt.to(DEV)
+    kc0 = torch.randn(npages, Hkv, page_size, D, generator=g).to(torch.bfloat16).to(DEV)
+    vc0 = torch.randn(npages, Hkv, page_size, D, generator=g).to(torch.bfloat16).to(DEV)
+    qkv0 = torch.randn(B, (Hq + 2 * Hkv) * D, generator=g).to(torch.bfloat16).to(DEV)
+    scale = 1.0 / math.sqrt(D)
+    parts = (max(lens) + kernels.DECODE_PARTITION - 1) // kernels.DECODE_PARTITION
+    items = torch.tensor([[b, b, lens[b], 0] for b in range(B)], dtype=torch.int32, device=DEV)
+    pos = torch.tensor([n - 1 for n in lens], dtype=torch.int32, device=DEV)
+    slots = torch.tensor([int(bt[b, (lens[b] - 1) // page_size]) * page_size + (lens[b] - 1) % page_size
+                          for b in range(B)], dtype=torch.int32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+
+    def buffers():
+        po = torch.full((B * Hq * parts * D,), float("nan"), device=DEV)
+        pm = torch.full((B * Hq * parts * 2,), float("nan"), device=DEV)
+        return po, pm, torch.zeros(B * Hkv, dtype=torch.int32, device=DEV), \
+            torch.full((B, Hq * D), float("nan"), device=DEV, dtype=torch.bfloat16)
+
+    # the two kernels
+    kc1, vc1, qkv1 = kc0.clone(), vc0.clone(), qkv0.clone()
+    kernels.rope_kv_write(qkv1, pos, slots, cos, sin, kc1, vc1, Hq, Hkv, D, page_size, status)
+    po, pm, cnt, want = buffers()
+    kernels.attn_decode(qkv1, qkv1.shape[1], kc1, vc1, btd, items, po, pm, parts, cnt, want, B, Hq, Hkv, D,
+                        page_size, window, scale, 3)
+    # the one kernel
+    kc2, vc2, qkv2 = kc0.clone(), vc0.clone(), qkv0.clone()
+    po, pm, cnt, got = buffers()
+    assert kernels.attn_decode_streams(qkv2, qkv2.shape[1], kc2, vc2, po, cnt, got, parts, B, Hq, Hkv, D, page_size)
+    kernels.attn_decode_rope(qkv2, qkv2.shape[1], kc2, vc2, btd, items, po, pm, parts, cnt, got, B, Hq, Hkv, D,
+                             page_size, window, scale, cos, sin, Hq * D, (Hq + Hkv) * D, status)
+    assert status.item() == 0 and int(cnt.abs().max()) == 0
+    assert torch.equal(qkv2, qkv0), "the token rows stay unrotated"
+    close(got, want, 4e-3)
+    close(kc2, kc1, 1e-2)
+    assert torch.equal(vc2, vc1)
+    changed = (kc2 != kc0).any(dim=-1)                 # [pages, heads, slots]: only the tokens' own slots may differ
+    allowed = torch.zeros_like(changed)
+    for b in range(B):
+        sl = int(slots[b])
+        allowed[sl // page_size, :, sl % page_size] = True
+    assert not (changed & ~allowed).any()
+
+
 def test_attention_decode_beyond_256_partitions():
     """A context of 40,000 keys has 313 partitions, more than the one-partition kernel can merge: the
     default choice must take the streaming kernel there (and the CUDA-core kernel must agree)."""
