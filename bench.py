@@ -84,7 +84,7 @@ class ClockSampler:
         if not exe:
             return
         self.proc = subprocess.Popen([exe, f"--id={self.device}", f"--query-gpu={self.QUERY}",
-                                      "--format=csv,noheader,nounits", "-lms", "100"],
+                                      "--format=csv,noheader,nounits", "-lms", "25"],
                                      stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         threading.Thread(target=self._read, daemon=True).start()
 
@@ -105,8 +105,14 @@ class ClockSampler:
                 self.proc.kill()
 
     def summary(self, lo: int = 0, hi: Optional[int] = None) -> Dict[str, Any]:
+        """Samples lo..hi (marks around the timed region).  A region too short for three samples is
+        widened backwards into the warm-up steps before it, which run the same load; "widened" says so."""
         sm, mx, reasons = [], 0.0, set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        hi = len(self.lines) if hi is None else hi
+        widened = hi - lo < 3
+        if widened:
+            lo = max(0, hi - 8)
         for line in self.lines[lo:hi]:
             parts = [x.strip() for x in line.split(",")]
             if len(parts) < 7:
@@ -121,7 +127,7 @@ class ClockSampler:
                     reasons.add(name)
         sm.sort()
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx or None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm), "widened": widened}
 
 
 def model_numbers(cfg: Dict[str, Any]) -> Dict[str, float]:
@@ -197,7 +203,6 @@ def decode_run(model: str, batch: int, prompt_len: int, steps: int, warmup: int,
     while len(eng.records) < steps:               # the last launched step is read one call later
         eng.step()
     torch.cuda.synchronize()
-    mark1 = sampler.mark()
     recs = eng.records[:steps]
     assert all(r.kind == "decode" and r.num_seqs == batch for r in recs), "timed steps must be pure decode"
     gpu_ms = sum(r.gpu_ms for r in recs)
@@ -214,6 +219,7 @@ def decode_run(model: str, batch: int, prompt_len: int, steps: int, warmup: int,
         eng.step()
     torch.cuda.synchronize()
     wall = time.perf_counter() - t1
+    mark1 = sampler.mark()                        # the clocks cover both timed regions
     assert len(eng._seqs) == batch, "a request finished inside the timed region"
     produced = sum(len(s.tokens) for s in eng._seqs.values()) - done_before
     ctx_mid = prompt_len + warmup + steps // 2

@@ -113,10 +113,17 @@ def bench_skinny(args) -> None:
             torch.mm(x, w.t(), out=yl)
         elif args.norm:
             kernels.gemm_skinny(w, y, epi, M, residual=res, norm_w=nw, eps=1e-5)
+        elif args.hand_out:
+            kernels.gemm_skinny(w, y, epi, M, x=x, hand_out=(nwn, xw, sums))
+        elif args.hand_in:
+            kernels.gemm_skinny(w, y, epi, M, x=x, hand_in=sums_in, eps=1e-5)
         else:
             kernels.gemm_skinny(w, y, epi, M, x=x)
 
     yl = torch.empty(M, wn, device=dev, dtype=torch.bfloat16)
+    nwn = torch.ones(N, device=dev, dtype=torch.bfloat16)          # a norm handed over: to the next product ...
+    xw, sums = kernels.norm_handover_buffers(8, N, dev)
+    sums_in = torch.ones(8, (K + 15) // 16, device=dev)            # ... and from the one before
     us = graph_time_us(fn, copies, use_graph=not args.no_graph)
     nbytes = wn * K * 2
     pk = peaks()
@@ -213,6 +220,8 @@ def main() -> int:
             p.add_argument("--n", type=int, default=3072)
             p.add_argument("--k", type=int, default=2048)
             p.add_argument("--norm", action="store_true", help="fuse the RMSNorm of a float32 residual")
+            p.add_argument("--hand-out", action="store_true", help="with --epilogue residual: hand the next norm over")
+            p.add_argument("--hand-in", action="store_true", help="take a norm that was handed over (at most 8 rows)")
             p.add_argument("--epilogue", default="bf16", choices=["bf16", "f32", "residual", "swiglu"])
             p.add_argument("--library", action="store_true", help="time the library product instead")
     args = ap.parse_args()

@@ -18,6 +18,13 @@
 //             CTA from the float32 residual stream (optionally gathered by row index)
 //   epilogue  bfloat16 store | float32 store (logits) | residual += y (float32) |
 //             SiLU-gated product silu(gate) * up
+//   between two products: the RMSNorm after a `residual += y` handed over instead of run as a
+//             kernel: the first product also leaves bfloat16(residual * norm_weight) and per-tile
+//             sums of residual^2, the second takes that as its x and scales its rows by
+//             rsqrt(sum / K + eps)
+// What an epilogue needs from global memory (the residual values, the norm weights, the partial
+// sums) is copied into shared memory at the kernel's start, so that no round trip is left for the
+// kernel's end and no register is held across the k loop, which has none to spare.
 //
 // mma.sync.m16n8k16 is used rather than tcgen05: with at most 16 rows the product is
 // bound by the weight stream, a 128-row UMMA tile would be 1/16 full, and mma.sync can
@@ -39,7 +46,20 @@ struct SkinnyArgs {
   void* y;                // output (bf16 / float), or the residual stream for kAddResidual
   int M, N, K, ldx, ldy;
   int row_tiles;          // 16-row tiles per CTA (run one after another)
+  // The norm after a `residual += y` handed over to the next product (kAddResidual only; xw == nullptr:
+  // not done): xw[m, n] = bfloat16(residual[m, n] * next_w[n]) and, per row and 16-feature tile,
+  // ss_out[m * tiles + tile] = the tile's sum of residual^2 (tiles = ceil(N / 16)).
+  const void* next_w;
+  int next_w_f32;
+  bf16* xw;
+  int ldxw;
+  float* ss_out;
+  // ... and taken over (unstaged bfloat16 x of up to 8 rows only; ss_in == nullptr: x is used as it is):
+  // x is such an xw, and row m of the product is scaled by rsqrt(sum(ss_in[m, 0 : ss_n]) / K + eps).
+  const float* ss_in;
+  int ss_n;
 };
+
 
 __device__ __forceinline__ void mma_bf16(float* d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                          uint32_t b0, uint32_t b1) {
@@ -58,6 +78,13 @@ __device__ __forceinline__ uint4 ldg_stream(const void* p) {
   return v;
 }
 
+// 4 bytes from global to shared memory without a register in between (cp.async), and the wait for all
+// such copies of the thread
+__device__ __forceinline__ void cp_async4(const void* smem, const void* gmem) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem))), "l"(gmem));
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;\n" ::: "memory"); }
+
 constexpr int kSB = 128;  // k per warp iteration (a "super-block": two 64-wide MMA blocks)
 
 // The weights of one super-block as a thread holds them: rows g and g + 8 of the tile,
@@ -67,14 +94,50 @@ struct WFrag {
   uint4 x[4];     // XG only: the activations of the same k, row g of the batch
 };
 
+// The epilogue `residual += y` that also hands the next norm over (see SkinnyArgs).  A function of its
+// own that is not inlined: the kernels with 16 warps have no register to spare in their k loop, and
+// whatever this needs must not be kept alive across that loop.  red: the warps' partial sums
+// [WARPS][16][MT] in shared memory; the CTA's round begins at feature cta_n0.
+template <int MT, int WARPS, int KW>
+// early: the round's residual values [TPC * 16 * MT] and norm weights [TPC * 16] staged in shared
+// memory at the kernel's start (nullptr: read from global memory here).
+__device__ __noinline__ void hand_over_epilogue(const float* red, const float* early, float* y, int ldy, const void* next_w,
+                                                int next_w_f32, bf16* xw, int ldxw, float* ss_out, int M, int N,
+                                                int cta_n0, int tid) {
+  constexpr int TPC = WARPS / KW;
+  for (int i = tid; i < TPC * 16 * MT; i += WARPS * 32) {     // a multiple of 32: whole warps
+    const int m = i / (TPC * 16), ft = i - m * (TPC * 16);
+    const int tl = ft >> 4, f = ft & 15;
+    const int n = cta_n0 + ft;
+    const bool live = m < M && n < N;
+    float v = 0.f;
+#pragma unroll
+    for (int w = 0; w < KW; ++w) v += red[((tl * KW + w) * 16 + f) * MT + m];
+    float r = 0.f;
+    if (live) {
+      const size_t o = static_cast<size_t>(m) * ldy + n;
+      r = (early ? early[i] : y[o]) + __bfloat162float(__float2bfloat16_rn(v));
+      y[o] = r;
+      const float nw = early         ? early[TPC * 16 * MT + ft]
+                       : next_w_f32 ? static_cast<const float*>(next_w)[n]
+                                    : __bfloat162float(static_cast<const bf16*>(next_w)[n]);
+      xw[static_cast<size_t>(m) * ldxw + n] = __float2bfloat16_rn(r * nw);
+    }
+    float sq = r * r;          // the 16 lanes of a tile (one row m) add up in a fixed order
+#pragma unroll
+    for (int x = 8; x > 0; x >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, x);
+    if (f == 0 && m < M && cta_n0 + tl * 16 < N) ss_out[static_cast<size_t>(m) * ((N + 15) / 16) + (cta_n0 >> 4) + tl] = sq;
+  }
+}
+
 // MT: token rows padded to 8 or 16; WARPS: warps per CTA; EPI: epilogue; NORM: fused norm.
 // MT: token rows padded to 8 or 16; WARPS: warps per CTA; KW: warps that split the K of one
 // 16-row weight stream; EPI: epilogue; NORM: fused norm.  The CTA's WARPS / KW groups of warps
 // take different streams at the same time: 16-row tiles next to each other and, for the gated
 // product, the gate rows and the up rows of a tile.
 template <int MT, int WARPS, int KW, int EPI, bool NORM>
-__global__ void __launch_bounds__(WARPS * 32)
-gemm_skinny_kernel(const SkinnyArgs a, int kc) {
+__global__ void __launch_bounds__(WARPS * 32, WARPS <= 8 ? 2 : 1)     // (at most 128 registers: two CTAs of 8 warps per SM)
+gemm_skinny_kernel(const SkinnyArgs a, int kc, int extra_off) {
   constexpr bool GATED = (EPI == kSwiglu);
   constexpr int NG = MT / 8;                    // 8-token groups
   // XG: with bfloat16 activations and at most 8 rows the activations are not staged in shared memory
@@ -90,6 +153,11 @@ gemm_skinny_kernel(const SkinnyArgs a, int kc) {
                                        // multiple of 128 B, so the 16-byte fragment reads do not collide
   bf16* xs = reinterpret_cast<bf16*>(smem_raw);
   float* red = reinterpret_cast<float*>(smem_raw);   // reused after the k loop
+  // Behind both: what the epilogue of the CTA's first round needs from global memory, copied there at the
+  // kernel's start so that no round trip is left for the kernel's end (and no register is held for it
+  // across the k loop): for `residual +=` the residual values [TPC * 16 * MT] and, with a norm handed
+  // over, its weights [TPC * 16]; for a norm taken over, the partial sums [M][ss_n].
+  float* early = reinterpret_cast<float*>(smem_raw + extra_off);
   __shared__ float inv_rms[MT];
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -150,7 +218,21 @@ gemm_skinny_kernel(const SkinnyArgs a, int kc) {
   for (int q = 0; q < 4; ++q) load_piece(fb.lo[q], fb.hi[q], q);
   load_advance();
   int step = 0;       // super-blocks this warp has multiplied
+  if (EPI == kAddResidual && a.xw != nullptr && tid < TPC * 16) {
+    // the weights of the norm that is handed over (they do not depend on the kernels before this one)
+    const int n = blockIdx.x * a.row_tiles * TPC * 16 + tid;
+    if (n < a.N)
+      early[TPC * 16 * MT + tid] = a.next_w_f32 ? static_cast<const float*>(a.next_w)[n]
+                                                : __bfloat162float(static_cast<const bf16*>(a.next_w)[n]);
+  }
   pdl_wait();   // everything below reads what earlier kernels of the step wrote
+  if (EPI == kAddResidual) {
+    const int n00 = blockIdx.x * a.row_tiles * TPC * 16;
+    for (int i = tid; i < TPC * 16 * MT; i += WARPS * 32) {
+      const int m = i / (TPC * 16), n = n00 + (i - m * (TPC * 16));
+      if (m < M && n < a.N) cp_async4(early + i, static_cast<const float*>(a.y) + static_cast<size_t>(m) * a.ldy + n);
+    }
+  }
   if (XG) {     // the activations of the first two steps (the load cursor is already two steps on)
     const int sb2 = l_sb;
     const bool ok2 = l_ok;
@@ -164,6 +246,14 @@ gemm_skinny_kernel(const SkinnyArgs a, int kc) {
     for (int q = 0; q < 4; ++q) load_x(fb.x[q], q);
     l_sb = sb2;
     l_ok = ok2;
+  }
+
+  // a norm handed over by the product before: row m's partial sums are added up by warp m after the k loop
+  constexpr bool TAKES = XG && EPI != kAddResidual;
+  if (TAKES && a.ss_in != nullptr && warp < M) {
+#pragma unroll 1
+    for (int c = lane; c < a.ss_n; c += 32)
+      cp_async4(early + warp * a.ss_n + c, a.ss_in + static_cast<size_t>(warp) * a.ss_n + c);
   }
 
   if (NORM) {
@@ -184,7 +274,6 @@ gemm_skinny_kernel(const SkinnyArgs a, int kc) {
   }
 
   for (int rt = 0; rt < a.row_tiles; ++rt) {
-    const int n0 = (tile0 + rt * TPC) * 16;                           // this warp's tile (may lie past N)
     const int cta_n0 = (blockIdx.x * a.row_tiles + rt) * TPC * 16;   // first feature of the CTA's round
     if (cta_n0 >= a.N) break;
     float acc[NG][4];
@@ -192,7 +281,6 @@ gemm_skinny_kernel(const SkinnyArgs a, int kc) {
     for (int j = 0; j < NG; ++j)
 #pragma unroll
       for (int e = 0; e < 4; ++e) acc[j][e] = 0.f;
-
     for (int k0 = 0; k0 < K; k0 += kc) {
       const int kn = min(kc, K - k0);
       if (!XG) __syncthreads();   // the previous chunk (or the previous tile's reduction) is done with smem
@@ -256,6 +344,18 @@ gemm_skinny_kernel(const SkinnyArgs a, int kc) {
         if (step & 1) multiply(fb); else multiply(fa);
       }
     }
+    if (TAKES && a.ss_in != nullptr && rt == 0) {     // (WARPS >= 8 >= M: every row has its warp)
+      float ss = 0.f;
+      cp_async_wait_all();       // (a lane adds what it copied itself)
+      if (warp < M) {
+#pragma unroll 1
+        for (int c = lane; c < a.ss_n; c += 32) ss += early[warp * a.ss_n + c];
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      if (lane == 0 && warp < MT) inv_rms[warp] = rsqrtf(ss / static_cast<float>(K) + a.eps);
+    }
+    if (EPI == kAddResidual) cp_async_wait_all();
     // ---- partial sums of the warps meet in shared memory: red[warp][16][MT]
     __syncthreads();
 #pragma unroll
@@ -268,6 +368,11 @@ gemm_skinny_kernel(const SkinnyArgs a, int kc) {
       r[(g + 8) * MT + col + 1] = acc[j][3];
     }
     __syncthreads();
+    if (EPI == kAddResidual && a.xw != nullptr) {       // (the same for the whole CTA)
+      hand_over_epilogue<MT, WARPS, KW>(red, rt == 0 ? early : nullptr, static_cast<float*>(a.y), a.ldy, a.next_w,
+                                        a.next_w_f32, a.xw, a.ldxw, a.ss_out, M, a.N, cta_n0, tid);
+      continue;
+    }
     for (int i = tid; i < TPC * 16 * MT; i += WARPS * 32) {
       // consecutive threads take consecutive features of one token: coalesced stores
       const int m = i / (TPC * 16), ft = i - m * (TPC * 16);
@@ -281,6 +386,10 @@ gemm_skinny_kernel(const SkinnyArgs a, int kc) {
         v += red[((w0 + w) * 16 + f) * MT + m];
         if (GATED) u += red[((w0 + KW + w) * 16 + f) * MT + m];
       }
+      if (TAKES && a.ss_in != nullptr) {
+        v *= inv_rms[m];
+        u *= inv_rms[m];
+      }
       const size_t o = static_cast<size_t>(m) * a.ldy + n;
       if (EPI == kStoreBf16) {
         static_cast<bf16*>(a.y)[o] = __float2bfloat16_rn(v);
@@ -288,7 +397,7 @@ gemm_skinny_kernel(const SkinnyArgs a, int kc) {
         static_cast<float*>(a.y)[o] = v;
       } else if (EPI == kAddResidual) {
         // the unfused path rounds the product to bfloat16 before the add; so does this one
-        static_cast<float*>(a.y)[o] += __bfloat162float(__float2bfloat16_rn(v));
+        static_cast<float*>(a.y)[o] = (rt == 0 ? early[i] : static_cast<const float*>(a.y)[o]) + __bfloat162float(__float2bfloat16_rn(v));
       } else {
         const float gt = __bfloat162float(__float2bfloat16_rn(v)), up = __bfloat162float(__float2bfloat16_rn(u));
         static_cast<bf16*>(a.y)[o] = __float2bfloat16_rn(gt / (1.f + expf(-gt)) * up);
@@ -324,7 +433,12 @@ int launch_one(const SkinnyArgs& a0, int sm_count, cudaStream_t stream) {
   const size_t xbytes = static_cast<size_t>(MT) * (kc + 32) * 2;
   const size_t rbytes = static_cast<size_t>(WARPS) * 16 * MT * 4;
   constexpr bool XG = !NORM && MT == 8;               // no staging of x: only the reduction uses shared memory
-  const size_t smem = (!XG && xbytes > rbytes) ? xbytes : rbytes;
+  const size_t base = ((!XG && xbytes > rbytes) ? xbytes : rbytes);
+  const size_t extra_off = (base + 15) / 16 * 16;
+  const size_t extra = EPI == kAddResidual ? static_cast<size_t>(TPC * 16 * MT + TPC * 16) * 4
+                                           : (a.ss_in != nullptr ? static_cast<size_t>(MT) * a.ss_n * 4 : 0);
+  const size_t smem = extra_off + extra;
+  if (smem > 200 * 1024) return static_cast<int>(cudaErrorInvalidValue);
   static size_t set_for = 0;
   if (smem > set_for) {
     cudaError_t e = cudaFuncSetAttribute(gemm_skinny_kernel<MT, WARPS, KW, EPI, NORM>,
@@ -332,7 +446,8 @@ int launch_one(const SkinnyArgs& a0, int sm_count, cudaStream_t stream) {
     if (e != cudaSuccess) return static_cast<int>(e);
     set_for = smem;
   }
-  launch_kernel(gemm_skinny_kernel<MT, WARPS, KW, EPI, NORM>, dim3(ctas), dim3(WARPS * 32), smem, stream, a, kc);
+  launch_kernel(gemm_skinny_kernel<MT, WARPS, KW, EPI, NORM>, dim3(ctas), dim3(WARPS * 32), smem, stream, a, kc,
+                static_cast<int>(extra_off));
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -384,12 +499,30 @@ int rl_gemm_skinny_max_rows() { return 16; }
 // N gate rows then N up rows).  norm != 0: x is rmsnorm(residual[rows_idx]) * norm_w.
 // Requirements: M <= 16, K a multiple of 8, 16-byte aligned rows.  Returns cudaErrorInvalidValue
 // otherwise (the caller then takes another path).
-int rl_gemm_skinny(const void* w, const void* x, int ldx, const float* residual, const void* norm_w,
-                   int norm_w_f32, const int32_t* rows_idx, float eps, int norm, void* y, int ldy,
-                   int epilogue, int M, int N, int K, int sm_count, cudaStream_t stream) {
+//
+// The norm between two products handed over (both optional, see SkinnyArgs): with xw_out, a product with
+// epilogue 2 also leaves bfloat16(residual * next_w) and per-tile sums of residual^2 (ss_out, float32
+// [M, ceil(N / 16)]); with ss_in, a product of up to 8 rows without the fused norm takes such an x and
+// scales its rows by rsqrt(sum / K + eps).
+int rl_gemm_skinny_handover(const void* w, const void* x, int ldx, const float* residual, const void* norm_w,
+                            int norm_w_f32, const int32_t* rows_idx, float eps, int norm, void* y, int ldy,
+                            int epilogue, int M, int N, int K, const void* next_w, int next_w_f32, void* xw_out,
+                            int ldxw, float* ss_out, const float* ss_in, int ss_n, int sm_count,
+                            cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (M > 16 || K % 8 != 0 || (!norm && ldx % 8 != 0)) return static_cast<int>(cudaErrorInvalidValue);
+  if (xw_out != nullptr && (epilogue != kAddResidual || next_w == nullptr || ss_out == nullptr))
+    return static_cast<int>(cudaErrorInvalidValue);
+  if (ss_in != nullptr && (norm || M > 8 || ss_n <= 0 || epilogue == kAddResidual))
+    return static_cast<int>(cudaErrorInvalidValue);
   SkinnyArgs a;
+  a.next_w = next_w;
+  a.next_w_f32 = next_w_f32;
+  a.xw = static_cast<bf16*>(xw_out);
+  a.ldxw = ldxw;
+  a.ss_out = ss_out;
+  a.ss_in = ss_in;
+  a.ss_n = ss_n;
   a.w = static_cast<const bf16*>(w);
   a.x = static_cast<const bf16*>(x);
   a.residual = residual;
@@ -419,6 +552,13 @@ int rl_gemm_skinny(const void* w, const void* x, int ldx, const float* residual,
     }
   }
   return static_cast<int>(cudaErrorInvalidValue);
+}
+
+int rl_gemm_skinny(const void* w, const void* x, int ldx, const float* residual, const void* norm_w,
+                   int norm_w_f32, const int32_t* rows_idx, float eps, int norm, void* y, int ldy,
+                   int epilogue, int M, int N, int K, int sm_count, cudaStream_t stream) {
+  return rl_gemm_skinny_handover(w, x, ldx, residual, norm_w, norm_w_f32, rows_idx, eps, norm, y, ldy, epilogue, M, N,
+                                 K, nullptr, 0, nullptr, 0, nullptr, nullptr, 0, sm_count, stream);
 }
 
 }  // extern "C"

@@ -138,6 +138,12 @@ class StepContext:
     has_src: bool = False
     any_sampling: bool = False
     host: Optional["HostBatch"] = None
+    # a norm handed over between parts (parts.base.NormHandover); set and cleared by the block
+    next_norm: Optional[object] = None         # the norm applied to the stream after the running part
+    hand_in: Optional[object] = None           # what the part before left for the running part's norm
+    hand_out: Optional[object] = None          # what the running part leaves
+    block_next_norm: Optional[object] = None   # set by the model: the first norm of the block after this one
+    block_hand: Optional[object] = None        # carried from a block's last part to the next block
 
 
 @dataclass

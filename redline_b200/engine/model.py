@@ -117,8 +117,13 @@ class DecoderModel:
         residual = ws.get("residual", (rt.max_tokens, self.spec.hidden_size), torch.float32)[:T]
         self.embedding.forward(ctx, residual)
         pending = None
-        for i, call in enumerate(self.spec.order):
+        order = self.spec.order
+        ctx.block_hand = None
+        for i, call in enumerate(order):
+            # (the block after this one may take over its first norm from this block's last kernel)
+            ctx.block_next_norm = self.blocks[order[i + 1].layer].first_norm() if i + 1 < len(order) else None
             pending = self.blocks[call.layer].forward(residual, pending, ctx, caches[i], states[i])
+        ctx.block_hand = ctx.block_next_norm = None
         if R > 0 and pending is None and self.head.forward_from(residual, self.final_norm, ctx.logit_rows, R, logits):
             pass
         elif R > 0:

@@ -182,19 +182,36 @@ def skinny_ok(rows: int, w: torch.Tensor, x_dtype: torch.dtype) -> bool:
             and w.shape[1] % 8 == 0 and w.is_contiguous())
 
 
+def norm_handover_buffers(rows: int, width: int, device) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Buffers for a norm handed over between two skinny products: xw [rows, width] bfloat16 and the
+    per-tile sums of squares [rows, ceil(width / 16)] float32."""
+    return (torch.zeros((rows, width), dtype=torch.bfloat16, device=device),
+            torch.zeros((rows, (width + 15) // 16), dtype=torch.float32, device=device))
+
+
 def gemm_skinny(w: torch.Tensor, y: torch.Tensor, epilogue: int, rows: int, x: Optional[torch.Tensor] = None,
                 residual: Optional[torch.Tensor] = None, norm_w: Optional[torch.Tensor] = None,
-                eps: float = 0.0, rows_idx: Optional[torch.Tensor] = None) -> None:
+                eps: float = 0.0, rows_idx: Optional[torch.Tensor] = None,
+                hand_out: Optional[Tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = None,
+                hand_in: Optional[torch.Tensor] = None) -> None:
     """y = epilogue(x @ w^T) for at most 16 rows on the tensor cores (csrc/gemm_skinny.cu).
 
     x given: bfloat16 activations [rows, K].  residual + norm_w given instead: x is
     bfloat16(rmsnorm(residual[rows_idx]) * norm_w) formed inside the kernel.
     epilogue EPI_BF16 / EPI_F32: store into y; EPI_ADD_RESIDUAL: y (float32 stream) += product;
-    EPI_SWIGLU: w is [2 N, K] (gate rows, then up rows), y = silu(gate) * up, [rows, N]."""
+    EPI_SWIGLU: w is [2 N, K] (gate rows, then up rows), y = silu(gate) * up, [rows, N].
+
+    The RMSNorm between a product that ends in ``residual +=`` and the product after it can be handed
+    over instead of run as a kernel: with ``hand_out = (next_norm_weight, xw, sums)`` (EPI_ADD_RESIDUAL)
+    the product also leaves xw = bfloat16(residual * next_norm_weight) and per-tile sums of residual^2
+    (buffers of ``norm_handover_buffers``); the next product is then called with ``x = xw``,
+    ``hand_in = sums`` and the norm's ``eps`` (at most 8 rows) and scales its rows by
+    rsqrt(sum / K + eps): the same norm, with the rounding to bfloat16 before the scaling."""
     _need_cuda(w, y)
-    f = _fn(_lib("gemm_skinny", "gemm_skinny.cu"), "rl_gemm_skinny",
+    f = _fn(_lib("gemm_skinny", "gemm_skinny.cu"), "rl_gemm_skinny_handover",
             [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_float, c_int, c_void_p, c_int,
-             c_int, c_int, c_int, c_int, c_int, c_void_p])
+             c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
+             c_void_p])
     K = w.shape[1]
     N = w.shape[0] // 2 if epilogue == EPI_SWIGLU else w.shape[0]
     norm = residual is not None
@@ -210,9 +227,28 @@ def gemm_skinny(w: torch.Tensor, y: torch.Tensor, epilogue: int, rows: int, x: O
             EPI_SWIGLU: torch.bfloat16}[epilogue]
     if y.dtype != want or y.shape[1] != N or y.stride(1) != 1:
         raise KernelError(f"gemm_skinny: output must be {want} [rows, {N}]")
+    next_w = xw = ss_out = None
+    ldxw = ss_n = 0
+    if hand_out is not None:
+        next_w, xw, ss_out = hand_out
+        tiles = (N + 15) // 16
+        if (epilogue != EPI_ADD_RESIDUAL or xw.dtype != torch.bfloat16 or xw.shape[1] != N or xw.stride(1) != 1
+                or xw.shape[0] < rows or ss_out.dtype != torch.float32 or not ss_out.is_contiguous()
+                or ss_out.shape[1] != tiles or ss_out.shape[0] < rows or next_w.numel() != N
+                or next_w.dtype not in (torch.float32, torch.bfloat16)):
+            raise KernelError("gemm_skinny: hand_out needs EPI_ADD_RESIDUAL, a norm weight [N], xw bfloat16 "
+                              "[rows, N] and sums float32 [rows, ceil(N / 16)]")
+        ldxw = xw.stride(0)
+    if hand_in is not None:
+        if (norm or rows > SKINNY_UNSTAGED_ROWS or epilogue == EPI_ADD_RESIDUAL or hand_in.dtype != torch.float32
+                or not hand_in.is_contiguous() or hand_in.shape[0] < rows):
+            raise KernelError("gemm_skinny: hand_in needs bfloat16 x of at most 8 rows and sums float32 [rows, n]")
+        ss_n = hand_in.shape[1]
     _check(f(_ptr(w), _ptr(x), ldx, _ptr(residual), _ptr(norm_w),
              1 if (norm_w is not None and norm_w.dtype == torch.float32) else 0, _ptr(rows_idx), float(eps),
-             1 if norm else 0, _ptr(y), y.stride(0), epilogue, rows, N, K, sm_count(w.device), _stream()),
+             1 if norm else 0, _ptr(y), y.stride(0), epilogue, rows, N, K, _ptr(next_w),
+             1 if (next_w is not None and next_w.dtype == torch.float32) else 0, _ptr(xw), ldxw, _ptr(ss_out),
+             _ptr(hand_in), ss_n, sm_count(w.device), _stream()),
            "gemm_skinny")
 
 

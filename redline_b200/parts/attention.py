@@ -18,7 +18,7 @@ import torch
 
 from ..ops import kernels
 from ..ops.linear import linear
-from .base import LayerCache, Mixer, build_part, register
+from .base import LayerCache, Mixer, build_part, norm_handover, register
 from .spec import CacheSpec, PartSpec, TensorSpec
 
 
@@ -105,7 +105,12 @@ class GQAttention(Mixer):
                 or not kernels.skinny_ok(T, self.w_qkv, rt.dtype) or not kernels.skinny_ok(T, self.w_o, rt.dtype)):
             return False
         qkv = rt.workspace.get("attn.qkv", (rt.max_tokens, self.qkv_size), rt.dtype)[:T]
-        if T <= kernels.SKINNY_UNSTAGED_ROWS:
+        small = T <= kernels.SKINNY_UNSTAGED_ROWS
+        hand = ctx.hand_in if small else None
+        if hand is not None:
+            # the part before left the norm half done: its xw, and the row scales in this product
+            kernels.gemm_skinny(self.w_qkv, qkv, kernels.EPI_BF16, T, x=hand.xw[:T], hand_in=hand.sums, eps=rms[1])
+        elif small:
             # (see SwiGLUMLP.forward_into: a norm kernel of its own and a product without staging)
             xn = rt.workspace.get("attn.xn", (kernels.SKINNY_UNSTAGED_ROWS, self.params.hidden_size), rt.dtype)[:T]
             kernels.add_rmsnorm(residual, None, rms[0], xn, rms[1], rows=T)
@@ -113,7 +118,10 @@ class GQAttention(Mixer):
         else:
             kernels.gemm_skinny(self.w_qkv, qkv, kernels.EPI_BF16, T, residual=residual, norm_w=rms[0], eps=rms[1])
         attn = self._attend(qkv, ctx, cache)
-        kernels.gemm_skinny(self.w_o, residual, kernels.EPI_ADD_RESIDUAL, T, x=attn)
+        out = norm_handover(self, "attn", ctx, residual.shape[1], kernels.SKINNY_UNSTAGED_ROWS) if small else None
+        kernels.gemm_skinny(self.w_o, residual, kernels.EPI_ADD_RESIDUAL, T, x=attn,
+                            hand_out=None if out is None else (out.norm.rms_params()[0], out.xw, out.sums))
+        ctx.hand_out = out
         return True
 
     def _counters(self, max_items: int) -> torch.Tensor:

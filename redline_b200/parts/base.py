@@ -14,6 +14,7 @@ after which a ``PartSpec(kind="my_mixer", ...)`` in a ``ModelSpec`` builds it.
 
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass, field
 from typing import Any, Callable, Dict, List, Optional, Tuple
 
@@ -133,6 +134,38 @@ class Norm(Part):
         return None
 
 
+@dataclass
+class NormHandover:
+    """An RMSNorm that the part before has half done in its last kernel, for the part after it.
+
+    A part whose fused form ends in ``residual += ...`` and that finds ``ctx.next_norm`` set (the norm
+    that will be applied to the stream next, an RMSNorm) may leave, instead of nothing,
+    ``ctx.hand_out = NormHandover(norm, xw, sums)``: xw = bfloat16(residual * norm.weight) and per-row
+    partial sums of residual^2.  The block passes it to the next part's fused form as ``ctx.hand_in``
+    (only if it was made for that part's norm); a part that takes it skips its norm kernel, multiplies
+    xw and scales the rows of the product by rsqrt(sum / width + eps).  A part that knows nothing of
+    this ignores both fields and norms the stream itself."""
+
+    norm: "Norm"
+    xw: torch.Tensor        # [T, H] bfloat16
+    sums: torch.Tensor      # [T, n] float32; a row's sum of squares is sums[row].sum()
+
+
+def norm_handover(part: "Part", name: str, ctx, width: int, rows: int) -> Optional[NormHandover]:
+    """The hand-over that ``part``'s last product is to fill for ``ctx.next_norm`` (buffers named after
+    ``name`` in the workspace, for up to ``rows`` rows), or None if there is no such norm or it is not an
+    RMSNorm of this width.  ``REDLINE_NORM_HANDOVER=0`` turns hand-overs off (every norm its own kernel)."""
+    norm = ctx.next_norm
+    if norm is None or os.environ.get("REDLINE_NORM_HANDOVER", "1") == "0":
+        return None
+    rms = norm.rms_params()
+    if rms is None or rms[0].numel() != width:
+        return None
+    ws = part.rt.workspace
+    return NormHandover(norm, ws.get(name + ".hand_xw", (rows, width), torch.bfloat16),
+                        ws.get(name + ".hand_sums", (rows, (width + 15) // 16), torch.float32))
+
+
 class PositionEncoding(Part):
     """How positions enter a mixer.  A rotary encoding exposes ``rotary_tables()``
     (cos, sin [max_pos, D/2] float32) and the attention mixer rotates q and k in the
@@ -163,7 +196,8 @@ class Mixer(Part):
                      state: Optional[torch.Tensor]) -> bool:
         """Optional fused form for small batches: residual += mixer(norm(residual)), the norm
         computed by the mixer's first kernel and the add by its last.  Returns False (and
-        does nothing) when the part does not take this batch that way."""
+        does nothing) when the part does not take this batch that way.  ``ctx.hand_in`` /
+        ``ctx.next_norm`` / ``ctx.hand_out``: see ``NormHandover`` (optional)."""
         return False
 
 
@@ -207,6 +241,11 @@ class Block:
 
     def parts(self) -> List[Part]:
         return [self.mixer_norm, self.mixer, self.ffn_norm, self.ffn]
+
+    def first_norm(self) -> Optional[Norm]:
+        """The norm this block applies to the incoming stream first, if the block before may hand it
+        over (``NormHandover``); None if the block does not begin with a norm of the stream."""
+        return None
 
     def forward(self, residual: torch.Tensor, pending: Optional[torch.Tensor], ctx,
                 cache: Optional[LayerCache], state: Optional[torch.Tensor]) -> Optional[torch.Tensor]:

@@ -11,7 +11,7 @@ import torch
 
 from ..ops import kernels
 from ..ops.linear import linear
-from .base import FeedForward, register
+from .base import FeedForward, norm_handover, register
 from .spec import TensorSpec
 
 
@@ -82,7 +82,13 @@ class SwiGLUMLP(FeedForward):
                 or not kernels.skinny_ok(T, self.w_gate_up, rt.dtype) or not kernels.skinny_ok(T, self.w_down, rt.dtype)):
             return False
         act = rt.workspace.get("ffn.act", (rt.max_tokens, p.intermediate_size), rt.dtype)[:T]
-        if T <= kernels.SKINNY_UNSTAGED_ROWS:
+        small = T <= kernels.SKINNY_UNSTAGED_ROWS
+        hand = ctx.hand_in if small else None
+        if hand is not None:
+            # the part before left the norm half done: its xw, and the row scales in this product
+            kernels.gemm_skinny(self.w_gate_up, act, kernels.EPI_SWIGLU, T, x=hand.xw[:T], hand_in=hand.sums,
+                                eps=rms[1])
+        elif small:
             # up to 8 rows: the product takes bfloat16 activations straight from global memory (no staging,
             # no barriers in its k loop), which is worth a norm kernel of its own (measured: 2 % of the step)
             xn = rt.workspace.get("ffn.xn", (kernels.SKINNY_UNSTAGED_ROWS, p.hidden_size), rt.dtype)[:T]
@@ -91,5 +97,8 @@ class SwiGLUMLP(FeedForward):
         else:
             kernels.gemm_skinny(self.w_gate_up, act, kernels.EPI_SWIGLU, T, residual=residual, norm_w=rms[0],
                                 eps=rms[1])
-        kernels.gemm_skinny(self.w_down, residual, kernels.EPI_ADD_RESIDUAL, T, x=act)
+        out = norm_handover(self, "ffn", ctx, residual.shape[1], kernels.SKINNY_UNSTAGED_ROWS) if small else None
+        kernels.gemm_skinny(self.w_down, residual, kernels.EPI_ADD_RESIDUAL, T, x=act,
+                            hand_out=None if out is None else (out.norm.rms_params()[0], out.xw, out.sums))
+        ctx.hand_out = out
         return True

@@ -582,6 +582,54 @@ def test_gemm_skinny_norm_prologue_and_gated_epilogue(M, N, K, w32):
     close(act2, want_act, 2e-2)
 
 
+@pytest.mark.parametrize("M,H,N2,K1", [(8, 2048, 3072, 2048), (5, 328, 200, 72), (1, 1000, 96, 8192), (8, 4400, 64, 256)])
+@pytest.mark.parametrize("w32", [False, True])
+def test_gemm_skinny_norm_handed_over_between_two_products(M, H, N2, K1, w32):
+    """residual += x W1^T leaves bfloat16(residual * norm_weight) and per-tile sums of squares; the next
+    product takes them and scales its rows: together the RMSNorm between the two, against float64."""
+    g = torch.Generator(device="cuda").manual_seed(M + H + N2)
+    x = torch.randn(M, K1, device=DEV, generator=g).to(torch.bfloat16)
+    w1 = (torch.randn(H, K1, device=DEV, generator=g) * 0.05).to(torch.bfloat16)
+    res = torch.randn(M + 2, H, device=DEV, generator=g)[:M] * 3
+    nw = (1 + 0.1 * torch.randn(H, device=DEV, generator=g)).to(torch.float32 if w32 else torch.bfloat16)
+    w2 = (torch.randn(2 * N2, H, device=DEV, generator=g) * 0.05).to(torch.bfloat16)
+    eps = 1e-5
+    want_res = res.double() + (x.double() @ w1.double().T).to(torch.bfloat16).double()
+    xw, sums = kernels.norm_handover_buffers(8, H, DEV)
+    xw.fill_(float("nan"))
+    sums.fill_(float("nan"))
+    kernels.gemm_skinny(w1, res, kernels.EPI_ADD_RESIDUAL, M, x=x, hand_out=(nw, xw, sums))
+    close(res, want_res, 1e-2)
+    got = res.double()                                     # what the kernel itself stored
+    close(xw[:M], got * nw.double(), 5e-3)
+    assert torch.isnan(xw[M:]).all()
+    ss = (got * got).sum(1)
+    assert ((sums[:M].double().sum(1) - ss).abs() <= 1e-5 * ss).all()
+    inv = torch.rsqrt(ss / H + eps)[:, None]
+    ref = (xw[:M].double() @ w2.double().T) * inv          # from the xw the kernel stored ...
+    exact = ((got * inv) * nw.double()) @ w2.double().T    # ... and the norm as it is defined
+    y = torch.full((M, 2 * N2), float("nan"), device=DEV, dtype=torch.bfloat16)
+    kernels.gemm_skinny(w2, y, kernels.EPI_BF16, M, x=xw[:M], hand_in=sums, eps=eps)
+    close(y, ref, 1.2e-2)
+    close(y, exact, 1.5e-2)
+    yf = torch.full((M, 2 * N2), float("nan"), device=DEV)
+    kernels.gemm_skinny(w2, yf, kernels.EPI_F32, M, x=xw[:M], hand_in=sums, eps=eps)
+    close(yf, ref, 2e-5)
+    act = torch.full((M, N2), float("nan"), device=DEV, dtype=torch.bfloat16)
+    kernels.gemm_skinny(w2, act, kernels.EPI_SWIGLU, M, x=xw[:M], hand_in=sums, eps=eps)
+    P.STORE_DTYPE = torch.bfloat16
+    try:
+        want_act = P.swiglu(P.stored(ref[:, :N2].cpu()), P.stored(ref[:, N2:].cpu()))
+    finally:
+        P.STORE_DTYPE = None
+    close(act, want_act, 2e-2)
+    # without the hand-over the same call is the plain product
+    kernels.gemm_skinny(w2, yf, kernels.EPI_F32, M, x=xw[:M])
+    close(yf, xw[:M].double() @ w2.double().T, 2e-5)
+    with pytest.raises(kernels.KernelError):               # a hand-over only from `residual +=`
+        kernels.gemm_skinny(w1, torch.zeros(M, H, device=DEV), kernels.EPI_F32, M, x=x, hand_out=(nw, xw, sums))
+
+
 def test_gemm_skinny_refuses_what_it_cannot_do():
     w = torch.zeros(32, 20, device=DEV, dtype=torch.bfloat16)      # K no multiple of 8
     x = torch.zeros(4, 20, device=DEV, dtype=torch.bfloat16)

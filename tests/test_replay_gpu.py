@@ -87,6 +87,33 @@ def test_last_32_tokens_one_by_one(name, dtype, models, engines):
     check_logits(np.concatenate(outs), C.ALL[name], w, toks, dtype, rows=range(n0 - 1, len(toks)))
 
 
+@pytest.mark.parametrize("name", CONFIGS)
+def test_norms_handed_over_between_the_products_of_small_steps(name, models, monkeypatch):
+    """In steps of up to 8 tokens the bfloat16 engine hands every norm but a step's first and last from
+    the product before it to the product after it: fewer launches, the same logits within the tolerance
+    against the oracle as with every norm a kernel of its own."""
+    from redline_b200.ops import kernels
+    d, w = models[name, "bfloat16"]
+    toks = random_tokens(vocab(name), 40, 9)
+    layers = C.ALL[name]["num_hidden_layers"]
+    launches, outs = {}, {}
+    for mode in ("1", "0"):
+        monkeypatch.setenv("REDLINE_NORM_HANDOVER", mode)
+        eng = engine_for(d, "bfloat16")
+        got = [eng.step_tokens([("h", toks[:20], [19])]).cpu().numpy()]
+        i = 20
+        for n in (1, 3, 8, 2, 5, 1):                      # small steps of several sizes
+            before = kernels.LAUNCHES
+            got.append(eng.step_tokens([("h", toks[i:i + n], list(range(n)))]).cpu().numpy())
+            launches.setdefault(mode, []).append(kernels.LAUNCHES - before)
+            i += n
+        eng.close_request("h")
+        outs[mode] = np.concatenate(got)
+        check_logits(outs[mode], C.ALL[name], w, toks[:i], "bfloat16", rows=range(19, i))
+    assert all(a == b - (2 * layers - 1) for a, b in zip(launches["1"], launches["0"])), launches
+    assert rel_max(outs["1"], outs["0"]) < 2e-2
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", CONFIGS)
 def test_portions_of_changing_size(name, dtype, models, engines):
