@@ -55,12 +55,25 @@ struct TcArgs {
   int M, N, K, ldy;
   int n_up;         // kTcSwiglu: row of W where the up rows start (the number of gate rows)
   int tiles_m, tiles_n;
+  int group_n;      // feature tiles per group of the tile order (see tc_tile)
   int* status;
 };
 
-// Persistent: CTA c takes tiles c, c + gridDim.x, ... (features fastest, so CTAs that run together
-// share rows of x and sweep the weights once).  TMEM holds two accumulators: while the epilogue
-// warps drain one tile, the MMAs of the next tile fill the other.
+// The order of the tiles: groups of group_n feature tiles, every row tile of a group before the next
+// group, so that the CTAs that run together (tiles c, c + 1, ...) cover all rows of x and a few tiles of
+// the weights: x stays in L2 and the weights are read from DRAM once.  Gives the tile's row tile and
+// feature tile.
+__device__ __forceinline__ void tc_tile(const TcArgs& a, int tile, int& mt, int& nt) {
+  const int per_group = a.group_n * a.tiles_m;
+  const int grp = tile / per_group, r = tile - grp * per_group;
+  const int n_first = grp * a.group_n;
+  const int gn = min(a.group_n, a.tiles_n - n_first);      // the last group may be narrower
+  mt = r / gn;
+  nt = n_first + r - mt * gn;
+}
+
+// Persistent: CTA c takes tiles c, c + gridDim.x, ... of the order of tc_tile.  TMEM holds two
+// accumulators: while the epilogue warps drain one tile, the MMAs of the next tile fill the other.
 template <int EPI, int kBN>
 __global__ void __launch_bounds__(kTcThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const TcArgs a) {
@@ -118,7 +131,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       // The weights do not depend on earlier kernels of the step: the first stages' weight tiles are
       // asked for before the wait on those kernels, the activation tiles after it.
       const int pre = (blockIdx.x < ntiles) ? min(kStages, nkb) : 0;
-      const int pre_n0 = (blockIdx.x % a.tiles_n) * kTileN;
+      int pre_mt = 0, pre_nt = 0;
+      if (blockIdx.x < ntiles) tc_tile(a, blockIdx.x, pre_mt, pre_nt);
+      const int pre_n0 = pre_nt * kTileN;
       for (int kb = 0; kb < pre; ++kb) {
         mbar_expect_tx(&sh->full[kb], kStageBytesA + kStageBytesB);
         load_b(kb, kb, pre_n0);
@@ -127,7 +142,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       int it = 0, issued = 0;      // it: k blocks over all of this CTA's tiles
       bool ok = true;
       for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
-        const int m0 = (tile / a.tiles_n) * kBM, n0 = (tile % a.tiles_n) * kTileN;
+        int mt, nt;
+        tc_tile(a, tile, mt, nt);
+        const int m0 = mt * kBM, n0 = nt * kTileN;
         for (int kb = 0; kb < nkb; ++kb, ++it) {
           const int s = it % kStages;
           if (it < pre) {          // armed above, the weight tile is on its way
@@ -188,7 +205,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     pdl_wait();        // y (or the residual stream) may still be in use by earlier kernels
     for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++t) {
       const int buf = t & 1;
-      const int m0 = (tile / a.tiles_n) * kBM, n0 = (tile % a.tiles_n) * kTileN;
+      int mt, nt;
+        tc_tile(a, tile, mt, nt);
+        const int m0 = mt * kBM, n0 = nt * kTileN;
       if (!mbar_wait(&sh->acc_full[buf], (t >> 1) & 1, &sh->abort)) break;
       tc_fence_after();
       const int row = m0 + q * 32 + lane;
@@ -300,6 +319,9 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcArgs&
   a.tiles_n = (a.N + tile_n - 1) / tile_n;
   a.tiles_m = (a.M + kBM - 1) / kBM;
   const int tiles = a.tiles_m * a.tiles_n;
+  a.group_n = (sm_count + a.tiles_m / 2) / a.tiles_m;      // a wave of CTAs covers about one group
+  if (a.group_n < 1) a.group_n = 1;
+  if (a.group_n > a.tiles_n) a.group_n = a.tiles_n;
   dim3 grid(tiles < sm_count ? tiles : sm_count);
   launch_kernel(gemm_tc_kernel<EPI, BN>, grid, dim3(kTcThreads), smem, stream, ma, mb, a);
   return static_cast<int>(cudaGetLastError());
