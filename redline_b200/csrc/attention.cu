@@ -264,8 +264,54 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<const uint32_t*>(&h);
 }
 
+// The rotary position encoding and the cache write of the query tokens inside the tensor-core decode
+// kernels, instead of in a kernel of their own before them: what such a kernel needs (cos == nullptr:
+// not done in the kernel).  The token's unrotated q, k and v
+// lie in one row (q at column 0, k at k_col, v at v_col).  A warp rotates the q rows it loads; the one
+// warp that takes the token's own key rotates k, writes k and v into the cache for later steps and
+// uses them for this one.
+struct DecodeRope {
+  const float* cos;        // [max_pos, D / 2]
+  const float* sin;
+  int max_pos;
+  int k_col, v_col;
+  bf16* kcache;            // writable views of the caches
+  bf16* vcache;
+  int* status;             // bit 1 is set for a position outside the tables
+};
+
+// Rotates the pairs (x0[e], x1[e]) of eight packed bfloat16 each by the angles whose cosines and sines
+// start at c and s: y0 = x0 c - x1 s, y1 = x1 c + x0 s in float32, rounded once.
+__device__ __forceinline__ void rope_rotate8(uint4& x0, uint4& x1, const float* c, const float* s) {
+  float a[8], b[8], cc[8], ss[8];
+  const uint32_t w0[4] = {x0.x, x0.y, x0.z, x0.w}, w1[4] = {x1.x, x1.y, x1.z, x1.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    a[2 * i] = __uint_as_float(w0[i] << 16);
+    a[2 * i + 1] = __uint_as_float(w0[i] & 0xFFFF0000u);
+    b[2 * i] = __uint_as_float(w1[i] << 16);
+    b[2 * i + 1] = __uint_as_float(w1[i] & 0xFFFF0000u);
+  }
+  load16(c, cc);
+  load16(c + 4, cc + 4);
+  load16(s, ss);
+  load16(s + 4, ss + 4);
+  uint32_t o0[4], o1[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float y00 = a[2 * i] * cc[2 * i] - b[2 * i] * ss[2 * i];
+    const float y01 = a[2 * i + 1] * cc[2 * i + 1] - b[2 * i + 1] * ss[2 * i + 1];
+    const float y10 = b[2 * i] * cc[2 * i] + a[2 * i] * ss[2 * i];
+    const float y11 = b[2 * i + 1] * cc[2 * i + 1] + a[2 * i + 1] * ss[2 * i + 1];
+    o0[i] = pack_bf16(y00, y01);
+    o1[i] = pack_bf16(y10, y11);
+  }
+  x0 = make_uint4(o0[0], o0[1], o0[2], o0[3]);
+  x1 = make_uint4(o1[0], o1[1], o1[2], o1[3]);
+}
+
 __global__ void __launch_bounds__(128)
-decode_attn_mma_kernel(const DecodeArgs<bf16> a) {
+decode_attn_mma_kernel(const DecodeArgs<bf16> a, const DecodeRope rope) {
   pdl_launch();
   pdl_wait();
   constexpr int DB = kD / 32;   // 32-wide blocks of d for Q.K^T
@@ -295,16 +341,40 @@ decode_attn_mma_kernel(const DecodeArgs<bf16> a) {
   const int ps_shift = __ffs(a.page_size) - 1, ps_mask = a.page_size - 1;   // page sizes are powers of two
 
   // ---- every load of the warp is issued up front: K and V (through the block table), then Q
+  // With rope.cos set the token's own k and v (key ctx - 1) are not in the cache yet: the threads whose
+  // fragments hold them take them from the token's row (k rotated: a thread's pieces db and db + DB / 2
+  // are the pairs d, d + D / 2) and write them into the cache for later steps.
+  const bool fused = rope.cos != nullptr;
+  const int newest = fused ? ctx - 1 : -1;
+  int pos = ctx - 1;
+  if (fused && pos >= rope.max_pos) {
+    if (threadIdx.x == 0) atomicOr(rope.status, 2);
+    pos = 0;
+  }
+  const bf16* trow = a.q + static_cast<size_t>(tok) * a.q_stride;
+  const float* cs = rope.cos + static_cast<size_t>(pos) * (kD / 2) + t * 8;
+  const float* sn = rope.sin + static_cast<size_t>(pos) * (kD / 2) + t * 8;
   uint4 kf[4][DB];
 #pragma unroll
   for (int nt = 0; nt < 4; ++nt) {
     const int key = k0 + nt * 8 + g;
     const bool live = key < ctx;
     const size_t page = live ? bt[key >> ps_shift] : 0;
-    const bf16* kp = a.kcache + (page * a.hkv + kvh) * head_stride + static_cast<size_t>(key & ps_mask) * kD + t * 8;
+    const size_t at = (page * a.hkv + kvh) * head_stride + static_cast<size_t>(key & ps_mask) * kD + t * 8;
+    if (key == newest) {
+      const bf16* kp = trow + rope.k_col + kvh * kD + t * 8;
 #pragma unroll
-    for (int db = 0; db < DB; ++db)
-      kf[nt][db] = live ? *reinterpret_cast<const uint4*>(kp + db * 32) : make_uint4(0, 0, 0, 0);
+      for (int db = 0; db < DB; ++db) kf[nt][db] = *reinterpret_cast<const uint4*>(kp + db * 32);
+#pragma unroll
+      for (int db = 0; db < DB / 2; ++db) rope_rotate8(kf[nt][db], kf[nt][db + DB / 2], cs + db * 32, sn + db * 32);
+#pragma unroll
+      for (int db = 0; db < DB; ++db) *reinterpret_cast<uint4*>(rope.kcache + at + db * 32) = kf[nt][db];
+    } else {
+      const bf16* kp = a.kcache + at;
+#pragma unroll
+      for (int db = 0; db < DB; ++db)
+        kf[nt][db] = live ? *reinterpret_cast<const uint4*>(kp + db * 32) : make_uint4(0, 0, 0, 0);
+    }
   }
   // V pieces: for each 16-key step the keys t*2, t*2+1, t*2+8, t*2+9, d = dg*64 + g*8 ..
   uint4 vf[2][4][DG];
@@ -315,10 +385,20 @@ decode_attn_mma_kernel(const DecodeArgs<bf16> a) {
       const int key = k0 + ks * 16 + t * 2 + (q & 1) + (q >> 1) * 8;
       const bool live = key < ctx;
       const size_t page = live ? bt[key >> ps_shift] : 0;
-      const bf16* vp = a.vcache + (page * a.hkv + kvh) * head_stride + static_cast<size_t>(key & ps_mask) * kD + g * 8;
+      const size_t at = (page * a.hkv + kvh) * head_stride + static_cast<size_t>(key & ps_mask) * kD + g * 8;
+      if (key == newest) {
+        const bf16* vp = trow + rope.v_col + kvh * kD + g * 8;
 #pragma unroll
-      for (int dg = 0; dg < DG; ++dg)
-        vf[ks][q][dg] = live ? *reinterpret_cast<const uint4*>(vp + dg * 64) : make_uint4(0, 0, 0, 0);
+        for (int dg = 0; dg < DG; ++dg) {
+          vf[ks][q][dg] = *reinterpret_cast<const uint4*>(vp + dg * 64);
+          *reinterpret_cast<uint4*>(rope.vcache + at + dg * 64) = vf[ks][q][dg];
+        }
+      } else {
+        const bf16* vp = a.vcache + at;
+#pragma unroll
+        for (int dg = 0; dg < DG; ++dg)
+          vf[ks][q][dg] = live ? *reinterpret_cast<const uint4*>(vp + dg * 64) : make_uint4(0, 0, 0, 0);
+      }
     }
   // Q fragments: rows g and g + 8 of the group, all of d
   uint4 qlo[DB], qhi[DB];
@@ -327,6 +407,13 @@ decode_attn_mma_kernel(const DecodeArgs<bf16> a) {
     const bf16* qp = a.q + static_cast<size_t>(tok) * a.q_stride + static_cast<size_t>(kvh * G) * kD + db * 32 + t * 8;
     qlo[db] = g < G ? *reinterpret_cast<const uint4*>(qp + g * kD) : make_uint4(0, 0, 0, 0);
     qhi[db] = g + 8 < G ? *reinterpret_cast<const uint4*>(qp + (g + 8) * kD) : make_uint4(0, 0, 0, 0);
+  }
+  if (fused) {
+#pragma unroll
+    for (int db = 0; db < DB / 2; ++db) {
+      rope_rotate8(qlo[db], qlo[db + DB / 2], cs + db * 32, sn + db * 32);
+      rope_rotate8(qhi[db], qhi[db + DB / 2], cs + db * 32, sn + db * 32);
+    }
   }
   float o[DG][8][4];
 #pragma unroll
@@ -934,7 +1021,7 @@ namespace {
 
 // The rotary tables and columns for a launch that also rotates q and k and writes the token's k and v
 // into the cache (streaming kernel only).
-struct StreamRopeHost {
+struct DecodeRopeHost {
   const float* cos;
   const float* sin;
   int max_pos, k_col, v_col;
@@ -964,11 +1051,20 @@ inline bool decode_streams(const void* q, int q_stride, const void* kc, const vo
 #endif
 }
 
+// Whether a bfloat16 launch that does not stream goes to the one-partition tensor-core kernel.
+inline bool decode_one_partition(const void* counters, int max_parts, int hq, int hkv, int page_size, int impl) {
+#ifdef RL_HAVE_MMA_DECODE
+  return impl != 1 && impl != 3 && hq / hkv <= 16 && page_size % 16 == 0 && counters != nullptr && max_parts <= kMaxMergeParts;
+#else
+  return false;
+#endif
+}
+
 template <typename T>
 int launch_decode(const void* q, int q_stride, const void* kc, const void* vc, const int32_t* bt,
                   int max_blocks, const int32_t* items, float* part_o, float* part_ml, int max_parts,
                   int* counters, void* out, int out_stride, int nitems, int hq, int hkv, int page_size,
-                  int window, float scale, int impl, const StreamRopeHost* rope, cudaStream_t stream) {
+                  int window, float scale, int impl, const DecodeRopeHost* rope, cudaStream_t stream) {
   DecodeArgs<T> a;
   a.q = static_cast<const T*>(q);
   a.q_stride = q_stride;
@@ -1011,7 +1107,7 @@ int launch_decode(const void* q, int q_stride, const void* kc, const void* vc, c
       // no more CTAs than the launch can have units
       const long long most = static_cast<long long>(nitems) * hkv * max_parts;
       const int ctas = static_cast<int>(most < sms ? most : sms);
-      StreamRope sr = {};
+      DecodeRope sr = {};
       if (rope != nullptr && rope->cos != nullptr) {
         sr.cos = rope->cos;
         sr.sin = rope->sin;
@@ -1029,16 +1125,28 @@ int launch_decode(const void* q, int q_stride, const void* kc, const void* vc, c
       return static_cast<int>(cudaGetLastError());
     }
     if (impl == 3) return static_cast<int>(cudaErrorInvalidValue);
-    if (rope != nullptr && rope->cos != nullptr) return static_cast<int>(cudaErrorInvalidValue);   // only that kernel rotates
     // tensor-core kernel: groups of up to 16 heads, pages that hold whole 16-key steps
-    if (impl != 1 && hq / hkv <= 16 && page_size % 16 == 0 && counters != nullptr && max_parts <= kMaxMergeParts) {
-      launch_kernel(decode_attn_mma_kernel, dim3(grid), dim3(128), 0, stream, a);
+    if (decode_one_partition(counters, max_parts, hq, hkv, page_size, impl)) {
+      DecodeRope sr = {};
+      if (rope != nullptr && rope->cos != nullptr) {
+        if (q_stride % 8 != 0 || ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(kc) | reinterpret_cast<uintptr_t>(vc)) & 15) != 0)
+          return static_cast<int>(cudaErrorInvalidValue);
+        sr.cos = rope->cos;
+        sr.sin = rope->sin;
+        sr.max_pos = rope->max_pos;
+        sr.k_col = rope->k_col;
+        sr.v_col = rope->v_col;
+        sr.kcache = const_cast<bf16*>(a.kcache);
+        sr.vcache = const_cast<bf16*>(a.vcache);
+        sr.status = rope->status;
+      }
+      launch_kernel(decode_attn_mma_kernel, dim3(grid), dim3(128), 0, stream, a, sr);
       return static_cast<int>(cudaGetLastError());
     }
   }
 #endif
   if (impl == 2 || impl == 3) return static_cast<int>(cudaErrorInvalidValue);
-  if (rope != nullptr && rope->cos != nullptr) return static_cast<int>(cudaErrorInvalidValue);
+  if (rope != nullptr && rope->cos != nullptr) return static_cast<int>(cudaErrorInvalidValue);   // only the tensor-core kernels rotate
   launch_kernel(decode_attn_kernel<T>, dim3(grid), dim3(kDecThreads), 0, stream, a);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return static_cast<int>(e);
@@ -1172,12 +1280,25 @@ int rl_attn_decode_streams(int dtype, const void* q, int q_stride, const void* k
                         impl) ? 1 : 0;
 }
 
-// rl_attn_decode for launches that the streaming kernel takes (rl_attn_decode_streams), with the rotary
+// Whether rl_attn_decode_rope takes a launch with these arguments (one of the two tensor-core kernels
+// does, and rows are 16-byte aligned).
+int rl_attn_decode_rope_ok(const void* q, int q_stride, const void* kc, const void* vc, const void* part_o,
+                           const void* counters, const void* out, int out_stride, int max_parts, int nitems, int hq,
+                           int hkv, int page_size, int k_col, int v_col) {
+  if (nitems <= 0 || k_col % 8 != 0 || v_col % 8 != 0) return 0;
+  if (decode_streams(q, q_stride, kc, vc, part_o, counters, out, out_stride, max_parts, nitems, hq, hkv, page_size, 0))
+    return 1;
+  const bool aligned = q_stride % 8 == 0 && ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(kc) |
+                                              reinterpret_cast<uintptr_t>(vc)) & 15) == 0;
+  return decode_one_partition(counters, max_parts, hq, hkv, page_size, 0) && aligned ? 1 : 0;
+}
+
+// rl_attn_decode for launches that a tensor-core kernel takes (rl_attn_decode_rope_ok), with the rotary
 // position encoding and the cache write of the query tokens done in the kernel: q points at rows of
 // UNROTATED [q | ... k at k_col ... | ... v at v_col ...]; cos / sin are float [max_pos, D / 2] tables; a
 // token's position is its context length - 1; its rotated k and its v are written into kc and vc at that
 // position (through the block table).  status: device int, bit 1 is set for a position outside the
-// tables.  Returns cudaErrorInvalidValue where the streaming kernel does not apply.
+// tables.  Returns cudaErrorInvalidValue where neither tensor-core kernel applies.
 int rl_attn_decode_rope(const void* q, int q_stride, void* kc, void* vc, const int32_t* bt, int max_blocks,
                         const int32_t* items, float* part_o, float* part_ml, int max_parts, int* counters, void* out,
                         int out_stride, int nitems, int hq, int hkv, int page_size, int window, float scale,
@@ -1186,7 +1307,7 @@ int rl_attn_decode_rope(const void* q, int q_stride, void* kc, void* vc, const i
   if (nitems <= 0) return 0;
   if (cos_t == nullptr || sin_t == nullptr || status == nullptr || k_col % 8 != 0 || v_col % 8 != 0)
     return static_cast<int>(cudaErrorInvalidValue);
-  StreamRopeHost r = {cos_t, sin_t, max_pos, k_col, v_col, status};
+  DecodeRopeHost r = {cos_t, sin_t, max_pos, k_col, v_col, status};
   return launch_decode<bf16>(q, q_stride, kc, vc, bt, max_blocks, items, part_o, part_ml, max_parts, counters, out,
                              out_stride, nitems, hq, hkv, page_size, window, scale, 0, &r, stream);
 }

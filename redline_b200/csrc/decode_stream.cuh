@@ -123,51 +123,6 @@ __device__ __forceinline__ float ex2_approx(float x) {      // 2^x; -inf gives 0
   return y;
 }
 
-// The rotary position encoding and the cache write of the query token, done in this kernel instead of
-// in a kernel of their own before it (cos == nullptr: not done here).  The token's unrotated q, k and v
-// lie in one row (q at column 0, k at k_col, v at v_col).  A warp rotates the q rows it loads; the one
-// warp that takes the sub-block with the token's own key rotates k, writes k and v into the cache for
-// later steps and into its shared-memory stage for this one.
-struct StreamRope {
-  const float* cos;        // [max_pos, D / 2]
-  const float* sin;
-  int max_pos;
-  int k_col, v_col;
-  bf16* kcache;            // writable views of the caches
-  bf16* vcache;
-  int* status;             // bit 1 is set for a position outside the tables
-};
-
-// Rotates the pairs (x0[e], x1[e]) of eight packed bfloat16 each by the angles whose cosines and sines
-// start at c and s: y0 = x0 c - x1 s, y1 = x1 c + x0 s in float32, rounded once.
-__device__ __forceinline__ void rope_rotate8(uint4& x0, uint4& x1, const float* c, const float* s) {
-  float a[8], b[8], cc[8], ss[8];
-  const uint32_t w0[4] = {x0.x, x0.y, x0.z, x0.w}, w1[4] = {x1.x, x1.y, x1.z, x1.w};
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    a[2 * i] = __uint_as_float(w0[i] << 16);
-    a[2 * i + 1] = __uint_as_float(w0[i] & 0xFFFF0000u);
-    b[2 * i] = __uint_as_float(w1[i] << 16);
-    b[2 * i + 1] = __uint_as_float(w1[i] & 0xFFFF0000u);
-  }
-  load16(c, cc);
-  load16(c + 4, cc + 4);
-  load16(s, ss);
-  load16(s + 4, ss + 4);
-  uint32_t o0[4], o1[4];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const float y00 = a[2 * i] * cc[2 * i] - b[2 * i] * ss[2 * i];
-    const float y01 = a[2 * i + 1] * cc[2 * i + 1] - b[2 * i + 1] * ss[2 * i + 1];
-    const float y10 = b[2 * i] * cc[2 * i] + a[2 * i] * ss[2 * i];
-    const float y11 = b[2 * i + 1] * cc[2 * i + 1] + a[2 * i + 1] * ss[2 * i + 1];
-    o0[i] = pack_bf16(y00, y01);
-    o1[i] = pack_bf16(y10, y11);
-  }
-  x0 = make_uint4(o0[0], o0[1], o0[2], o0[3]);
-  x1 = make_uint4(o1[0], o1[1], o1[2], o1[3]);
-}
-
 __device__ __forceinline__ int atomic_add_acq_rel(int* p, int v) {
   int old;
   asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], %2;" : "=r"(old) : "l"(p), "r"(v) : "memory");
@@ -243,7 +198,7 @@ __device__ __forceinline__ void stream_merge(const DecodeArgs<bf16>& a, const St
 // HI: groups of more than 8 heads (rows g + 8 of the MMA tile are in use).
 template <bool HI>
 __global__ void __launch_bounds__(kStreamThreads, 1)
-decode_attn_stream_kernel(const DecodeArgs<bf16> a, int nitems, const StreamRope rope) {
+decode_attn_stream_kernel(const DecodeArgs<bf16> a, int nitems, const DecodeRope rope) {
   constexpr int DB = kD / 32, DG = kD / 64;
   constexpr float kLog2e = 1.4426950408889634f, kLn2 = 0.6931471805599453f;
   constexpr int CPR = kD / 8;            // 16-byte chunks per row

@@ -338,8 +338,7 @@ def attn_decode_streams(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vc
                         part_o: torch.Tensor, counters: Optional[torch.Tensor], out: torch.Tensor, max_parts: int,
                         nitems: int, num_heads: int, num_kv_heads: int, head_dim: int, page_size: int,
                         impl: int = 0) -> bool:
-    """Whether ``attn_decode`` with these arguments runs the streaming kernel (which can also do the rotary
-    encoding and the cache write of the query tokens: ``attn_decode_rope``)."""
+    """Whether ``attn_decode`` with these arguments runs the streaming kernel."""
     if not q.is_cuda or q.dtype != torch.bfloat16 or head_dim not in (64, 128):
         return False
     f = _fn(_attn(head_dim), "rl_attn_decode_streams",
@@ -349,15 +348,30 @@ def attn_decode_streams(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vc
                   _ptr(out), out.stride(0), max_parts, nitems, num_heads, num_kv_heads, page_size, impl))
 
 
+def attn_decode_rope_ok(qkv: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcache: torch.Tensor,
+                        part_o: torch.Tensor, counters: Optional[torch.Tensor], out: torch.Tensor, max_parts: int,
+                        nitems: int, num_heads: int, num_kv_heads: int, head_dim: int, page_size: int,
+                        k_col: int, v_col: int) -> bool:
+    """Whether ``attn_decode_rope`` takes a launch with these arguments: bfloat16, head size 64 or 128,
+    and one of the two tensor-core decode kernels applies."""
+    if not qkv.is_cuda or qkv.dtype != torch.bfloat16 or head_dim not in (64, 128):
+        return False
+    f = _fn(_attn(head_dim), "rl_attn_decode_rope_ok",
+            [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+             c_int, c_int, c_int])
+    return bool(f(_ptr(qkv), q_stride, _ptr(kcache), _ptr(vcache), _ptr(part_o), _ptr(counters), _ptr(out),
+                  out.stride(0), max_parts, nitems, num_heads, num_kv_heads, page_size, k_col, v_col))
+
+
 def attn_decode_rope(qkv: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcache: torch.Tensor,
                      block_table: torch.Tensor, items: torch.Tensor, part_o: torch.Tensor, part_ml: torch.Tensor,
                      max_parts: int, counters: torch.Tensor, out: torch.Tensor, nitems: int, num_heads: int,
                      num_kv_heads: int, head_dim: int, page_size: int, window: int, scale: float,
                      cos: torch.Tensor, sin: torch.Tensor, k_col: int, v_col: int, status: torch.Tensor) -> None:
-    """``attn_decode`` by the streaming kernel with the rotary encoding and the cache write done in the
+    """``attn_decode`` by a tensor-core kernel with the rotary encoding and the cache write done in the
     kernel: ``qkv`` holds the UNROTATED rows [q | k | v] of the query tokens (k at column ``k_col``, v at
     ``v_col``); a token's position is its context length - 1; its rotated k and its v are written into the
-    cache there.  Only where ``attn_decode_streams`` says so."""
+    cache there.  Only where ``attn_decode_rope_ok`` says so."""
     _need_cuda(qkv, kcache, out)
     f = _fn(_attn(head_dim), "rl_attn_decode_rope",
             [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,

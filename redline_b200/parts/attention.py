@@ -148,13 +148,13 @@ class GQAttention(Mixer):
                             torch.float32)
             part_ml = ws.get("attn.part_ml", (ctx.max_items * p.num_heads * ctx.parts_capacity * 2,),
                              torch.float32)
-            # a step of single tokens only, on the streaming kernel: that kernel rotates q and k itself and
+            # a step of single tokens only, on a tensor-core kernel: that kernel rotates q and k itself and
             # writes the tokens' k and v into the cache, which saves the kernel that does so otherwise
             if (tables is not None and cache.write and ctx.num_decode == T and ctx.num_tiles == 0
-                    and kernels.attn_decode_streams(qkv, self.qkv_size, cache.k, cache.v, part_o,
+                    and kernels.attn_decode_rope_ok(qkv, self.qkv_size, cache.k, cache.v, part_o,
                                                     self._counters(ctx.max_items), attn, ctx.decode_parts,
                                                     ctx.num_decode, p.num_heads, p.num_kv_heads, p.head_dim,
-                                                    rt.page_size)):
+                                                    rt.page_size, self.q_size, self.q_size + self.kv_size)):
                 kernels.attn_decode_rope(qkv, self.qkv_size, cache.k, cache.v, g.block_table, ctx.decode_info,
                                          part_o, part_ml, ctx.decode_parts, self._counters(ctx.max_items), attn,
                                          ctx.num_decode, p.num_heads, p.num_kv_heads, p.head_dim, rt.page_size,

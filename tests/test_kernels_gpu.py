@@ -350,13 +350,16 @@ def test_attention_decode_streaming_kernel_many_units_per_cta():
 
 @pytest.mark.parametrize("Hq,Hkv,D", [(32, 8, 64), (16, 2, 128), (4, 4, 64)])
 @pytest.mark.parametrize("page_size,window", [(16, 0), (64, 0), (16, 300)])
-def test_attention_decode_with_rotation_and_cache_write_in_the_kernel(Hq, Hkv, D, page_size, window):
+@pytest.mark.parametrize("streams", [True, False])
+def test_attention_decode_with_rotation_and_cache_write_in_the_kernel(Hq, Hkv, D, page_size, window, streams):
     """attn_decode_rope against rope_kv_write followed by attn_decode: the same outputs, and the same k and
-    v rows written into the cache at the tokens' own positions (and nowhere else)."""
+    v rows written into the cache at the tokens' own positions (and nowhere else); with many partitions
+    (the streaming kernel) and with few (the one-partition kernel)."""
     from redline_b200.config.model_config import RopeScaling
     from redline_b200.parts.rope import RotaryParams, rope_tables
     g = torch.Generator().manual_seed(51)
-    lens = [700, 1, 129, 2048, 33, 1500, 260, 2047] * 4      # context lengths including the new token
+    lens = [700, 1, 129, 2048, 33, 1500, 260, 2047]          # context lengths including the new token
+    lens = lens * 4 if streams else lens[:5]
     B = len(lens)
     cos, sin = rope_tables(RotaryParams(D, 10000.0, RopeScaling(), 4096), 2200)
     cos, sin = cos.to(DEV).contiguous(), sin.to(DEV).contiguous()
@@ -391,11 +394,14 @@ def test_attention_decode_with_rotation_and_cache_write_in_the_kernel(Hq, Hkv, D
     kernels.rope_kv_write(qkv1, pos, slots, cos, sin, kc1, vc1, Hq, Hkv, D, page_size, status)
     po, pm, cnt, want = buffers()
     kernels.attn_decode(qkv1, qkv1.shape[1], kc1, vc1, btd, items, po, pm, parts, cnt, want, B, Hq, Hkv, D,
-                        page_size, window, scale, 3)
+                        page_size, window, scale, 3 if streams else 2)
     # the one kernel
     kc2, vc2, qkv2 = kc0.clone(), vc0.clone(), qkv0.clone()
     po, pm, cnt, got = buffers()
-    assert kernels.attn_decode_streams(qkv2, qkv2.shape[1], kc2, vc2, po, cnt, got, parts, B, Hq, Hkv, D, page_size)
+    assert kernels.attn_decode_streams(qkv2, qkv2.shape[1], kc2, vc2, po, cnt, got, parts, B, Hq, Hkv, D,
+                                       page_size) == streams
+    assert kernels.attn_decode_rope_ok(qkv2, qkv2.shape[1], kc2, vc2, po, cnt, got, parts, B, Hq, Hkv, D, page_size,
+                                       Hq * D, (Hq + Hkv) * D)
     kernels.attn_decode_rope(qkv2, qkv2.shape[1], kc2, vc2, btd, items, po, pm, parts, cnt, got, B, Hq, Hkv, D,
                              page_size, window, scale, cos, sin, Hq * D, (Hq + Hkv) * D, status)
     assert status.item() == 0 and int(cnt.abs().max()) == 0
