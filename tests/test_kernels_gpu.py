@@ -417,6 +417,16 @@ def test_attention_decode_with_rotation_and_cache_write_in_the_kernel(Hq, Hkv, D
     assert not (changed & ~allowed).any()
 
 
+@pytest.mark.parametrize("window", [0, 200])
+def test_attention_decode_streaming_kernel_many_short_rows(window):
+    """Several rows per SM, short and long ones side by side, rows that end exactly at a partition's end,
+    one-key rows."""
+    lens = [516] * 24 + [1500, 33, 1, 129, 2048, 700, 1025, 260, 128, 1024] * 4
+    decode_only_case(32, 8, 64, lens, 16, window, 3, seed=37)
+    decode_only_case(32, 8, 64, lens[::-1], 16, window, 0, seed=38)
+    decode_only_case(16, 8, 128, [516, 77, 1300, 640] * 16, 32, window, 3, seed=39)
+
+
 def test_attention_decode_beyond_256_partitions():
     """A context of 40,000 keys has 313 partitions, more than the one-partition kernel can merge: the
     default choice must take the streaming kernel there (and the CUDA-core kernel must agree)."""
