@@ -162,6 +162,31 @@ def bench_gemm_tc(args) -> None:
                       "frac_of_measured_bf16": round(flops / us / 1e6 / pk["bf16_tflops"], 3), "copies": copies}))
 
 
+def bench_gemm_mid(args) -> None:
+    dev = "cuda"
+    M, N, K = args.rows, args.n, args.k
+    epi = {"bf16": kernels.EPI_BF16, "swiglu": kernels.EPI_SWIGLU}[args.epilogue]
+    wn = 2 * N if epi == kernels.EPI_SWIGLU else N
+    copies = max(2, min(args.copies, int(1e9 // (wn * K * 2))))
+    ws = [(torch.randn(wn, K, device=dev) * 0.02).to(torch.bfloat16) for _ in range(copies)]
+    x = torch.randn(M, K, device=dev).to(torch.bfloat16)
+    y = torch.zeros(M, N, device=dev, dtype=torch.bfloat16)
+    yl = torch.empty(M, wn, device=dev, dtype=torch.bfloat16)
+
+    def fn(i):
+        if args.library:
+            torch.mm(x, ws[i % copies].t(), out=yl)
+        else:
+            kernels.gemm_mid(x, ws[i % copies], y, epi)
+
+    us = graph_time_us(fn, copies, use_graph=not args.no_graph)
+    nbytes = wn * K * 2
+    pk = peaks()
+    print(json.dumps({"kernel": "library_mm" if args.library else "gemm_mid", "rows": M, "n": N, "k": K,
+                      "epilogue": args.epilogue, "us": round(us, 2), "GB/s": round(nbytes / us / 1e3, 1),
+                      "frac_of_measured_hbm": round(nbytes / us / 1e3 / pk["hbm_gbs"], 3), "copies": copies}))
+
+
 def bench_attn_prefill(args) -> None:
     dev = "cuda"
     T, Hq, Hkv, D, ps = args.tokens, args.heads, args.kv_heads, args.head_dim, args.page_size
@@ -193,7 +218,7 @@ def bench_attn_prefill(args) -> None:
 def main() -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     sub = ap.add_subparsers(dest="kernel", required=True)
-    for name in ("attn_decode", "attn_prefill", "skinny", "gemm_tc"):
+    for name in ("attn_decode", "attn_prefill", "skinny", "gemm_tc", "gemm_mid"):
         p = sub.add_parser(name)
         p.add_argument("--heads", type=int, default=32)
         p.add_argument("--kv-heads", type=int, default=8)
@@ -224,12 +249,18 @@ def main() -> int:
             p.add_argument("--hand-in", action="store_true", help="take a norm that was handed over (at most 8 rows)")
             p.add_argument("--epilogue", default="bf16", choices=["bf16", "f32", "residual", "swiglu"])
             p.add_argument("--library", action="store_true", help="time the library product instead")
+        if name == "gemm_mid":
+            p.add_argument("--rows", type=int, default=64)
+            p.add_argument("--n", type=int, default=3072)
+            p.add_argument("--k", type=int, default=2048)
+            p.add_argument("--epilogue", default="bf16", choices=["bf16", "swiglu"])
+            p.add_argument("--library", action="store_true", help="time the library product instead")
     args = ap.parse_args()
     if not torch.cuda.is_available():
         print("kernel_bench needs a CUDA device", file=sys.stderr)
         return 1
     {"attn_decode": bench_attn_decode, "attn_prefill": bench_attn_prefill, "skinny": bench_skinny,
-     "gemm_tc": bench_gemm_tc}[args.kernel](args)
+     "gemm_tc": bench_gemm_tc, "gemm_mid": bench_gemm_mid}[args.kernel](args)
     return 0
 
 

@@ -187,6 +187,8 @@ class ModelRunner:
                 what.append("a wait inside the tcgen05 matrix product that ran out")
             if tc_code & 4:
                 what.append("a wait inside the tcgen05 attention that ran out")
+            if tc_code & 8:
+                what.append("a wait inside the tcgen05 product for few rows that ran out")
             raise EngineError("a kernel met " + " and ".join(what))
 
     def memory_report(self) -> Dict[str, int]:

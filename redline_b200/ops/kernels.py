@@ -259,7 +259,7 @@ _tc_status: Dict[int, torch.Tensor] = {}
 
 def tc_status(device: torch.device) -> torch.Tensor:
     """The device word in which the tcgen05 kernels report a wait that ran out (bit 0: gemm_tc,
-    bit 2: prompt-portion attention)."""
+    bit 2: prompt-portion attention, bit 3: gemm_mid)."""
     i = device.index if device.index is not None else torch.cuda.current_device()
     if i not in _tc_status:
         _tc_status[i] = torch.zeros(1, dtype=torch.int32, device=device)
@@ -287,6 +287,60 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, epilogue: int = E
         raise KernelError(f"gemm_tc: shapes x{tuple(x.shape)} w{tuple(w.shape)} y{tuple(y.shape)} {y.dtype}")
     _check(f(_ptr(x), x.stride(0), _ptr(w), _ptr(y), y.stride(0), epilogue, M, N, K, _ptr(tc_status(x.device)),
              sm_count(x.device), tile_n, _stream()), "gemm_tc")
+
+
+# ------------------------------------------------- tcgen05 gemm for 17 to 128 rows
+
+MID_MAX_ROWS = 128
+_mid_scratch: Dict[int, Tuple[torch.Tensor, torch.Tensor]] = {}
+
+
+def gemm_mid_ok(rows: int, x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether gemm_mid takes this product: at most 128 rows, bfloat16 operands, K a multiple of 8,
+    16-byte aligned rows."""
+    return 0 < rows <= MID_MAX_ROWS and gemm_tc_ok(x, w)
+
+
+def _mid_workspace(device: torch.device, floats: int, counters: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """The scratch area of the split products and their arrival counters (zero between launches), shared
+    by all products of a device (launches on a stream run one after another) and of a fixed size, so that
+    CUDA graphs keep pointing at it: a split product has at most one partial tile of 128 x 128 per SM."""
+    i = device.index if device.index is not None else torch.cuda.current_device()
+    if i not in _mid_scratch:
+        _mid_scratch[i] = (torch.empty(sm_count(device) * 128 * 128, dtype=torch.float32, device=device),
+                           torch.zeros(1 << 16, dtype=torch.int32, device=device))
+    part, cnt = _mid_scratch[i]
+    if part.numel() < floats or cnt.numel() < counters:
+        raise KernelError("gemm_mid: the product needs more scratch than the package keeps")
+    return part, cnt
+
+
+def gemm_mid(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, epilogue: int = EPI_BF16) -> None:
+    """y = epilogue(x @ w^T) for up to 128 rows with tcgen05 tensor cores (csrc/gemm_mid.cu): the weight
+    rows are the 128-row operand, the tokens the narrow one, K is split over CTAs and the partial tiles
+    are added in a fixed order.  bfloat16 x [M, K], w [N, K] (EPI_SWIGLU: [2 N, K], gate rows then up
+    rows), y bfloat16 [M, N]; epilogue EPI_BF16 or EPI_SWIGLU.
+
+    The engine does not route any product here yet: at 64 rows the library's kernels are faster (measured
+    on a B200, weights of 1B-model size: 10.8 / 11.9 / 16.4 / 20.1 us for the qkv, o, down and gated
+    gate/up shapes against 5.7 / 5.4 / 12.8 / 12.5 + 3.6 us)."""
+    _need_cuda(x, w, y)
+    lib = _lib("gemm_mid", "gemm_mid.cu")
+    f = _fn(lib, "rl_gemm_mid", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                                 c_void_p, c_void_p, c_int, c_void_p])
+    size = _fn(lib, "rl_gemm_mid_workspace", [c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+    M, K = x.shape
+    gated = epilogue == EPI_SWIGLU
+    N = w.shape[0] // 2 if gated else w.shape[0]
+    if (epilogue not in (EPI_BF16, EPI_SWIGLU) or w.shape[1] != K or y.dtype != torch.bfloat16 or y.shape[1] != N
+            or y.stride(1) != 1 or not gemm_mid_ok(M, x, w)):
+        raise KernelError(f"gemm_mid: shapes x{tuple(x.shape)} w{tuple(w.shape)} y{tuple(y.shape)} {y.dtype}")
+    floats, counters = ctypes.c_longlong(0), ctypes.c_int(0)
+    size(M, N, K, 1 if gated else 0, sm_count(x.device), ctypes.byref(floats), ctypes.byref(counters))
+    part, cnt = _mid_workspace(x.device, floats.value, counters.value)
+    _check(f(_ptr(x), x.stride(0), _ptr(w), _ptr(y), y.stride(0), epilogue, M, N, K, _ptr(part), _ptr(cnt),
+             _ptr(tc_status(x.device)), sm_count(x.device), _stream()), "gemm_mid")
+
 
 # ------------------------------------------------------------------- attention
 
@@ -447,6 +501,7 @@ def build_all(head_dims=(64, 128), verbose: bool = True) -> None:
     build.compile_module("gemm_simt", "gemm_simt.cu", verbose=verbose)
     build.compile_module("gemm_skinny", "gemm_skinny.cu", verbose=verbose)
     build.compile_module("gemm_tc", "gemm_tc.cu", verbose=verbose)
+    build.compile_module("gemm_mid", "gemm_mid.cu", verbose=verbose)
     build.compile_module("sampling", "sampling.cu", verbose=verbose)
     build.compile_module("host_core", "host_core.cpp", verbose=verbose)     # host-only: cache manager, batch filler
     for d in head_dims:

@@ -659,6 +659,43 @@ def test_gemm_skinny_refuses_what_it_cannot_do():
                             x=torch.zeros(4, 64, device=DEV, dtype=torch.bfloat16))
 
 
+MID_SHAPES = [(64, 3072, 2048), (17, 2048, 8192), (128, 331, 200), (33, 1000, 72), (100, 704, 256), (1, 128, 8),
+              (96, 8192, 2048), (32, 64, 4096)]
+
+
+@pytest.mark.parametrize("M,N,K", MID_SHAPES)
+def test_gemm_mid_epilogues(M, N, K):
+    """The tcgen05 product for up to 128 rows (weights as the wide operand, K split over CTAs) against
+    float64: both epilogues, edge tiles in N and K, every width of the token operand; a second run gives
+    the same bits (the partial tiles are added in a fixed order, the counters are left at zero)."""
+    g = torch.Generator(device="cuda").manual_seed(M + N + K)
+    x = torch.randn(M + 2, K, device=DEV, generator=g).to(torch.bfloat16)[:M]
+    w = (torch.randn(2 * N, K, device=DEV, generator=g) * 0.05).to(torch.bfloat16)
+    ref = x.double() @ w.double().T
+    status = kernels.tc_status(x.device)
+    y = torch.full((M, 2 * N), float("nan"), device=DEV, dtype=torch.bfloat16)
+    kernels.gemm_mid(x, w, y, kernels.EPI_BF16)
+    close(y, ref, 1.2e-2)
+    y2 = torch.full((M + 1, 2 * N + 8), float("nan"), device=DEV, dtype=torch.bfloat16)[:M, :2 * N]    # a strided output
+    kernels.gemm_mid(x, w, y2, kernels.EPI_BF16)
+    assert torch.equal(y2, y)
+    act = torch.full((M, N), float("nan"), device=DEV, dtype=torch.bfloat16)
+    kernels.gemm_mid(x, w, act, kernels.EPI_SWIGLU)
+    P.STORE_DTYPE = torch.bfloat16
+    try:
+        want_act = P.swiglu(P.stored(ref[:, :N].cpu()), P.stored(ref[:, N:].cpu()))
+    finally:
+        P.STORE_DTYPE = None
+    close(act, want_act, 2e-2)
+    act2 = torch.empty_like(act)
+    kernels.gemm_mid(x, w, act2, kernels.EPI_SWIGLU)
+    assert torch.equal(act2, act)
+    assert int(status.item()) == 0
+    with pytest.raises(kernels.KernelError):
+        kernels.gemm_mid(torch.zeros(129, K, device=DEV, dtype=torch.bfloat16), w,
+                         torch.zeros(129, 2 * N, device=DEV, dtype=torch.bfloat16))
+
+
 TC_SHAPES = [(128, 128, 64), (17, 331, 200), (256, 384, 512), (130, 200, 72), (2048, 3072, 2048), (300, 1000, 384),
              (1, 128, 8), (640, 2048, 8192)]
 
