@@ -129,3 +129,18 @@ def compile_module(name: str, source: str, defines: Optional[Dict[str, object]] 
             print(f"[redline_b200] compiled {name} in {time.time() - t0:.1f} s -> {out}",
                   file=sys.stderr, flush=True)
     return out
+
+
+def remove_other_versions(paths: Iterable[str]) -> None:
+    """Deletes, next to each of the given built files ``<module>-<key>.so``, the files of the same module
+    with another key (built from other versions of the sources; nothing loads them any more)."""
+    for path in paths:
+        folder, name = os.path.split(path)
+        module = name.rsplit("-", 1)[0]
+        for other in os.listdir(folder):
+            if other != name and other.endswith(".so") and other.rsplit("-", 1)[0] == module:
+                try:
+                    os.remove(os.path.join(folder, other))
+                except OSError:
+                    pass
+

@@ -496,13 +496,17 @@ def gather_logprob(logits: torch.Tensor, rows: int, target: torch.Tensor, out: t
 
 
 def build_all(head_dims=(64, 128), verbose: bool = True) -> None:
-    """Compiles every kernel family (attention for the given head sizes)."""
-    build.compile_module("elementwise", "elementwise.cu", verbose=verbose)
-    build.compile_module("gemm_simt", "gemm_simt.cu", verbose=verbose)
-    build.compile_module("gemm_skinny", "gemm_skinny.cu", verbose=verbose)
-    build.compile_module("gemm_tc", "gemm_tc.cu", verbose=verbose)
-    build.compile_module("gemm_mid", "gemm_mid.cu", verbose=verbose)
-    build.compile_module("sampling", "sampling.cu", verbose=verbose)
-    build.compile_module("host_core", "host_core.cpp", verbose=verbose)     # host-only: cache manager, batch filler
+    """Compiles every kernel family (attention for the given head sizes) and removes built files of
+    these modules that belong to other versions of the sources."""
+    built = [
+        build.compile_module("elementwise", "elementwise.cu", verbose=verbose),
+        build.compile_module("gemm_simt", "gemm_simt.cu", verbose=verbose),
+        build.compile_module("gemm_skinny", "gemm_skinny.cu", verbose=verbose),
+        build.compile_module("gemm_tc", "gemm_tc.cu", verbose=verbose),
+        build.compile_module("gemm_mid", "gemm_mid.cu", verbose=verbose),
+        build.compile_module("sampling", "sampling.cu", verbose=verbose),
+        build.compile_module("host_core", "host_core.cpp", verbose=verbose),   # host-only: cache manager, batch filler
+    ]
     for d in head_dims:
-        build.compile_module(f"attention_d{d}", "attention.cu", {"RL_HEAD_DIM": d}, verbose=verbose)
+        built.append(build.compile_module(f"attention_d{d}", "attention.cu", {"RL_HEAD_DIM": d}, verbose=verbose))
+    build.remove_other_versions(built)
