@@ -279,6 +279,34 @@ def profile_step(args) -> int:
     return 0
 
 
+def profile_prefill(args) -> int:
+    """One prompt of PREFILL_TOKENS tokens between cudaProfilerStart and cudaProfilerStop (after three
+    untimed ones), for `ncu --profile-from-start off`."""
+    import numpy as np
+    import torch
+    from redline_b200.engine.engine import Engine
+    tmp = tempfile.mkdtemp(prefix="redline_bench_")
+    try:
+        model = write_model(tmp, args.layers)
+        T = PREFILL_TOKENS
+        eng = Engine(model, dtype="bfloat16", max_num_seqs=2, max_num_batched_tokens=T, max_seq_len=T + 16,
+                     kv_cache_tokens=2 * T + 64, cuda_graphs=False, async_scheduling=False)
+        toks = np.random.RandomState(1).randint(0, eng.vocab_size, size=T).tolist()
+        for i in range(4):
+            torch.cuda.synchronize()
+            if i == 3:
+                torch.cuda.profiler.start()
+            eng.step_tokens([("p", toks, [T - 1])])
+            torch.cuda.synchronize()
+            if i == 3:
+                torch.cuda.profiler.stop()
+            eng.close_request("p")
+        print(json.dumps({"profiled": "one prompt step", "tokens": T}))
+    finally:
+        shutil.rmtree(tmp, ignore_errors=True)
+    return 0
+
+
 def prefill_run(model: str, tokens: int, reps: int = 6, warmup: int = 3) -> Dict[str, Any]:
     """Prompts of ``tokens`` tokens through Engine.step_tokens (host token ids in, logits of the last
     position on the device).  "ms": per prompt when ``reps`` prompts are submitted one after another
@@ -420,6 +448,7 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration has (named in config)")
     ap.add_argument("--profile-step", action="store_true", help="bracket one decode step with cudaProfilerStart/Stop and exit")
+    ap.add_argument("--profile-prefill", action="store_true", help="bracket one prompt step of 2,048 tokens with cudaProfilerStart/Stop and exit")
     ap.add_argument("--profile-batch", type=int, default=BATCH)
     ap.add_argument("--profile-prompt", type=int, default=0, help="with --profile-step: prompt length (default: context - 96)")
     ap.add_argument("--profile-eager", action="store_true", help="with --profile-step: no CUDA graph")
@@ -429,6 +458,8 @@ def main() -> int:
         return 2
     if args.profile_step:
         return profile_step(args)
+    if args.profile_prefill:
+        return profile_prefill(args)
     args.warmup = max(args.warmup, 3)
     args.steps = max(1, min(args.steps, 1000))
     res = run_reference(args) if args.impl == "reference" else run_ours(args)
