@@ -254,8 +254,20 @@ __global__ void rope_kv_write_kernel(TA* __restrict__ qkv, const int32_t* __rest
   const int off = slot >= 0 ? slot % page_size : 0;
   const int rot_heads = hq + hkv;
   const int vec_per_head = half / VEC;
-  // one (head, run of VEC pairs (i, i + D/2)) per thread-iteration over q and k heads
-  for (int idx = threadIdx.x; idx < rot_heads * vec_per_head; idx += blockDim.x) {
+  // One item per thread and round: a (head, run of VEC pairs (i, i + D/2)) of the q and k heads, or a
+  // 16-byte piece of v for the cache.  Both kinds are in one loop, so that all of a token's loads are in
+  // flight together.
+  const int n_rot = rot_heads * vec_per_head;
+  const int n_v = slot >= 0 ? hkv * d / VEC : 0;
+  for (int idx = threadIdx.x; idx < n_rot + n_v; idx += blockDim.x) {
+    if (idx >= n_rot) {
+      const int e0 = (idx - n_rot) * VEC;
+      const int h = e0 / d, i = e0 - h * d;
+      const TA* vrow = row + (hq + hkv) * d;
+      *reinterpret_cast<uint4*>(vcache + ((page * hkv + h) * page_size + off) * d + i) =
+          *reinterpret_cast<const uint4*>(vrow + e0);
+      continue;
+    }
     const int h = idx / vec_per_head, i = (idx - h * vec_per_head) * VEC;
     TA* v = row + h * d;
     float x0[VEC], x1[VEC];
@@ -283,14 +295,6 @@ __global__ void rope_kv_write_kernel(TA* __restrict__ qkv, const int32_t* __rest
       TA* dst = kcache + ((page * hkv + (h - hq)) * page_size + off) * d;
       store16(dst + i, x0);
       store16(dst + i + half, x1);
-    }
-  }
-  if (slot >= 0) {
-    const TA* vrow = row + (hq + hkv) * d;
-    for (int idx = threadIdx.x * VEC; idx < hkv * d; idx += blockDim.x * VEC) {
-      const int h = idx / d, i = idx - h * d;
-      *reinterpret_cast<uint4*>(vcache + ((page * hkv + h) * page_size + off) * d + i) =
-          *reinterpret_cast<const uint4*>(vrow + idx);
     }
   }
 }
