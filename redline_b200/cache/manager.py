@@ -189,6 +189,21 @@ class CacheManager:
         if code < 0:
             _raise_free_error(code, bad.value)
 
+    def adopt(self, key: object, rid: int) -> RequestCache:
+        """The face of a request that native code (the scheduler's planner) has opened in the core."""
+        if key in self._open:
+            raise CacheError(f"request {key!r} is already open")
+        rc = RequestCache(key, rid, self._lib.rl_hc_state_slot(self._h, rid), self)
+        self._open[key] = rc
+        if self.on_open is not None:
+            self.on_open(rc)
+        return rc
+
+    def forget(self, key: object) -> None:
+        """Drops the face of a request that native code has already closed in the core."""
+        if self._open.pop(key, None) is None:
+            raise CacheError(f"request {key!r} is not open")
+
     def num_open(self) -> int:
         return len(self._open)
 

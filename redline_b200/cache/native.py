@@ -1,11 +1,11 @@
 """ctypes binding of the native host core (``csrc/host_core.cpp``): page pools, the cache
-manager's state and the routine that fills a step's metadata buffer.  The shared object
+manager's state, the scheduler's planner and the routine that fills a step's metadata buffer.  The shared object
 is host-only code, compiled at first use like the kernels."""
 
 from __future__ import annotations
 
 import ctypes
-from ctypes import POINTER, c_char_p, c_float, c_int, c_int32, c_uint32, c_void_p
+from ctypes import POINTER, c_char_p, c_double, c_float, c_int, c_int32, c_uint32, c_void_p
 
 from ..ops import build
 
@@ -24,6 +24,16 @@ class RlSegment(ctypes.Structure):
                 ("token_off", c_int32), ("want_off", c_int32), ("num_want", c_int32), ("has_sampling", c_int32),
                 ("temperature", c_float), ("top_p", c_float), ("top_k", c_int32), ("seed_lo", c_uint32),
                 ("seed_hi", c_uint32)]
+
+
+class RlSchedCfg(ctypes.Structure):
+    _fields_ = [("max_num_seqs", c_int32), ("budget", c_int32), ("max_seq_len", c_int32), ("mix", c_int32),
+                ("watermark", c_double)]
+
+
+SCHED_SEQ_FIELDS = ("rid", "known", "pending", "computed", "prompt_len", "max_new", "pending_ok", "pending_row",
+                    "where", "preempted", "cache_changed")       # RlSchedSeq: int32 each
+SCHED_ENTRY_FIELDS = ("seq", "start_pos", "num_tokens", "sample", "from_device", "src_row")   # RlSchedEntry
 
 
 # the same record as a numpy dtype (a step's segments are marshalled in one call)
@@ -69,6 +79,8 @@ def lib() -> ctypes.CDLL:
             "rl_hc_build": (c_int, [c_void_p, c_void_p, POINTER(RlLayout), i32p, i32p, c_int, c_int, c_int,
                                     c_void_p, c_void_p, c_void_p, c_int, c_int, i32p]),
             "rl_hc_pad": (None, [c_void_p, POINTER(RlLayout), c_int, c_int]),
+            "rl_sched_plan": (c_int, [c_void_p, POINTER(RlSchedCfg), c_void_p, c_int, c_int, c_void_p, c_void_p,
+                                      c_void_p, c_void_p, c_void_p]),
         }
         for name, (res, args) in sig.items():
             f = getattr(L, name)

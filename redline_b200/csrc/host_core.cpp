@@ -1,8 +1,9 @@
-// The host side of the cache and of a step's metadata, in C++: page pools with LIFO reuse,
-// per-request block tables for every cache group, window release, state slots, and the
-// routine that fills a step's pinned metadata buffer.  No CUDA in this file: it is
+// The host side of the cache, of the scheduler and of a step's metadata, in C++: page pools with
+// LIFO reuse, per-request block tables for every cache group, window release, state slots, the
+// scheduler's plan of a step (at the end of the file), and the routine that fills a step's pinned
+// metadata buffer.  No CUDA in this file: it is
 // compiled as a host-only shared object and bound with ctypes (redline_b200/cache/manager.py,
-// redline_b200/engine/batch.py).
+// redline_b200/engine/scheduler.py, redline_b200/engine/batch.py).
 //
 // Policy of the reference's block allocator (src/core/block_allocator.cpp:7-35): pages are
 // handed out lowest id first and reused last-freed first; page 0 of every pool is never handed
@@ -438,6 +439,239 @@ void rl_hc_pad(int32_t* out, const RlLayout* lay, int from, int to) {
     std::memcpy(out + lay->top_p + i, &one, 4);
     out[lay->sample_pos + i] = 1;
   }
+}
+
+}  // extern "C"
+
+// ------------------------------------------------------------------ the scheduler's plan of one step
+// Policy of the reference's scheduler (src/core/scheduler.cpp:104-218): under a token budget, first one
+// token for every running sequence that is decoding, then portions of prompts (running sequences that
+// are mid-prompt first, then admissions from the front of the waiting queue while a watermark of pages
+// stays free, unless nothing is running).  A decoding sequence that cannot get its next page preempts
+// the newest running sequence that is not in the plan yet (all its pages go back, it is queued again at
+// the front), or itself if there is none.  If nothing could be planned while sequences are stuck
+// mid-prompt, the newest are freed until the oldest goes on.
+//
+// The caller passes the running sequences in admission order followed by the front of the waiting
+// queue; the planner works on the cache manager's state directly (opens, reserves, closes) and gives
+// back, per sequence, its new request id, computed count and queue, the queues' new orders and the
+// entries of the plan.
+struct RlSchedSeq {
+  int32_t rid;            // in/out: the sequence's request in the cache manager, -1: none
+  int32_t known;          // tokens the host knows (prompt + received samples)
+  int32_t pending;        // tokens sampled on the GPU that the host has not read yet
+  int32_t computed;       // in/out: positions whose cache writes have been enqueued
+  int32_t prompt_len;
+  int32_t max_new;
+  int32_t pending_ok;     // the pending token is the previous step's: it can be read on the device
+  int32_t pending_row;
+  int32_t where;          // in/out: 0 running, 1 waiting; out also 2: parked (preempted with a token in flight)
+  int32_t preempted;      // out: times preempted in this call
+  int32_t cache_changed;  // out: its request was opened or closed in this call
+};
+
+struct RlSchedCfg {
+  int32_t max_num_seqs, budget, max_seq_len, mix;
+  double watermark;       // fraction of a group's pages that an admission must leave free
+};
+
+struct RlSchedEntry {
+  int32_t seq, start_pos, num_tokens, sample, from_device, src_row;
+};
+
+namespace {
+
+struct Planner {
+  Core* c;
+  RlSchedCfg cfg;
+  RlSchedSeq* s;
+  std::vector<int> running, waiting, parked;
+  std::vector<RlSchedEntry> plan;
+  int budget = 0, num_preempted = 0, error_seq = -1;
+
+  int total(int i) const { return s[i].known + s[i].pending; }
+  int uncomputed(int i) const { return total(i) - s[i].computed; }
+  bool needs_compute(int i) const {
+    const int u = uncomputed(i);
+    if (u > 1) return true;
+    if (u == 0) return false;
+    if (total(i) - s[i].prompt_len >= s[i].max_new) return false;
+    return total(i) < cfg.max_seq_len;
+  }
+  bool ensure(int i, int positions) {
+    if (s[i].rid < 0) {
+      const int rid = rl_hc_open(c);
+      if (rid < 0) return false;
+      s[i].rid = rid;
+      s[i].cache_changed = 1;
+    }
+    return rl_hc_reserve(c, s[i].rid, positions) == 1;
+  }
+  void drop_cache(int i) {
+    if (s[i].rid >= 0) {
+      int bad = 0;
+      rl_hc_close(c, s[i].rid, &bad);
+      s[i].rid = -1;
+      s[i].cache_changed = 1;
+    }
+  }
+  void preempt(int i) {
+    drop_cache(i);
+    s[i].computed = 0;
+    ++s[i].preempted;
+    running.erase(std::remove(running.begin(), running.end(), i), running.end());
+    if (s[i].pending > 0) {
+      s[i].where = 2;
+      parked.push_back(i);
+    } else {
+      s[i].where = 1;
+      waiting.insert(waiting.begin(), i);
+    }
+  }
+  bool add_entry(int i, int n) {
+    RlSchedEntry e;
+    e.seq = i;
+    e.start_pos = s[i].computed;
+    e.num_tokens = n;
+    e.sample = (s[i].computed + n == total(i)) ? 1 : 0;
+    e.from_device = 0;
+    e.src_row = -1;
+    if (e.start_pos >= s[i].known) {
+      if (!(n == 1 && s[i].pending > 0 && s[i].pending_ok)) {
+        error_seq = i;
+        return false;
+      }
+      e.from_device = 1;
+      e.src_row = s[i].pending_row;
+    }
+    s[i].computed += n;
+    budget -= n;
+    plan.push_back(e);
+    return true;
+  }
+  bool schedule_prefill() {
+    const std::vector<int> snapshot = running;
+    for (int i : snapshot) {
+      if (budget <= 0) return true;
+      if (uncomputed(i) <= 1) continue;
+      // a pending token cannot be part of a multi-token portion
+      const int chunk = std::min(s[i].pending > 0 ? s[i].known - s[i].computed : uncomputed(i), budget);
+      if (chunk <= 0) continue;
+      if (!ensure(i, s[i].computed + chunk)) return true;
+      if (!add_entry(i, chunk)) return false;
+    }
+    while (!waiting.empty() && budget > 0 && static_cast<int>(running.size()) < cfg.max_num_seqs) {
+      const int i = waiting.front();
+      const int chunk = std::min(uncomputed(i), budget);
+      if (!running.empty()) {
+        const int need = c->blocks_for(s[i].computed + chunk);
+        for (size_t g = 0; g < c->pools.size(); ++g) {
+          const int mark = static_cast<int>(cfg.watermark * c->pools[g].usable());
+          if (static_cast<int>(c->pools[g].free_list.size()) - need < mark) return true;
+        }
+      }
+      if (c->num_open >= c->num_state_slots && s[i].rid < 0) return true;
+      if (!ensure(i, s[i].computed + chunk)) {
+        drop_cache(i);
+        return true;
+      }
+      waiting.erase(waiting.begin());
+      s[i].where = 0;
+      running.push_back(i);
+      if (!add_entry(i, chunk)) return false;
+    }
+    return true;
+  }
+  bool schedule_decode() {
+    size_t k = 0;
+    while (k < running.size()) {
+      const int i = running[k];
+      if (budget <= 0) break;
+      if (uncomputed(i) != 1 || !needs_compute(i)) {
+        ++k;
+        continue;
+      }
+      bool self_preempted = false;
+      while (!ensure(i, s[i].computed + 1)) {
+        const int victim = running.back();
+        bool in_plan = false;
+        for (const RlSchedEntry& e : plan) in_plan = in_plan || e.seq == victim;
+        if (victim == i || in_plan) {
+          preempt(i);
+          self_preempted = true;
+          break;
+        }
+        preempt(victim);
+        ++num_preempted;
+      }
+      if (self_preempted) {
+        ++num_preempted;
+        continue;                        // running shrank at position k
+      }
+      if (!add_entry(i, 1)) return false;
+      ++k;
+    }
+    return true;
+  }
+  bool run() {
+    budget = cfg.budget;
+    if (cfg.mix) {
+      if (!schedule_decode() || !schedule_prefill()) return false;
+    } else {
+      if (!schedule_prefill()) return false;
+      if (plan.empty() && !schedule_decode()) return false;
+    }
+    // sequences stuck mid-prompt can hold every page with none able to go on
+    while (plan.empty() && running.size() > 1) {
+      bool any = false;
+      for (int i : running) any = any || needs_compute(i);
+      if (!any) break;
+      preempt(running.back());
+      ++num_preempted;
+      if (!schedule_prefill()) return false;
+      if (plan.empty() && !schedule_decode()) return false;
+    }
+    return true;
+  }
+};
+
+}  // namespace
+
+extern "C" {
+
+// seqs: num_running running sequences (oldest first), then num_waiting from the front of the waiting
+// queue.  Out: entries (capacity: one per sequence), the new running order, the new order of the passed
+// part of the waiting queue (preempted sequences in front), the parked ones; counts in n_out[0..3] =
+// entries, running, waiting, parked, n_out[4] = preemptions.  Returns 0, or -10 when a sequence would
+// need a device token that is not available (n_out[5] = its index), -5 for bad arguments.
+int rl_sched_plan(void* h, const RlSchedCfg* cfg, RlSchedSeq* seqs, int num_running, int num_waiting,
+                  RlSchedEntry* entries, int32_t* running_out, int32_t* waiting_out, int32_t* parked_out,
+                  int32_t* n_out) {
+  if (!h || !cfg || num_running < 0 || num_waiting < 0) return -5;
+  Planner p;
+  p.c = static_cast<Core*>(h);
+  p.cfg = *cfg;
+  p.s = seqs;
+  const int n = num_running + num_waiting;
+  for (int i = 0; i < n; ++i) {
+    seqs[i].preempted = 0;
+    seqs[i].cache_changed = 0;
+    seqs[i].where = i < num_running ? 0 : 1;
+    (i < num_running ? p.running : p.waiting).push_back(i);
+  }
+  const bool ok = p.run();
+  // a sequence is planned at most once in a step (one token, or one portion)
+  n_out[0] = static_cast<int32_t>(p.plan.size());
+  n_out[1] = static_cast<int32_t>(p.running.size());
+  n_out[2] = static_cast<int32_t>(p.waiting.size());
+  n_out[3] = static_cast<int32_t>(p.parked.size());
+  n_out[4] = p.num_preempted;
+  n_out[5] = p.error_seq;
+  std::copy(p.plan.begin(), p.plan.end(), entries);
+  std::copy(p.running.begin(), p.running.end(), running_out);
+  std::copy(p.waiting.begin(), p.waiting.end(), waiting_out);
+  std::copy(p.parked.begin(), p.parked.end(), parked_out);
+  return ok ? 0 : -10;
 }
 
 }  // extern "C"

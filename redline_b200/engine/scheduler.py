@@ -13,16 +13,19 @@ is none, the sequence itself is.  A sequence whose newest token is still on the 
 Policy of the reference's scheduler (src/core/scheduler.cpp:24-218).
 
 This module is host code only; it talks to the ``CacheManager`` and to nothing on
-the GPU.
+the GPU.  The plan loop is native code (``rl_sched_plan`` in csrc/host_core.cpp, beside the
+cache manager's state it works on); the request objects, the queues and the life cycle
+(add, finish, preempt on request, tokens received) are kept here.
 """
 
 from __future__ import annotations
 
-import time
+import ctypes
 from collections import deque
 from dataclasses import dataclass, field
 from typing import Deque, List, Optional
 
+from ..cache import native
 from ..cache.manager import CacheManager, RequestCache
 from ..sampling.params import SamplingParams
 
@@ -148,14 +151,6 @@ class Scheduler:
         return bool(self.running or self.waiting or self.parked)
 
     # ---------------------------------------------------------------- pages
-    def _watermark(self, group: int) -> int:
-        return int(self.cfg.admission_watermark * self.cache.num_total_pages(group))
-
-    def _ensure(self, seq: Sequence, num_positions: int) -> bool:
-        if seq.cache is None:
-            seq.cache = self.cache.open(seq.id)
-        return self.cache.reserve(seq.cache, num_positions)
-
     def _drop_cache(self, seq: Sequence) -> None:
         if seq.cache is not None:
             self.cache.close(seq.id)
@@ -204,100 +199,62 @@ class Scheduler:
 
     # ------------------------------------------------------------- planning
     def schedule(self, step_id: int, prev_step_id: int = -1) -> StepPlan:
-        plan = StepPlan(step_id=step_id)
-        budget = self.cfg.max_num_batched_tokens
-
-        def add_entry(seq: Sequence, n: int) -> None:
-            nonlocal budget
-            e = ScheduledSeq(seq, seq.num_computed, n, seq.num_computed + n == seq.total_len)
-            if e.start_pos >= len(seq.tokens):
-                if not (n == 1 and seq.num_pending > 0 and seq.pending_step == prev_step_id):
-                    raise SchedulerError(f"sequence {seq.id} needs a device token that is not available")
-                e.input_from_device = True
-                e.src_row = seq.pending_row
-            seq.num_computed += n
-            budget -= n
-            plan.num_tokens += n
-            if n == 1 and e.sample:
+        """Plans one step.  The plan loop itself is native (``rl_sched_plan`` in csrc/host_core.cpp): it
+        works on the cache manager's state directly; here the sequences' numbers are handed to it and
+        what it decided is written back to the sequences and the queues."""
+        import numpy as np
+        cfg = self.cfg
+        # every running sequence, and as much of the waiting queue's front as could be admitted
+        nw = min(len(self.waiting), cfg.max_num_seqs)
+        seqs: List[Sequence] = list(self.running) + [self.waiting[i] for i in range(nw)]
+        nr = len(self.running)
+        n = len(seqs)
+        rec = np.empty((max(n, 1), len(native.SCHED_SEQ_FIELDS)), dtype=np.int32)
+        for i, q in enumerate(seqs):
+            rec[i] = (q.cache.rid if q.cache is not None else -1, len(q.tokens), q.num_pending, q.num_computed,
+                      q.prompt_len, q.params.max_new_tokens,
+                      1 if (q.num_pending > 0 and q.pending_step == prev_step_id) else 0, q.pending_row, 0, 0, 0)
+        entries = np.empty((max(n, 1), len(native.SCHED_ENTRY_FIELDS)), dtype=np.int32)
+        order = np.empty((3, max(n, 1)), dtype=np.int32)
+        counts = np.zeros(6, dtype=np.int32)
+        ncfg = native.RlSchedCfg(cfg.max_num_seqs, cfg.max_num_batched_tokens, cfg.max_seq_len,
+                                 1 if cfg.mix_prefill_decode else 0, cfg.admission_watermark)
+        code = self.cache._lib.rl_sched_plan(self.cache._h, ctypes.byref(ncfg), rec.ctypes.data, nr, nw,
+                                             entries.ctypes.data, order[0].ctypes.data, order[1].ctypes.data,
+                                             order[2].ctypes.data, counts.ctypes.data)
+        ne, n_run, n_wait, n_park, n_pre, bad = (int(x) for x in counts)
+        # ---- what the planner did to the sequences
+        for i, q in enumerate(seqs):
+            rid, computed, where, preempted, changed = (int(rec[i, 0]), int(rec[i, 3]), int(rec[i, 8]),
+                                                         int(rec[i, 9]), int(rec[i, 10]))
+            q.num_computed = computed
+            q.num_preemptions += preempted
+            if changed:
+                if q.cache is not None:
+                    self.cache.forget(q.id)
+                q.cache = self.cache.adopt(q.id, rid) if rid >= 0 else None
+            if where == 0:
+                q.status = RUNNING
+            else:
+                q.status = WAITING
+                if where == 2:
+                    q.requeue_when_received = True
+        self.running = [seqs[int(i)] for i in order[0, :n_run]]
+        for _ in range(nw):
+            self.waiting.popleft()
+        self.waiting.extendleft(seqs[int(i)] for i in reversed(order[1, :n_wait]))
+        self.parked.extend(seqs[int(i)] for i in order[2, :n_park])
+        if code == -10:
+            raise SchedulerError(f"sequence {seqs[bad].id} needs a device token that is not available")
+        if code != 0:
+            raise SchedulerError(f"the planner refused its arguments (code {code})")
+        plan = StepPlan(step_id=step_id, num_preempted=n_pre)
+        for k in range(ne):
+            i, start, num, sample, from_device, src_row = (int(x) for x in entries[k])
+            plan.seqs.append(ScheduledSeq(seqs[i], start, num, bool(sample), bool(from_device), src_row))
+            plan.num_tokens += num
+            if num == 1 and sample:
                 plan.num_decode_tokens += 1
             else:
-                plan.num_prefill_tokens += n
-            plan.seqs.append(e)
-
-        def schedule_prefill() -> None:
-            for seq in list(self.running):
-                if budget <= 0:
-                    return
-                if seq.num_uncomputed <= 1:
-                    continue
-                # a pending token cannot be part of a multi-token portion
-                known = len(seq.tokens) - seq.num_computed
-                chunk = min(known if seq.num_pending else seq.num_uncomputed, budget)
-                if chunk <= 0:
-                    continue
-                if not self._ensure(seq, seq.num_computed + chunk):
-                    return
-                add_entry(seq, chunk)
-            while self.waiting and budget > 0 and len(self.running) < self.cfg.max_num_seqs:
-                seq = self.waiting[0]
-                chunk = min(seq.num_uncomputed, budget)
-                if self.running:
-                    need = self.cache.blocks_for(seq.num_computed + chunk)
-                    short = any(self.cache.num_free_pages(g) - need < self._watermark(g)
-                                for g in range(len(self.cache.groups)))
-                    if short:
-                        return
-                if self.cache.num_open() >= self.cache.num_state_slots and seq.cache is None:
-                    return
-                if not self._ensure(seq, seq.num_computed + chunk):
-                    self._drop_cache(seq)
-                    return
-                self.waiting.popleft()
-                seq.status = RUNNING
-                self.running.append(seq)
-                add_entry(seq, chunk)
-
-        def schedule_decode() -> None:
-            i = 0
-            while i < len(self.running):
-                seq = self.running[i]
-                if budget <= 0:
-                    break
-                if seq.num_uncomputed != 1 or not self.needs_compute(seq):
-                    i += 1
-                    continue
-                self_preempted = False
-                while not self._ensure(seq, seq.num_computed + 1):
-                    victim = self.running[-1]
-                    in_plan = any(e.seq is victim for e in plan.seqs)
-                    if victim is seq or in_plan:
-                        self.preempt(seq)
-                        self_preempted = True
-                        break
-                    self.preempt(victim)
-                    plan.num_preempted += 1
-                if self_preempted:
-                    plan.num_preempted += 1
-                    continue            # running shrank at position i
-                add_entry(seq, 1)
-                i += 1
-
-        if self.cfg.mix_prefill_decode:
-            schedule_decode()
-            schedule_prefill()
-        else:
-            schedule_prefill()
-            if plan.empty:
-                schedule_decode()
-
-        # Sequences stuck mid-prompt can hold every page with none able to go on:
-        # free the newest until the oldest can continue.
-        while plan.empty and len(self.running) > 1:
-            if not any(self.needs_compute(s) for s in self.running):
-                break
-            self.preempt(self.running[-1])
-            plan.num_preempted += 1
-            schedule_prefill()
-            if plan.empty:
-                schedule_decode()
+                plan.num_prefill_tokens += num
         return plan

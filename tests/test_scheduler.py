@@ -171,3 +171,61 @@ def test_starved_prompts_free_the_newest_until_the_oldest_goes_on():
         deliver(sched, p, step)
         cache.check_invariants()
     assert done and a.status == FINISHED and b.status == FINISHED
+
+
+@pytest.mark.parametrize("asynchronous", [False, True])
+def test_random_workloads_keep_the_invariants_and_everything_finishes(asynchronous):
+    """Random arrivals, lengths, pools and limits: every plan stays within the budget and the sequence
+    limit, a sequence's portions follow one another without gaps, no page is lost or held twice, and every
+    request that was accepted finishes (with its tokens received one step late if asynchronous)."""
+    import random
+    for seed in range(60):
+        rng = random.Random(seed)
+        pages, max_seqs = rng.choice([6, 10, 20, 40, 200]), rng.choice([1, 2, 3, 4, 8])
+        budget = max(rng.choice([4, 16, 32, 100]), max_seqs)
+        max_len, mix = rng.choice([64, 128, 400]), rng.random() < 0.7
+        sched, cache = make(pages, max_seqs, budget, max_len, mix, rng.choice([0.0, 0.01, 0.1, 0.3]))
+        accepted, inflight, nid, step = [], [], 0, 0
+        computed = {}
+        while step < 60 or sched.has_unfinished() or inflight:
+            assert step < 5000, f"seed {seed}: the workload does not come to an end"
+            if step < 60:
+                for _ in range(rng.choice([0, 0, 1, 1, 2])):
+                    s = seq(nid, rng.randint(1, max_len - 2), rng.randint(1, 40))
+                    nid += 1
+                    try:
+                        sched.add(s)
+                        accepted.append(s)
+                    except SchedulerError:
+                        pass
+            plan = sched.schedule(step, step - 1)
+            assert plan.num_tokens <= budget and len(sched.running) <= max_seqs
+            assert plan.num_tokens == sum(e.num_tokens for e in plan.seqs) == plan.num_prefill_tokens + plan.num_decode_tokens
+            assert len({e.seq.id for e in plan.seqs}) == len(plan.seqs)
+            for e in plan.seqs:
+                assert e.seq.status == RUNNING and e.seq in sched.running and e.seq.cache is not None
+                # a portion begins where the last one ended, or at 0 after a preemption
+                assert e.start_pos == computed.get(e.seq.id, 0) or e.start_pos == 0
+                computed[e.seq.id] = e.start_pos + e.num_tokens
+                assert e.seq.num_computed == computed[e.seq.id] <= len(e.seq.tokens) + e.seq.num_pending
+                assert e.seq.cache.num_tokens >= computed[e.seq.id]
+                assert e.sample == (computed[e.seq.id] == len(e.seq.tokens) + e.seq.num_pending)
+                assert e.input_from_device == (e.start_pos >= len(e.seq.tokens))
+            for s in list(sched.waiting) + sched.parked:
+                assert s.cache is None and s.num_computed == 0
+            got = deliver(sched, plan, step, sync=False)
+            sched.after_step(plan)
+            todo, inflight = (inflight, got) if asynchronous else (got, [])
+            for s in todo:                                  # as the engine does: length limits end a request
+                s.num_pending -= 1
+                if s.status == FINISHED:
+                    continue
+                s.tokens.append(5)
+                if len(s.tokens) - s.prompt_len >= s.params.max_new_tokens or len(s.tokens) >= max_len:
+                    sched.finish(s, "length")
+                else:
+                    sched.on_tokens_received(s)
+            cache.check_invariants()
+            step += 1
+        assert all(s.status == FINISHED for s in accepted), f"seed {seed}"
+        assert cache.num_open() == 0 and cache.num_free_pages(0) == cache.num_total_pages(0)
