@@ -212,7 +212,7 @@ class Scheduler:
         rec = np.empty((max(n, 1), len(native.SCHED_SEQ_FIELDS)), dtype=np.int32)
         for i, q in enumerate(seqs):
             rec[i] = (q.cache.rid if q.cache is not None else -1, len(q.tokens), q.num_pending, q.num_computed,
-                      q.prompt_len, q.params.max_new_tokens,
+                      q.prompt_len, min(q.params.max_new_tokens, 2**31 - 1),
                       1 if (q.num_pending > 0 and q.pending_step == prev_step_id) else 0, q.pending_row, 0, 0, 0)
         entries = np.empty((max(n, 1), len(native.SCHED_ENTRY_FIELDS)), dtype=np.int32)
         order = np.empty((3, max(n, 1)), dtype=np.int32)
