@@ -209,11 +209,13 @@ class Scheduler:
         seqs: List[Sequence] = list(self.running) + [self.waiting[i] for i in range(nw)]
         nr = len(self.running)
         n = len(seqs)
-        rec = np.empty((max(n, 1), len(native.SCHED_SEQ_FIELDS)), dtype=np.int32)
-        for i, q in enumerate(seqs):
-            rec[i] = (q.cache.rid if q.cache is not None else -1, len(q.tokens), q.num_pending, q.num_computed,
-                      q.prompt_len, min(q.params.max_new_tokens, 2**31 - 1),
-                      1 if (q.num_pending > 0 and q.pending_step == prev_step_id) else 0, q.pending_row, 0, 0, 0)
+        flat: List[int] = []
+        for q in seqs:
+            flat += (q.cache.rid if q.cache is not None else -1, len(q.tokens), q.num_pending, q.num_computed,
+                     q.prompt_len, min(q.params.max_new_tokens, 2**31 - 1),
+                     1 if (q.num_pending > 0 and q.pending_step == prev_step_id) else 0, q.pending_row, 0, 0, 0)
+        nf = len(native.SCHED_SEQ_FIELDS)
+        rec = np.array(flat, dtype=np.int32).reshape(n, nf) if n else np.zeros((1, nf), dtype=np.int32)
         entries = np.empty((max(n, 1), len(native.SCHED_ENTRY_FIELDS)), dtype=np.int32)
         order = np.empty((3, max(n, 1)), dtype=np.int32)
         counts = np.zeros(6, dtype=np.int32)
@@ -222,13 +224,13 @@ class Scheduler:
         code = self.cache._lib.rl_sched_plan(self.cache._h, ctypes.byref(ncfg), rec.ctypes.data, nr, nw,
                                              entries.ctypes.data, order[0].ctypes.data, order[1].ctypes.data,
                                              order[2].ctypes.data, counts.ctypes.data)
-        ne, n_run, n_wait, n_park, n_pre, bad = (int(x) for x in counts)
+        ne, n_run, n_wait, n_park, n_pre, bad = counts.tolist()
         # ---- what the planner did to the sequences
-        for i, q in enumerate(seqs):
-            rid, computed, where, preempted, changed = (int(rec[i, 0]), int(rec[i, 3]), int(rec[i, 8]),
-                                                         int(rec[i, 9]), int(rec[i, 10]))
+        for q, r in zip(seqs, rec.tolist()):
+            rid, computed, where, preempted, changed = r[0], r[3], r[8], r[9], r[10]
             q.num_computed = computed
-            q.num_preemptions += preempted
+            if preempted:
+                q.num_preemptions += preempted
             if changed:
                 if q.cache is not None:
                     self.cache.forget(q.id)
@@ -239,18 +241,18 @@ class Scheduler:
                 q.status = WAITING
                 if where == 2:
                     q.requeue_when_received = True
-        self.running = [seqs[int(i)] for i in order[0, :n_run]]
+        order_l = order.tolist()
+        self.running = [seqs[i] for i in order_l[0][:n_run]]
         for _ in range(nw):
             self.waiting.popleft()
-        self.waiting.extendleft(seqs[int(i)] for i in reversed(order[1, :n_wait]))
-        self.parked.extend(seqs[int(i)] for i in order[2, :n_park])
+        self.waiting.extendleft(seqs[i] for i in reversed(order_l[1][:n_wait]))
+        self.parked.extend(seqs[i] for i in order_l[2][:n_park])
         if code == -10:
             raise SchedulerError(f"sequence {seqs[bad].id} needs a device token that is not available")
         if code != 0:
             raise SchedulerError(f"the planner refused its arguments (code {code})")
         plan = StepPlan(step_id=step_id, num_preempted=n_pre)
-        for k in range(ne):
-            i, start, num, sample, from_device, src_row = (int(x) for x in entries[k])
+        for i, start, num, sample, from_device, src_row in entries[:ne].tolist():
             plan.seqs.append(ScheduledSeq(seqs[i], start, num, bool(sample), bool(from_device), src_row))
             plan.num_tokens += num
             if num == 1 and sample:
