@@ -4,7 +4,11 @@
 # resolved), its engine and command-line programs by its own CMake build for sm_100.
 # Usage: baseline/build_reference.sh /path/to/reference
 set -e
-REF=${1:-/root/reference}
+if [ -z "$1" ] || [ ! -d "$1" ]; then
+    echo "usage: $0 /path/to/reference (a checkout of Neil456/Redline)" >&2
+    exit 2
+fi
+REF=$1
 HERE=$(cd "$(dirname "$0")" && pwd)
 SRC=$(mktemp -d)/reference
 cp -r "$REF" "$SRC"      # the build writes into the source tree; the original may be read-only

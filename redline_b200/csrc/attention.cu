@@ -1019,6 +1019,8 @@ using namespace rl;
 
 namespace {
 
+constexpr int kMaxDevices = 64;   // per-device launch set-up is remembered for this many devices
+
 // The rotary tables and columns for a launch that also rotates q and k and writes the token's k and v
 // into the cache (streaming kernel only).
 struct DecodeRopeHost {
@@ -1039,11 +1041,7 @@ inline bool decode_streams(const void* q, int q_stride, const void* kc, const vo
                          reinterpret_cast<uintptr_t>(kc) | reinterpret_cast<uintptr_t>(vc) |
                          reinterpret_cast<uintptr_t>(part_o)) & 15) == 0;
   // (with few units the one-partition kernel, four warps to a partition, has the shorter critical path)
-  static const long long min_units = [] {
-    const char* e = std::getenv("REDLINE_STREAM_MIN_UNITS");     // a tuning knob
-    return e ? std::atoll(e) : static_cast<long long>(kStreamMinUnits);
-  }();
-  const bool many = static_cast<long long>(nitems) * hkv * max_parts >= min_units;
+  const bool many = static_cast<long long>(nitems) * hkv * max_parts >= static_cast<long long>(kStreamMinUnits);
   return (impl == 3 || (impl == 0 && (many || max_parts > kMaxMergeParts))) && hq / hkv <= 16 && page_size >= 16 &&
          kPart % page_size == 0 && counters != nullptr && nitems <= kStreamMaxItems && aligned;   // (any number of partitions)
 #else
@@ -1054,7 +1052,9 @@ inline bool decode_streams(const void* q, int q_stride, const void* kc, const vo
 // Whether a bfloat16 launch that does not stream goes to the one-partition tensor-core kernel.
 inline bool decode_one_partition(const void* counters, int max_parts, int hq, int hkv, int page_size, int impl) {
 #ifdef RL_HAVE_MMA_DECODE
-  return impl != 1 && impl != 3 && hq / hkv <= 16 && page_size % 16 == 0 && counters != nullptr && max_parts <= kMaxMergeParts;
+  // (the kernel finds a key's page with a shift and a mask: pages of a power of two keys)
+  return impl != 1 && impl != 3 && hq / hkv <= 16 && page_size >= 16 && (page_size & (page_size - 1)) == 0 &&
+         counters != nullptr && max_parts <= kMaxMergeParts;
 #else
   return false;
 #endif
@@ -1089,12 +1089,15 @@ int launch_decode(const void* q, int q_stride, const void* kc, const void* vc, c
   if constexpr (sizeof(T) == 2) {
     if (decode_streams(q, q_stride, kc, vc, part_o, counters, out, out_stride, max_parts, nitems, hq, hkv, page_size,
                        impl)) {
-      static int sms = 0;
-      static bool sattr = false;
-      if (!sattr) {
-        int dev = 0;
-        cudaError_t e = cudaGetDevice(&dev);
-        if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+      // (a kernel's shared-memory limit and the SM count belong to a device: looked up once on each)
+      static int sms_of[kMaxDevices];
+      int dev = 0;
+      cudaError_t e = cudaGetDevice(&dev);
+      if (e != cudaSuccess) return static_cast<int>(e);
+      if (dev < 0 || dev >= kMaxDevices) return static_cast<int>(cudaErrorInvalidDevice);
+      if (sms_of[dev] == 0) {
+        int n = 0;
+        e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
         if (e == cudaSuccess)
           e = cudaFuncSetAttribute(decode_attn_stream_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    static_cast<int>(kStreamSmem));
@@ -1102,8 +1105,9 @@ int launch_decode(const void* q, int q_stride, const void* kc, const void* vc, c
           e = cudaFuncSetAttribute(decode_attn_stream_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    static_cast<int>(kStreamSmem));
         if (e != cudaSuccess) return static_cast<int>(e);
-        sattr = true;
+        sms_of[dev] = n > 0 ? n : 1;
       }
+      const int sms = sms_of[dev];
       // no more CTAs than the launch can have units
       const long long most = static_cast<long long>(nitems) * hkv * max_parts;
       const int ctas = static_cast<int>(most < sms ? most : sms);
@@ -1188,20 +1192,21 @@ int launch_prefill(const void* q, int q_stride, const void* kc, const void* vc, 
                            reinterpret_cast<uintptr_t>(kc) | reinterpret_cast<uintptr_t>(vc)) & 15) == 0;
     // the tcgen05 kernel: power-of-two pages, 16-byte aligned rows, a status word for its bounded waits
     if ((impl == 0 || impl == 3) && status != nullptr && aligned && (page_size & (page_size - 1)) == 0) {
-      static bool tattr = false;
-      if (!tattr) {
-        cudaError_t e = cudaFuncSetAttribute(prefill_attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             static_cast<int>(kPrefillTcSmem));
+      static int tsms_of[kMaxDevices];
+      int dev = 0;
+      cudaError_t e = cudaGetDevice(&dev);
+      if (e != cudaSuccess) return static_cast<int>(e);
+      if (dev < 0 || dev >= kMaxDevices) return static_cast<int>(cudaErrorInvalidDevice);
+      if (tsms_of[dev] == 0) {
+        int n = 0;
+        e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        if (e == cudaSuccess)
+          e = cudaFuncSetAttribute(prefill_attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   static_cast<int>(kPrefillTcSmem));
         if (e != cudaSuccess) return static_cast<int>(e);
-        tattr = true;
+        tsms_of[dev] = n > 0 ? n : 1;
       }
-      static int tsms = 0;
-      if (tsms == 0) {
-        int dev = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess ||
-            cudaDeviceGetAttribute(&tsms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || tsms <= 0)
-          tsms = 1;
-      }
+      const int tsms = tsms_of[dev];
       const long long items = static_cast<long long>(tiles) * hq;
       const int ctas = static_cast<int>(items < tsms ? items : tsms);      // persistent: one CTA per SM
       launch_kernel(prefill_attn_tc_kernel, dim3(ctas), dim3(kTcThreads), kPrefillTcSmem, stream, a, tiles, status);
@@ -1212,14 +1217,18 @@ int launch_prefill(const void* q, int q_stride, const void* kc, const void* vc, 
   if (impl == 3) return static_cast<int>(cudaErrorInvalidValue);
 #ifdef RL_HAVE_MMA_DECODE
   if constexpr (sizeof(T) == 2) {
-    if (impl != 1 && page_size % 16 == 0 && out_stride % 8 == 0 && q_stride % 8 == 0) {
+    if (impl != 1 && page_size >= 16 && (page_size & (page_size - 1)) == 0 && out_stride % 8 == 0 && q_stride % 8 == 0) {
       const size_t msmem = static_cast<size_t>(4) * kMK * kD * sizeof(bf16);
-      static bool mattr = false;
-      if (!mattr) {
-        cudaError_t e = cudaFuncSetAttribute(prefill_attn_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             static_cast<int>(msmem));
+      static bool mattr[kMaxDevices];
+      int dev = 0;
+      cudaError_t e = cudaGetDevice(&dev);
+      if (e != cudaSuccess) return static_cast<int>(e);
+      if (dev < 0 || dev >= kMaxDevices) return static_cast<int>(cudaErrorInvalidDevice);
+      if (!mattr[dev]) {
+        e = cudaFuncSetAttribute(prefill_attn_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(msmem));
         if (e != cudaSuccess) return static_cast<int>(e);
-        mattr = true;
+        mattr[dev] = true;
       }
       launch_kernel(prefill_attn_mma_kernel, dim3(dim3(tiles * (kPreTile / kPreRows), hq)), dim3(128), msmem, stream, a);
       return static_cast<int>(cudaGetLastError());
@@ -1228,13 +1237,18 @@ int launch_prefill(const void* q, int q_stride, const void* kc, const void* vc, 
 #endif
   if (impl == 2) return static_cast<int>(cudaErrorInvalidValue);
   const size_t smem = sizeof(float) * (kBQ * (kD + 1) + kBK * (kD + 1) + kBK * kD + kBQ * (kBK + 1));
-  static bool attr_set = false;  // per instantiation; the attribute belongs to the device function
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(prefill_attn_kernel<T>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         static_cast<int>(smem));
+  static bool attr_set[kMaxDevices];  // per instantiation and device: the limit belongs to the function on a device
+  {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return static_cast<int>(e);
-    attr_set = true;
+    if (dev < 0 || dev >= kMaxDevices) return static_cast<int>(cudaErrorInvalidDevice);
+    if (!attr_set[dev]) {
+      e = cudaFuncSetAttribute(prefill_attn_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(smem));
+      if (e != cudaSuccess) return static_cast<int>(e);
+      attr_set[dev] = true;
+    }
   }
   launch_kernel(prefill_attn_kernel<T>, dim3(dim3(tiles * 4, hq)), dim3(kPreThreads), smem, stream, a);
   return static_cast<int>(cudaGetLastError());
@@ -1333,6 +1347,7 @@ int rl_attn_prefill(int dtype, const void* q, int q_stride, const void* kc, cons
 // The entry point that allocates nothing (declared and explained in attention_noalloc.h).
 // ------------------------------------------------------------------------------------
 #include <cstdio>
+#include <mutex>
 
 #include "attention_noalloc.h"
 
@@ -1342,8 +1357,8 @@ namespace {
 // cudaGetSymbolAddress, never a pointer to pass to a kernel.
 static __device__ __align__(256) unsigned char g_noalloc_scratch[RL_ATTN_NOALLOC_SCRATCH_BYTES];
 
-constexpr int kMaxDevices = 64;
 unsigned char* g_noalloc_ptr[kMaxDevices];   // device address of the array, per device; null until looked up
+std::mutex g_noalloc_lock;                   // first calls from several threads look the address up one at a time
 
 }  // namespace
 
@@ -1371,14 +1386,18 @@ extern "C" int rl_attn_decode_noalloc(int dtype, const void* q, int q_stride, co
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return static_cast<int>(e);
   if (dev < 0 || dev >= kMaxDevices) return static_cast<int>(cudaErrorInvalidDevice);
-  if (g_noalloc_ptr[dev] == nullptr) {
-    // set-up, once per device, with that device current: the array's address on this device
-    void* p = nullptr;
-    e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    g_noalloc_ptr[dev] = static_cast<unsigned char*>(p);
+  unsigned char* base = nullptr;
+  {
+    std::lock_guard<std::mutex> hold(g_noalloc_lock);
+    if (g_noalloc_ptr[dev] == nullptr) {
+      // set-up, once per device, with that device current: the array's address on this device
+      void* p = nullptr;
+      e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+      if (e != cudaSuccess) return static_cast<int>(e);
+      g_noalloc_ptr[dev] = static_cast<unsigned char*>(p);
+    }
+    base = g_noalloc_ptr[dev];
   }
-  unsigned char* base = g_noalloc_ptr[dev];
   int* counters = reinterpret_cast<int*>(base);
   float* part_ml = reinterpret_cast<float*>(base + counter_bytes);
   float* part_o = reinterpret_cast<float*>(base + counter_bytes + ml_bytes);

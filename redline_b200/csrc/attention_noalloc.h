@@ -16,13 +16,17 @@
 // What to know before calling:
 //   * The array is RL_ATTN_NOALLOC_SCRATCH_BYTES (8 MiB) per loaded copy of the library
 //     (one per head size) on every GPU that loads it, and stays until the process exits.
-//   * The scratch a call needs is
-//         nitems * hq * max_parts * (head_dim + 2) * 4  +  round_up(nitems * hkv * 4, 256)
-//     bytes.  A call that needs more than the array holds is refused: the function
+//   * The scratch a call needs, with rows = nitems * hq * max_parts, is
+//         round_up(nitems * hkv * 4, 256)  +  round_up(rows * 8, 256)  +  rows * head_dim * 4
+//     bytes (arrival counters, softmax statistics, partition outputs; the first two are each
+//     rounded up to 256 bytes).  A call that needs more than the array holds is refused: the function
 //     returns RL_ATTN_NOALLOC_TOO_LARGE, writes a message that names both numbers into
 //     errbuf (if given) and launches nothing.
 //   * The first call on each device looks up the array's device address (with that
-//     device current) and remembers it.  Make that first call outside any stream capture.
+//     device current), sets the kernels' shared-memory limits there, and remembers both.
+//     Make that first call outside any stream capture.  First calls from several threads
+//     at once are safe: the look-up is under a lock, and the limits are the same values
+//     whoever sets them first.
 //   * All calls share the one array, and it keeps what the last call left.  The part that
 //     must start at zero (the arrival counters) is cleared on the caller's stream at the
 //     start of every call; nothing else needs clearing.  Two calls whose work overlaps on

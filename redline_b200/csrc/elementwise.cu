@@ -232,12 +232,14 @@ __global__ void add_bias_kernel(TA* __restrict__ x, const TW* __restrict__ bias,
 // slot of the token: page = slot / page_size, offset = slot % page_size, cache
 // layout [pages, Hkv, page_size, D] (rope_kv.cu:60-70).  A negative slot skips
 // the write (a call that reads another call's cache).  cos == nullptr: no rotation.
+// A slot at or beyond num_slots (pages of the pool times page_size) is not written either and
+// sets bit 4 of the status word.
 template <typename TA>
 __global__ void rope_kv_write_kernel(TA* __restrict__ qkv, const int32_t* __restrict__ positions,
                                      const int32_t* __restrict__ slots,
                                      const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                                      TA* __restrict__ kcache, TA* __restrict__ vcache, int hq, int hkv,
-                                     int d, int page_size, int max_pos, int* status) {
+                                     int d, int page_size, int max_pos, long long num_slots, int* status) {
   pdl_launch();
   pdl_wait();
   constexpr int VEC = Vec16<TA>::N;    // head sizes are multiples of 16, so D / 2 is a multiple of VEC
@@ -245,9 +247,13 @@ __global__ void rope_kv_write_kernel(TA* __restrict__ qkv, const int32_t* __rest
   const int half = d >> 1;
   const int pos = positions[t];
   TA* row = qkv + static_cast<size_t>(t) * (hq + 2 * hkv) * d;
-  const int slot = slots ? slots[t] : -1;
+  int slot = slots ? slots[t] : -1;
   const bool bad_pos = (pos < 0 || pos >= max_pos);
   if (bad_pos && threadIdx.x == 0) atomicOr(status, 2);
+  if (slot >= num_slots) {
+    if (threadIdx.x == 0) atomicOr(status, 4);
+    slot = -1;
+  }
   const float* c = cos_t ? cos_t + static_cast<size_t>(bad_pos ? 0 : pos) * half : nullptr;
   const float* s = sin_t ? sin_t + static_cast<size_t>(bad_pos ? 0 : pos) * half : nullptr;
   const size_t page = slot >= 0 ? slot / page_size : 0;
@@ -397,18 +403,18 @@ int rl_add_bias(void* x, int act_dtype, const void* bias, int b_dtype, int rows,
 
 int rl_rope_kv_write(void* qkv, int act_dtype, const int32_t* positions, const int32_t* slots,
                      const float* cos_t, const float* sin_t, void* kcache, void* vcache, int tokens,
-                     int hq, int hkv, int d, int page_size, int max_pos, int* status,
+                     int hq, int hkv, int d, int page_size, int max_pos, long long num_slots, int* status,
                      cudaStream_t stream) {
   if (tokens <= 0) return 0;
   const int th = 256;
   if (act_dtype == RL_F32)
     launch_kernel(rope_kv_write_kernel<float>, dim3(tokens), dim3(th), 0, stream, 
         static_cast<float*>(qkv), positions, slots, cos_t, sin_t, static_cast<float*>(kcache),
-        static_cast<float*>(vcache), hq, hkv, d, page_size, max_pos, status);
+        static_cast<float*>(vcache), hq, hkv, d, page_size, max_pos, num_slots, status);
   else
     launch_kernel(rope_kv_write_kernel<bf16>, dim3(tokens), dim3(th), 0, stream, 
         static_cast<bf16*>(qkv), positions, slots, cos_t, sin_t, static_cast<bf16*>(kcache),
-        static_cast<bf16*>(vcache), hq, hkv, d, page_size, max_pos, status);
+        static_cast<bf16*>(vcache), hq, hkv, d, page_size, max_pos, num_slots, status);
   RL_LAUNCH_END();
 }
 

@@ -467,7 +467,6 @@ template <int MT, int EPI, bool NORM>
 int launch_kw(const SkinnyArgs& a, int sm_count, cudaStream_t stream) {
   constexpr int STREAMS = (EPI == kSwiglu) ? 2 : 1;
   int kw = choose_kw(a.N, a.K, STREAMS, sm_count);
-  if (const char* e = std::getenv("REDLINE_SKINNY_KW")) kw = std::atoi(e);   // for tuning runs
   if (STREAMS == 2 && kw > 4) kw = 4;      // 8 warps hold both streams of a tile
   switch (kw) {
     case 1: return launch_one<MT, 8, 1, EPI, NORM>(a, sm_count, stream);

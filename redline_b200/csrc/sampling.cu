@@ -12,8 +12,14 @@
 // passes over order-preserving integer keys of the logits, counting tokens (top-k)
 // or probability mass (top-p).  Mass is summed as 40-bit fixed point in integer
 // atomics, so the result does not depend on the order in which threads arrive.
-// Behaviour follows src/cuda/kernels/sampling.cu:53-203 and
-// src/cuda/kernels/common.cuh:105-140 of the reference.
+//
+// What is the reference's and what is this file's own: the threshold search follows the
+// reference's radix selection pass for pass (src/cuda/kernels/sampling.cu:53-127, including
+// its rule for a target that rounding left out of reach: keep all that remains), and the
+// Philox round, its counter layout and the constant 0x52444C4E in the counter are the
+// reference's (src/cuda/kernels/common.cuh:105-140), as they must be for a seed to draw the
+// same token in both engines.  The fixed-point mass in integer atomics, the two-stage arg max
+// over chunks of a row and the kernels' organisation are this file's.
 #include <cfloat>
 
 #include "common.cuh"

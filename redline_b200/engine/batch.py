@@ -30,7 +30,13 @@ import torch
 
 from ..cache import native
 from ..cache.manager import CacheManager, RequestCache
-from ..ops.kernels import DECODE_PARTITION, PREFILL_TILE_ROWS
+
+# The work lists of a step are cut for the mixers that read them: sequences that bring more than
+# one token into tiles of ``tile_rows`` query rows, the context of a single token into partitions
+# of ``partition`` keys.  The engine takes both numbers from its model's mixers (``Mixer.tiling``);
+# these defaults serve a builder made without a model.
+DEFAULT_TILE_ROWS = 128
+DEFAULT_PARTITION = 128
 
 
 @dataclass
@@ -157,15 +163,17 @@ class HostBatch:
 
 class BatchBuilder:
     def __init__(self, cache: CacheManager, max_tokens: int, max_seqs: int, max_rows: int,
-                 max_seq_len: int, device: torch.device):
+                 max_seq_len: int, device: torch.device, tile_rows: int = DEFAULT_TILE_ROWS,
+                 partition: int = DEFAULT_PARTITION):
         self.cache = cache
+        self.tile_rows, self.partition = tile_rows, partition
         self.G = len(cache.groups)
         self.page_size = cache.page_size
         self.max_tokens, self.max_seqs, self.max_rows = max_tokens, max_seqs, max_rows
         self.max_seq_len = max_seq_len
         self.B = cache.blocks_for(max_seq_len)
-        self.max_tiles = (max_tokens + PREFILL_TILE_ROWS - 1) // PREFILL_TILE_ROWS + max_seqs
-        self.parts_capacity = (max_seq_len + DECODE_PARTITION - 1) // DECODE_PARTITION
+        self.max_tiles = (max_tokens + tile_rows - 1) // tile_rows + max_seqs
+        self.parts_capacity = (max_seq_len + partition - 1) // partition
         cap = Layout(max_tokens, max_seqs, max_rows, self.max_tiles, self.G, self.B)
         self.device = device
         self.capacity_words = cap.words
@@ -215,7 +223,7 @@ class BatchBuilder:
             n = len(s.tokens)
             if n > 1:
                 tiles.append((si, n))
-        L_real = sum((n + PREFILL_TILE_ROWS - 1) // PREFILL_TILE_ROWS for _, n in tiles)
+        L_real = sum((n + self.tile_rows - 1) // self.tile_rows for _, n in tiles)
         if pad_to:
             T = S = R = pad_to
             L = 0
@@ -268,7 +276,7 @@ class BatchBuilder:
         res = (ctypes.c_int32 * 8)()
         code = self._lib.rl_hc_build(self.cache._h, h.ctypes.data, ctypes.byref(nl), lay.slots_c, lay.tables_c,
                                      self.G, self.B, S_real, segs.ctypes.data, tokens.ctypes.data, want.ctypes.data,
-                                     self.max_seq_len, PREFILL_TILE_ROWS, res)
+                                     self.max_seq_len, self.tile_rows, res)
         if code < 0:
             s = segments[res[5]]
             if code == -10:
@@ -292,7 +300,7 @@ class BatchBuilder:
             nd = pad_to
             decode_parts = self.parts_capacity
         else:
-            decode_parts = (max_ctx + DECODE_PARTITION - 1) // DECODE_PARTITION
+            decode_parts = (max_ctx + self.partition - 1) // self.partition
         dev = self.dev_buf
         if self.device.type == "cuda":
             dev[:lay.words].copy_(self.host_bufs[slot][:lay.words], non_blocking=True)

@@ -19,7 +19,7 @@ from __future__ import annotations
 import time
 from collections import deque
 from dataclasses import dataclass, field
-from typing import Any, Deque, Dict, List, Optional, Sequence as Seq, Tuple
+from typing import Any, Callable, Deque, Dict, List, Optional, Sequence as Seq, Tuple
 
 import torch
 
@@ -109,6 +109,10 @@ class Engine:
         self.records: List[StepRecord] = []
         self.num_preemptions = 0
         self._replay_pos: Dict[object, int] = {}
+        # Called after every launched step with ([(request id, position)] of the rows whose logits
+        # the step computed, in row order, and the float32 logits [rows, vocab] on the device, valid
+        # until the next launch).  For tests and tools that want the logits of scheduled generation.
+        self.on_logits: Optional[Callable[[List[Tuple[int, int]], torch.Tensor], None]] = None
 
     # ------------------------------------------------------------ properties
     @property
@@ -192,9 +196,11 @@ class Engine:
         graphs_before = self.runner.num_graph_steps
         if self.record_steps:
             self._ev_start[slot].record()
-        self.runner.run(segments, sample=True)
+        logits, _ = self.runner.run(segments, sample=True)
         if self.record_steps:
             self._ev_stop[slot].record()
+        if self.on_logits is not None and row > 0:
+            self.on_logits([(e.seq.id, e.start_pos + e.num_tokens - 1) for e in plan.seqs if e.sample], logits[:row])
         if row > 0:
             self._tok_host[slot][:row].copy_(self.runner.sampler.tokens[:row], non_blocking=True)
             self._lp_host[slot][:row].copy_(self.runner.sampler.logprobs[:row], non_blocking=True)
@@ -262,6 +268,9 @@ class Engine:
     # -------------------------------------------------------------- generate
     def generate_requests(self, requests: Seq[Tuple[Seq[int], SamplingParams]]) -> List[Dict[str, Any]]:
         """Runs (prompt, params) pairs to completion; outputs ordered by request."""
+        if self._replay_pos:
+            raise EngineError("requests opened with open_request / step_tokens are still open; close them first "
+                              "(they hold cache pages the scheduler does not count)")
         ids = [self.add_request(p, sp) for p, sp in requests]
         outs: Dict[int, Dict[str, Any]] = {}
         while self.has_unfinished():
@@ -313,6 +322,8 @@ class Engine:
 
     # ---------------------------------------------------------------- replay
     def open_request(self, key: object) -> None:
+        if self.has_unfinished():
+            raise EngineError("open_request needs an engine without unfinished scheduled requests")
         self.runner.open(key)
         self._replay_pos[key] = 0
 
@@ -320,12 +331,18 @@ class Engine:
         self.runner.close(key)
         self._replay_pos.pop(key, None)
 
-    def step_tokens(self, entries: Seq[Tuple[object, Seq[int], Seq[int]]]) -> torch.Tensor:
+    def step_tokens(self, entries: Seq[Tuple[object, Seq[int], Seq[int]]], graphs: bool = False) -> torch.Tensor:
         """One step of given tokens: entries are (request key, its next tokens, wanted
         indices among them).  Returns float32 logits [wanted, vocab] on the device, in the
         order of the entries and of their wanted indices.  Requests are opened on first
         use; a step larger than the engine's token or row limits is run as several
-        batches, which changes nothing about what a position attends to."""
+        batches, which changes nothing about what a position attends to.  With ``graphs`` a
+        batch of single tokens that all want their logits runs the way generation runs it:
+        padded to a fixed shape, sampler included, replayed as a CUDA graph (if the engine
+        has ``cuda_graphs`` on).  Requests given tokens here hold pages that the scheduler
+        does not know of, so this is refused while scheduled requests are unfinished."""
+        if self.has_unfinished():
+            raise EngineError("step_tokens needs an engine without unfinished scheduled requests")
         cache = self.runner.cache
         pieces: List[List[Segment]] = [[]]
         used_t = used_r = 0
@@ -374,9 +391,10 @@ class Engine:
         for segs in pieces:
             if not segs:
                 continue
-            logits, ctx = self.runner.run(segs, sample=False)
-            out[r:r + ctx.R].copy_(logits)
-            r += ctx.R
+            logits, _ = self.runner.run(segs, sample=graphs)
+            n = sum(len(sg.want) for sg in segs)       # (a graph step is padded: its context counts more rows)
+            out[r:r + n].copy_(logits[:n])
+            r += n
         for key, toks, _ in entries:
             if len(toks):
                 cache.release_passed(cache.get(key), self._replay_pos[key])
@@ -404,7 +422,7 @@ class Engine:
                 "max_num_seqs", "max_num_batched_tokens", "max_seq_len", "block_size", "kv_cache_tokens",
                 "gpu_memory_utilization", "cuda_graphs", "async_scheduling", "mix_prefill_decode")},
             "cache_groups": [{"kind": g.spec.kind, "window": g.spec.window, "layers": len(g.owners),
-                              "heads": g.spec.heads, "head_dim": g.spec.head_dim,
+                              "tensors": {t.name: list(t.shape) for t in g.spec.tensors},
                               "pages": c.num_total_pages(i)} for i, g in enumerate(c.groups)],
             "weight_bytes": self.runner.model.weight_bytes(),
         }

@@ -26,8 +26,11 @@ class DecoderModel:
         self.blocks: List[Block] = []
         for ls in spec.layers:
             block_cls = lookup("block", ls.arrangement)
+            if (ls.ffn is None) != (ls.ffn_norm is None):
+                raise ValueError("a layer has a feed-forward and its norm, or neither")
             self.blocks.append(block_cls(build_part("norm", ls.mixer_norm, rt), build_part("mixer", ls.mixer, rt),
-                                         build_part("norm", ls.ffn_norm, rt), build_part("ffn", ls.ffn, rt), rt))
+                                         build_part("norm", ls.ffn_norm, rt) if ls.ffn_norm is not None else None,
+                                         build_part("ffn", ls.ffn, rt) if ls.ffn is not None else None, rt))
         self.final_norm = build_part("norm", spec.final_norm, rt)
         self.head = build_part("head", spec.head, rt)
         self._check_order()
@@ -61,6 +64,13 @@ class DecoderModel:
                 continue
             groups.setdefault(cs.group_key(), GroupInfo(cs)).owners.append(i)
         return list(groups.values())
+
+    def tiling(self) -> Optional[Tuple[int, int]]:
+        """The one tiling of the step's work lists that this model's mixers ask for (None: no mixer reads them)."""
+        named = {b.mixer.tiling() for b in self.blocks} - {None}
+        if len(named) > 1:
+            raise ValueError(f"the model's mixers want the step's work lists cut in different ways: {sorted(named)}")
+        return next(iter(named)) if named else None
 
     def state_specs(self) -> Dict[int, StateSpec]:
         out = {}
@@ -100,7 +110,7 @@ class DecoderModel:
                 if name is not None and name in tensors:
                     mine[local] = tensors[name]
             part.load(mine)
-        if getattr(self.head, "weight", None) is None:
+        if self.head.wants_table():
             # no head tensor in use: the head shares the embedding table
             self.head.tie(self.embedding.table())
 

@@ -30,7 +30,8 @@ from .batch import BatchBuilder, Segment, StepContext
 from .model import DecoderModel
 
 GRAPH_BUCKETS = (1, 2, 4, 8, 12, 16, 24, 32, 48, 64, 96, 128, 160, 192, 256)
-STATUS_MESSAGES = {1: "a token id outside the vocabulary", 2: "a position beyond the rotary table"}
+STATUS_MESSAGES = {1: "a token id outside the vocabulary", 2: "a position beyond the rotary table",
+                   4: "a cache slot beyond the pool"}
 
 
 class EngineError(RuntimeError):
@@ -43,6 +44,16 @@ def require_cuda(device_index: int) -> torch.device:
     return torch.device("cuda", device_index)
 
 
+def pin_library_products() -> None:
+    """The library's matrix products (the bfloat16 products of more than 16 rows) must keep what the
+    package's own kernels promise: float32 accumulation all the way, also across the parts of a split
+    k dimension (torch's default lets cuBLAS reduce those parts in bfloat16), and no TF32 anywhere."""
+    torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
+    torch.backends.cuda.matmul.allow_fp16_reduced_precision_reduction = False
+    torch.backends.cuda.matmul.allow_tf32 = False
+    torch.backends.cudnn.allow_tf32 = False
+
+
 class ModelRunner:
     def __init__(self, cfg: EngineConfig, model_config: Optional[ModelConfig] = None,
                  spec: Optional[ModelSpec] = None):
@@ -50,6 +61,7 @@ class ModelRunner:
         self.cfg = cfg
         self.device = require_cuda(cfg.device)
         torch.cuda.set_device(self.device)
+        pin_library_products()
         self.model_config = model_config or load_config(cfg.model)
         self.spec = spec or model_spec(self.model_config)
         self.dtype = cfg.torch_dtype
@@ -71,8 +83,10 @@ class ModelRunner:
         self.states = StateStorage(self.model.state_specs(), cfg.max_num_seqs, self.device)
         if self.states.pools:   # a fresh request starts from zero state
             self.cache.on_open = lambda rc: self.states.reset_slot(rc.state_slot)
+        tiling = self.model.tiling()
         self.builder = BatchBuilder(self.cache, cfg.max_num_batched_tokens, cfg.max_num_seqs, self.max_rows,
-                                    cfg.max_seq_len, self.device)
+                                    cfg.max_seq_len, self.device, **({} if tiling is None else
+                                                                      {"tile_rows": tiling[0], "partition": tiling[1]}))
         order = self.spec.order
         self._caches = []
         for i, call in enumerate(order):
@@ -147,6 +161,12 @@ class ModelRunner:
             self.sampler.sample(self.logits, ctx)
 
     def _graph_bucket(self, segments: Sequence[Segment]) -> int:
+        """The padded size at which this step is replayed as a CUDA graph, or 0 for an eager step.
+        A model whose mixers keep per-request state always steps eagerly: a graph's padding rows would
+        need a state slot of their own, and capturing runs the step more than once, which a state that
+        is updated in place does not survive."""
+        if self.states.pools:
+            return 0
         n = len(segments)
         for s in segments:
             if len(s.tokens) != 1 or len(s.want) != 1:

@@ -135,14 +135,17 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, slots: Optional[to
                   vcache: Optional[torch.Tensor], num_heads: int, num_kv_heads: int, head_dim: int,
                   page_size: int, status: torch.Tensor, tokens: Optional[int] = None) -> None:
     """Rotates q and k heads of qkv [T, (Hq + 2 Hkv) D] in place and writes k, v to
-    the cache slot of each token (``slots`` None or negative: no write)."""
+    the cache slot of each token (``slots`` None or negative: no write; a slot beyond the pool is
+    not written and sets bit 4 of ``status``)."""
     _need_cuda(qkv, positions)
     f = _fn(_ew(), "rl_rope_kv_write", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                         c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+                                         c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_longlong, c_void_p,
+                                         c_void_p])
     max_pos = cos.shape[0] if cos is not None else 2 ** 31 - 1
+    num_slots = kcache.shape[0] * page_size if kcache is not None else 0
     _check(f(_ptr(qkv), _code(qkv.dtype), _ptr(positions), _ptr(slots), _ptr(cos), _ptr(sin), _ptr(kcache),
              _ptr(vcache), tokens if tokens is not None else qkv.shape[0], num_heads, num_kv_heads, head_dim,
-             page_size, max_pos, _ptr(status), _stream()), "rope_kv_write")
+             page_size, max_pos, num_slots, _ptr(status), _stream()), "rope_kv_write")
 
 
 # ------------------------------------------------------------------------ gemm

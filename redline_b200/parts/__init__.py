@@ -4,4 +4,4 @@ built-in parts."""
 from . import attention, block, embedding, mlp, rmsnorm, rope  # noqa: F401
 from .base import (Block, Embedding, FeedForward, Head, LayerCache, Mixer, Norm, Part, PositionEncoding,
                    Runtime, Workspace, build_part, lookup, register)
-from .spec import CacheSpec, LayerCall, LayerSpec, ModelSpec, PartSpec, StateSpec, TensorSpec
+from .spec import CacheSpec, CacheTensor, LayerCall, LayerSpec, ModelSpec, PartSpec, StateSpec, TensorSpec

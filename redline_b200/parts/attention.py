@@ -53,7 +53,10 @@ class GQAttention(Mixer):
 
     def cache_spec(self) -> CacheSpec:
         p = self.params
-        return CacheSpec("window" if p.window > 0 else "full", p.num_kv_heads, p.head_dim, p.window)
+        return CacheSpec.keys_values("window" if p.window > 0 else "full", p.num_kv_heads, p.head_dim, p.window)
+
+    def tiling(self):
+        return kernels.PREFILL_TILE_ROWS, kernels.DECODE_PARTITION
 
     def tensors(self) -> Dict[str, TensorSpec]:
         p = self.params

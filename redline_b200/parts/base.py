@@ -95,13 +95,21 @@ class Runtime:
 
 @dataclass
 class LayerCache:
-    """The cache one call of a layer works on: K and V [pages, heads, page_size, D]
-    of its cache group, and whether this call writes its tokens there."""
+    """The cache one call of a layer works on: the tensors its mixer's ``CacheSpec`` names, each
+    [pages, *leading axes, page_size, last axis] in the pages of its cache group (for attention
+    ``k`` and ``v`` [pages, heads, page_size, D]), and whether this call writes its tokens there."""
 
     group: int
-    k: torch.Tensor
-    v: torch.Tensor
+    tensors: Dict[str, torch.Tensor]
     write: bool = True
+
+    @property
+    def k(self) -> torch.Tensor:
+        return self.tensors["k"]
+
+    @property
+    def v(self) -> torch.Tensor:
+        return self.tensors["v"]
 
 
 class Part:
@@ -186,6 +194,13 @@ class Mixer(Part):
     def state_spec(self) -> Optional[StateSpec]:
         return None
 
+    def tiling(self) -> Optional[Tuple[int, int]]:
+        """(query rows of a tile, keys of a partition) in which this mixer's kernels want the step's
+        work lists cut (``ctx.tile_*`` for sequences that bring several tokens, ``ctx.decode_info`` /
+        ``ctx.decode_parts`` for single tokens), or None if it reads neither list.  All mixers of a
+        model that name a tiling must name the same one."""
+        return None
+
     def forward(self, x: torch.Tensor, ctx, cache: Optional[LayerCache],
                 state: Optional[torch.Tensor]) -> torch.Tensor:
         """x [T, H] -> [T, H] (what is added to the residual stream).  ``state`` is this
@@ -224,6 +239,14 @@ class Head(Part):
         """x [R, H] -> out [R, V] float32."""
         raise NotImplementedError
 
+    def wants_table(self) -> bool:
+        """True after ``load`` if the head has no weight of its own and is to share the embedding's
+        table; the model then calls ``tie`` with it."""
+        return False
+
+    def tie(self, table: torch.Tensor) -> None:
+        raise NotImplementedError
+
     def forward_from(self, residual: torch.Tensor, norm: Norm, rows_idx: torch.Tensor, rows: int,
                      out: torch.Tensor) -> bool:
         """Optional fused form: out[:rows] = head(norm(residual[rows_idx])).  False if not taken."""
@@ -236,11 +259,13 @@ class Block:
     block's last output, so that the add is fused with this block's first norm) and
     returns its own last output the same way."""
 
-    def __init__(self, mixer_norm: Norm, mixer: Mixer, ffn_norm: Norm, ffn: FeedForward, rt: Runtime):
+    def __init__(self, mixer_norm: Norm, mixer: Mixer, ffn_norm: Optional[Norm], ffn: Optional[FeedForward],
+                 rt: Runtime):
+        """``ffn_norm`` and ``ffn`` are None for a layer that has a mixer only."""
         self.mixer_norm, self.mixer, self.ffn_norm, self.ffn, self.rt = mixer_norm, mixer, ffn_norm, ffn, rt
 
     def parts(self) -> List[Part]:
-        return [self.mixer_norm, self.mixer, self.ffn_norm, self.ffn]
+        return [p for p in (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn) if p is not None]
 
     def first_norm(self) -> Optional[Norm]:
         """The norm this block applies to the incoming stream first, if the block before may hand it

@@ -1,5 +1,6 @@
 """Pre-norm residual block: h += mixer(norm(h)); h += ffn(norm(h)), the residual
-stream h in float32 (reference: src/cuda/model/llama.cpp:116-139)."""
+stream h in float32 (reference: src/cuda/model/llama.cpp:116-139).  A layer without a
+feed-forward stops after the first half."""
 
 from __future__ import annotations
 
@@ -33,7 +34,8 @@ class PreNormBlock(Block):
         # kernel and the residual add into their last (nothing is then left pending)
         taken = False
         if pending is None:
-            taken, hand = self._fused(ctx, hand, self.mixer_norm, self.ffn_norm,
+            taken, hand = self._fused(ctx, hand, self.mixer_norm,
+                                      self.ffn_norm if self.ffn is not None else ctx.block_next_norm,
                                       lambda: self.mixer.forward_into(residual, self.mixer_norm, ctx, cache, state))
         if taken:
             a = None
@@ -42,6 +44,9 @@ class PreNormBlock(Block):
             x = rt.workspace.get("block.normed", (rt.max_tokens, residual.shape[1]), rt.dtype)[:T]
             self.mixer_norm.add_norm(residual, pending, x, rows=T)
             a = self.mixer.forward(x, ctx, cache, state)
+        if self.ffn is None:               # a layer with a mixer only: its output is what is left to add
+            ctx.block_hand = hand if a is None else None
+            return a
         if a is None:
             taken, hand = self._fused(ctx, hand, self.ffn_norm, ctx.block_next_norm,
                                       lambda: self.ffn.forward_into(residual, self.ffn_norm, ctx))

@@ -57,6 +57,9 @@ class LMHead(Head):
         self.weight = None if self.params.tied else tensors.get("weight")
         self.shared = False
 
+    def wants_table(self) -> bool:
+        return self.weight is None
+
     def tie(self, table: torch.Tensor) -> None:
         self.weight = table
         self.shared = True

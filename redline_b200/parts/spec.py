@@ -27,13 +27,14 @@ class PartSpec:
 @dataclass(frozen=True)
 class LayerSpec:
     """A block: how a mixer and a feed-forward are arranged around the residual
-    stream.  ``arrangement`` names a registered block class."""
+    stream.  ``arrangement`` names a registered block class.  A layer that has a mixer
+    only leaves ``ffn_norm`` and ``ffn`` out."""
 
     arrangement: str
     mixer_norm: PartSpec
     mixer: PartSpec
-    ffn_norm: PartSpec
-    ffn: PartSpec
+    ffn_norm: Optional[PartSpec] = None
+    ffn: Optional[PartSpec] = None
 
 
 @dataclass(frozen=True)
@@ -72,20 +73,50 @@ class TensorSpec:
 
 
 @dataclass(frozen=True)
+class CacheTensor:
+    """One tensor that a mixer caches for each token it has seen.
+
+    name   how the mixer finds it in its ``LayerCache``
+    shape  of one token, for instance (heads, head_dim).  The last axis is kept contiguous; the pool
+           lays a tensor out as [pages, *shape[:-1], page_size, shape[-1]], so that the tokens of a page
+           under one index of the leading axes (a head's keys) are one contiguous box.
+    """
+
+    name: str
+    shape: Tuple[int, ...]
+
+    def elements(self) -> int:
+        n = 1
+        for x in self.shape:
+            n *= int(x)
+        return n
+
+
+@dataclass(frozen=True)
 class CacheSpec:
     """What a mixer needs cached for each token it has seen.
 
-    kind     "full": every key stays; "window": only the last ``window`` keys
-    heads, head_dim   size of the keys and of the values of one token
+    kind     "full": every token stays; "window": only the last ``window`` tokens
+    tensors  the tensors kept per token, each with a shape of its own (keys and values of the same
+             shape for ordinary attention; one latent vector, or keys and values of different widths,
+             for other mixers)
+    Layers whose mixers ask for the same spec share one group of pages and one block table per request.
     """
 
     kind: str
-    heads: int
-    head_dim: int
+    tensors: Tuple[CacheTensor, ...]
     window: int = 0
 
+    @staticmethod
+    def keys_values(kind: str, heads: int, head_dim: int, window: int = 0) -> "CacheSpec":
+        """Keys "k" and values "v" of [heads, head_dim] per token: what grouped-query attention caches."""
+        return CacheSpec(kind, (CacheTensor("k", (heads, head_dim)), CacheTensor("v", (heads, head_dim))), window)
+
+    def elements_per_token(self) -> int:
+        return sum(t.elements() for t in self.tensors)
+
     def group_key(self) -> Tuple:
-        return (self.kind, self.heads, self.head_dim, self.window)
+        return (self.kind, self.tensors, self.window)
 
 
 @dataclass(frozen=True)

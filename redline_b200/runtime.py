@@ -7,20 +7,14 @@
 Options carry the names of the command-line flags: ``max_seqs``, ``max_batched_tokens``,
 ``max_seq_len``, ``max_logit_rows``, ``block_size``, ``kv_cache_tokens``,
 ``gpu_memory_utilization``, ``cuda_graphs``, ``async_scheduling``, ``mix_prefill_decode``,
-``device``, plus ``dtype``.  ``CliEngine`` runs ``bin/redline_generate`` in a
-subprocess with the same interface; ``load_engine`` returns the in-process engine.
+``device``, plus ``dtype``.  The reference also has a subprocess engine around its
+compiled programs for installs without the extension module; this package is
+importable wherever its programs run, so ``load_engine`` always returns the in-process engine.
 """
 
 from __future__ import annotations
 
-import json
-import os
-import subprocess
-import sys
-import tempfile
 from typing import Any, Dict, List, Sequence
-
-ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 class Engine:
@@ -58,54 +52,7 @@ class Engine:
         return self._engine.describe()
 
 
-class CliEngine:
-    """Subprocess fallback around ``bin/redline_generate`` (one engine per call)."""
-
-    NEGATED = {"cuda_graphs": "--no-cuda-graphs", "async_scheduling": "--no-async",
-               "mix_prefill_decode": "--no-mixed-batches"}
-
-    def __init__(self, model: str, **options: Any):
-        self.model = model
-        self.flags: List[str] = []
-        for k, v in options.items():
-            if v is None:
-                continue
-            if k in self.NEGATED:
-                if v is False:
-                    self.flags.append(self.NEGATED[k])
-                continue
-            flag = "--" + k.replace("_", "-")
-            if isinstance(v, bool):
-                if v:
-                    self.flags.append(flag)
-                continue
-            self.flags += [flag, str(v)]
-        self.binary = os.path.join(ROOT, "bin", "redline_generate")
-
-    def _run(self, extra: List[str]) -> List[Dict[str, Any]]:
-        out = subprocess.run([sys.executable, self.binary, "--model", self.model, *self.flags, *extra],
-                             check=True, capture_output=True, text=True)
-        return [json.loads(line) for line in out.stdout.splitlines() if line.strip().startswith("{")]
-
-    def generate(self, prompts, max_new_tokens=128, temperature=0.0, top_k=0, top_p=1.0, seed=0,
-                 ignore_eos=False, stop_token_ids=()) -> List[Dict[str, Any]]:
-        with tempfile.NamedTemporaryFile("w", suffix=".json", delete=False) as f:
-            json.dump([list(p) for p in prompts], f)
-            path = f.name
-        try:
-            args = ["--prompts-json", path, "--max-new-tokens", str(max_new_tokens), "--temperature",
-                    str(temperature), "--top-k", str(top_k), "--top-p", str(top_p), "--seed", str(seed)]
-            if ignore_eos:
-                args.append("--ignore-eos")
-            if stop_token_ids:
-                args += ["--stop-token-ids", ",".join(map(str, stop_token_ids))]
-            return self._run(args)
-        finally:
-            os.unlink(path)
-
-    def score(self, tokens: Sequence[int]) -> List[float]:
-        return self._run(["--score-ids", ",".join(map(str, tokens))])[0]["logprobs"]
-
-
 def load_engine(model: str, **options: Any) -> Engine:
+    """The engine for a model folder (reference: python/redline/runtime.py:143-145, which
+    chooses between its extension module and its subprocess engine; here there is one)."""
     return Engine(model, **options)

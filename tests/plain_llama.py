@@ -1,8 +1,10 @@
 """Plain, slow implementation of the Llama decoder used as the oracle of the tests.
 
 Whole sequences, no cache, no batching, one function for each part, float64
-arithmetic on the CPU unless the reference fixes a narrower type (RoPE angles
-are formed in float32).  It shares no code with ``redline_b200``: it has its own
+arithmetic unless the reference fixes a narrower type (RoPE angles are formed in
+float32).  It runs where its weights lie: on the CPU in nearly all tests; the tests
+at the real layer sizes hand it weights on the GPU, where the same torch float64
+operations are fast enough for thousands of tokens.  It shares no code with ``redline_b200``: it has its own
 reading of ``config.json``, its own weight generator, its own safetensors writer.
 
 Every function cites the place in the reference project (Neil456/Redline, paths
@@ -158,7 +160,7 @@ def rope_rotate(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.
 
 def embedding(ids: Sequence[int], table: torch.Tensor) -> torch.Tensor:
     """Pure row gather, no scaling (src/cpu/reference_model.cpp:165-168)."""
-    return table[torch.as_tensor(list(ids), dtype=torch.long)].to(F64)
+    return table[torch.as_tensor(list(ids), dtype=torch.long, device=table.device)].to(F64)
 
 
 def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
@@ -188,11 +190,11 @@ def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: f
     T, Hq, D = q.shape
     Hkv = k.shape[1]
     G = Hq // Hkv
-    out = torch.zeros(T, Hq, D, dtype=F64)
+    out = torch.zeros(T, Hq, D, dtype=F64, device=q.device)
     for h in range(Hq):
         kh = h // G
         s = (q[:, h, :] @ k[:, kh, :].T) * scale  # [T, T]
-        idx = torch.arange(T)
+        idx = torch.arange(T, device=q.device)
         mask = idx[None, :] > idx[:, None]
         if window > 0:
             mask = mask | (idx[:, None] - idx[None, :] >= window)
@@ -246,8 +248,8 @@ def hidden_states(cfg: PlainConfig, w: Dict[str, torch.Tensor], tokens: Sequence
     """Embedding and the layer loop with pre-norm residual blocks; the result is
     the residual stream before the final norm (src/cpu/reference_model.cpp:157-233)."""
     T = len(tokens)
-    cos, sin = rope_tables(cfg, T)
     h = embedding(tokens, w["model.embed_tokens.weight"])
+    cos, sin = (t.to(h.device) for t in rope_tables(cfg, T))
     order = cfg.layer_order or [(i, -1) for i in range(cfg.num_layers)]
     kv_of_call: List[Tuple[torch.Tensor, torch.Tensor]] = []
     for layer, kv_owner in order:

@@ -10,9 +10,9 @@ from redline_b200.parts.spec import CacheSpec
 
 
 def setup(window=0):
-    groups = [GroupInfo(CacheSpec("full", 2, 64), [0])]
+    groups = [GroupInfo(CacheSpec.keys_values("full", 2, 64), [0])]
     if window:
-        groups.append(GroupInfo(CacheSpec("window", 2, 64, window), [1]))
+        groups.append(GroupInfo(CacheSpec.keys_values("window", 2, 64, window), [1]))
     cache = CacheManager(groups, [32] * len(groups), 16, 4)
     return cache, BatchBuilder(cache, max_tokens=128, max_seqs=4, max_rows=16, max_seq_len=128,
                                device=torch.device("cpu"))

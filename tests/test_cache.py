@@ -10,7 +10,7 @@ from redline_b200.parts.spec import CacheSpec
 
 
 def manager(pages=(9,), window=(0,), page_size=16, slots=4):
-    groups = [GroupInfo(CacheSpec("window" if w else "full", 2, 64, w), [i]) for i, w in enumerate(window)]
+    groups = [GroupInfo(CacheSpec.keys_values("window" if w else "full", 2, 64, w), [i]) for i, w in enumerate(window)]
     return CacheManager(groups, list(pages), page_size, slots)
 
 

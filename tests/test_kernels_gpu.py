@@ -103,6 +103,15 @@ def test_linear_bfloat16(M, N, K):
     close(linear(x, w, yf), ref, 1e-4)
 
 
+def plain_rope_tables(D, theta, num_pos, scaling=None):
+    """cos / sin [num_pos, D / 2] in float32 from the oracle's own table builder (not the product's)."""
+    pc = P.PlainConfig(vocab_size=0, hidden_size=0, intermediate_size=0, num_layers=0, num_heads=0, num_kv_heads=0,
+                       head_dim=D, rms_norm_eps=0.0, rope_theta=theta, rope_scaling=scaling, tie_word_embeddings=False,
+                       max_position_embeddings=num_pos)
+    cos, sin = P.rope_tables(pc, num_pos)
+    return cos.float().contiguous(), sin.float().contiguous()
+
+
 def paged_setup(dtype, Hq, Hkv, D, lens_past, lens_new, page_size, seed, sharp=None, cos=None, sin=None):
     """Random q/k/v for several sequences; pages with shuffled ids; returns everything a
     kernel launch needs plus the dense per-sequence tensors for the reference."""
@@ -153,10 +162,7 @@ def run_attention(dtype, Hq, Hkv, D, lens_past, lens_new, page_size=16, window=0
                   poison=True, decode_impl=0, prefill_impl=0):
     """Writes the past through rope_kv_write, then runs the new tokens (decode kernel for
     single tokens, prefill kernel for portions) and compares with the reference."""
-    from redline_b200.config.model_config import RopeScaling
-    from redline_b200.parts.rope import RotaryParams, rope_tables
-    cos, sin = rope_tables(RotaryParams(D, 10000.0, RopeScaling(), 4096),
-                           max(p + n for p, n in zip(lens_past, lens_new)) + 1)
+    cos, sin = plain_rope_tables(D, 10000.0, max(p + n for p, n in zip(lens_past, lens_new)) + 1)
     st = paged_setup(dtype, Hq, Hkv, D, lens_past, lens_new, page_size, seed, sharp, cos, sin)
     S, total, seqs = st["S"], st["total"], st["seqs"]
     scale = 1.0 / math.sqrt(D)
@@ -355,13 +361,11 @@ def test_attention_decode_with_rotation_and_cache_write_in_the_kernel(Hq, Hkv, D
     """attn_decode_rope against rope_kv_write followed by attn_decode: the same outputs, and the same k and
     v rows written into the cache at the tokens' own positions (and nowhere else); with many partitions
     (the streaming kernel) and with few (the one-partition kernel)."""
-    from redline_b200.config.model_config import RopeScaling
-    from redline_b200.parts.rope import RotaryParams, rope_tables
     g = torch.Generator().manual_seed(51)
     lens = [700, 1, 129, 2048, 33, 1500, 260, 2047]          # context lengths including the new token
     lens = lens * 4 if streams else lens[:5]
     B = len(lens)
-    cos, sin = rope_tables(RotaryParams(D, 10000.0, RopeScaling(), 4096), 2200)
+    cos, sin = plain_rope_tables(D, 10000.0, 2200)
     cos, sin = cos.to(DEV).contiguous(), sin.to(DEV).contiguous()
     blocks = [(n + page_size - 1) // page_size for n in lens]
     npages = sum(blocks) + 1
@@ -438,6 +442,10 @@ def test_attention_decode_beyond_256_partitions():
 def test_attention_mixed_launch_and_other_page_sizes(dtype):
     run_attention(dtype, 4, 2, 64, [300, 31, 0, 90], [1, 33, 2, 1], page_size=32, seed=5)
     run_attention(dtype, 3, 1, 128, [63, 64, 200], [1, 65, 1], page_size=64, seed=6)
+    # pages of 48 and 80 keys are no power of two: the tensor-core kernels, which find a key's page with a
+    # shift and a mask, must leave such launches to the CUDA-core kernels
+    run_attention(dtype, 4, 2, 64, [300, 31, 0, 90], [1, 33, 2, 1], page_size=48, seed=7)
+    run_attention(dtype, 8, 2, 128, [100, 700, 5], [1, 1, 140], page_size=80, seed=8)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -479,10 +487,8 @@ def test_a_far_key_is_found_among_hundreds(dtype):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_rope_kv_write_values_and_skipped_writes(dtype):
-    from redline_b200.config.model_config import RopeScaling
-    from redline_b200.parts.rope import RotaryParams, rope_tables
     Hq, Hkv, D, ps = 3, 2, 48, 16
-    cos, sin = rope_tables(RotaryParams(D, 5e4, RopeScaling("linear", 2.0), 512), 512)
+    cos, sin = plain_rope_tables(D, 5e4, 512, {"type": "linear", "factor": 2.0})
     T = 9
     x = torch.randn(T, (Hq + 2 * Hkv) * D).to(DT[dtype])
     pos = torch.tensor([0, 1, 15, 16, 17, 100, 255, 300, 511], dtype=torch.int32)
@@ -515,6 +521,11 @@ def test_rope_kv_write_values_and_skipped_writes(dtype):
     kernels.rope_kv_write(qkv, torch.full((T,), 512, dtype=torch.int32, device=DEV), None, cos.to(DEV),
                           sin.to(DEV), kc, vc, Hq, Hkv, D, ps, status)
     assert status.item() == 2                                     # a position beyond the table is flagged
+    status.zero_()
+    before = kc.clone()
+    far = torch.tensor([6 * ps, 6 * ps + 5, 2 ** 30] + [-1] * (T - 3), dtype=torch.int32, device=DEV)
+    kernels.rope_kv_write(x.to(DEV).clone(), pos.to(DEV), far, cos.to(DEV), sin.to(DEV), kc, vc, Hq, Hkv, D, ps, status)
+    assert status.item() == 4 and torch.equal(kc, before)         # a slot beyond the pool: flagged, not written
 
 
 def test_resolve_ids_and_bias_and_residual():

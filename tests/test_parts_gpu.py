@@ -69,7 +69,7 @@ def test_norm_embedding_head_mlp(dtype):
     norm.add_norm(res_d, delta.to(DEV), out)
     assert rel_max(out.double().cpu().numpy(), P.rmsnorm(res.double() + delta.double(), wn, 3e-6).numpy()) < tol
     # embedding
-    harness = Harness(__import__("redline_b200.parts.spec", fromlist=["CacheSpec"]).CacheSpec("full", 1, 16), dtype)
+    harness = Harness(__import__("redline_b200.parts.spec", fromlist=["CacheSpec"]).CacheSpec.keys_values("full", 1, 16), dtype)
     emb = build_part("embedding", PartSpec("token_embedding", EmbeddingParams(V, H), {"weight": "e"}), rt)
     table = r(V, H).to(dtype)
     emb.load({"weight": table.to(DEV)})

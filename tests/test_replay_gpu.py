@@ -74,16 +74,22 @@ def test_whole(name, dtype, models, engines):
     eng.runner.cache.check_invariants()
 
 
+@pytest.mark.parametrize("graphs", [False, True])
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", CONFIGS)
-def test_last_32_tokens_one_by_one(name, dtype, models, engines):
-    eng, (_, w) = engines(name, dtype), models[name, dtype]
+def test_last_32_tokens_one_by_one(name, dtype, graphs, models, engines):
+    """With ``graphs`` the single-token steps run as generation runs them: padded to a fixed shape, the
+    sampler behind the head, captured once and replayed as a CUDA graph whose launches are sized for the
+    longest sequence the engine allows."""
+    eng, (_, w) = engines(name, dtype, cuda_graphs=graphs), models[name, dtype]
     toks = random_tokens(vocab(name), LENGTHS[name], 2)
     n0 = len(toks) - 32
-    outs = [eng.step_tokens([("d", toks[:n0], [n0 - 1])]).cpu().numpy()]
+    before = eng.runner.num_graph_steps
+    outs = [eng.step_tokens([("d", toks[:n0], [n0 - 1])], graphs=graphs).cpu().numpy()]
     for i in range(n0, len(toks)):
-        outs.append(eng.step_tokens([("d", toks[i:i + 1], [0])]).cpu().numpy())
+        outs.append(eng.step_tokens([("d", toks[i:i + 1], [0])], graphs=graphs).cpu().numpy())
     eng.close_request("d")
+    assert eng.runner.num_graph_steps - before == (32 if graphs else 0)
     check_logits(np.concatenate(outs), C.ALL[name], w, toks, dtype, rows=range(n0 - 1, len(toks)))
 
 
@@ -164,19 +170,23 @@ def mixed_schedule(lengths, pool_tokens, seed):
     return steps
 
 
+@pytest.mark.parametrize("graphs", [False, True])
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", CONFIGS)
-def test_mixed_with_pages_used_again(name, dtype, models, engines):
+def test_mixed_with_pages_used_again(name, dtype, graphs, models, engines):
+    """With ``graphs`` the steps that hold single tokens only are padded with dummy rows on the reserved
+    page and replayed as CUDA graphs, between eager steps that hold portions."""
     lengths = [129, 70, 40, 97, 33, 150, 64, 5]
     pool = 384
-    eng, (_, w) = engines(name, dtype, kv_cache_tokens=pool), models[name, dtype]
+    eng, (_, w) = engines(name, dtype, kv_cache_tokens=pool, cuda_graphs=graphs), models[name, dtype]
+    graph_steps = eng.runner.num_graph_steps
     toks = {i: random_tokens(vocab(name), n, 100 + i) for i, n in enumerate(lengths)}
     got = {i: [] for i in toks}
     pages_seen = {}
     reused = False
     for entries, ends in mixed_schedule(lengths, pool, seed=7):
         batch = [(f"r{i}", toks[i][s:s + n], list(range(n))) for i, s, n in entries]
-        out = eng.step_tokens(batch).cpu().numpy()
+        out = eng.step_tokens(batch, graphs=graphs).cpu().numpy()
         r = 0
         for i, s, n in entries:
             got[i].append(out[r:r + n])
@@ -189,6 +199,7 @@ def test_mixed_with_pages_used_again(name, dtype, models, engines):
         eng.runner.cache.check_invariants()
     assert reused, "the pool was large enough that no page was handed out twice"
     assert eng.runner.cache.num_open() == 0
+    assert (eng.runner.num_graph_steps > graph_steps) == graphs
     for i in toks:
         check_logits(np.concatenate(got[i]), C.ALL[name], w, toks[i], dtype)
 

@@ -11,7 +11,7 @@ from redline_b200.sampling import SamplingParams
 
 
 def make(pages=64, max_seqs=4, budget=32, max_len=256, mix=True, watermark=0.01):
-    cache = CacheManager([GroupInfo(CacheSpec("full", 2, 64), [0, 1])], [pages + 1], 16, max_seqs)
+    cache = CacheManager([GroupInfo(CacheSpec.keys_values("full", 2, 64), [0, 1])], [pages + 1], 16, max_seqs)
     return Scheduler(SchedulerConfig(max_seqs, budget, max_len, mix, watermark), cache), cache
 
 

@@ -156,7 +156,8 @@ def toy_oracle(w, toks, table):
     return (P.rmsnorm(h, w["fn"], 1e-5) @ w["head"].double().T).numpy()
 
 
-def test_toy_parts_are_registered_built_loaded_and_stepped(tmp_path):
+def toy_engine(tmp_path, **options):
+    """(engine, weights) of the toy model in float32; the model folder is written once per test."""
     from redline_b200.config import EngineConfig
     from redline_b200.config.model_config import ModelConfig
     from redline_b200.engine.engine import Engine
@@ -164,13 +165,26 @@ def test_toy_parts_are_registered_built_loaded_and_stepped(tmp_path):
     register_toys()
     w = toy_weights()
     d = str(tmp_path / "toy")
-    os.makedirs(d)
-    P.write_safetensors(os.path.join(d, "model.safetensors"), w)
-    cfg = EngineConfig.from_options(d, dict(dtype="float32", kv_cache_tokens=256, max_seq_len=256, max_num_seqs=3,
-                                            max_num_batched_tokens=128, max_logit_rows=128, cuda_graphs=False,
-                                            async_scheduling=False))
-    runner = ModelRunner(cfg, ModelConfig("ToyForTests", V, H, 256, -1, ()), toy_spec())
-    eng = Engine.from_runner(runner)
+    if not os.path.isdir(d):
+        os.makedirs(d)
+        P.write_safetensors(os.path.join(d, "model.safetensors"), w)
+    opts = dict(dtype="float32", kv_cache_tokens=256, max_seq_len=256, max_num_seqs=3, max_num_batched_tokens=128,
+                max_logit_rows=128, cuda_graphs=False, async_scheduling=False)
+    opts.update(options)
+    runner = ModelRunner(EngineConfig.from_options(d, opts), ModelConfig("ToyForTests", V, H, 256, -1, ()), toy_spec())
+    return Engine.from_runner(runner), w
+
+
+def oracle_greedy(w, table, prompt, outputs):
+    """Whether ``outputs`` are the arg max of the restatement's logits after every prefix."""
+    seq = list(prompt) + list(outputs)
+    ref = toy_oracle(w, seq[:-1], table)
+    return [int(ref[len(prompt) - 1 + i].argmax()) for i in range(len(outputs))] == list(outputs)
+
+
+def test_toy_parts_are_registered_built_loaded_and_stepped(tmp_path):
+    eng, w = toy_engine(tmp_path)
+    runner = eng.runner
     assert sorted(runner.states.pools) == [0, 2] and runner.states.pools[0].shape == (3, H)
     assert len(runner.groups) == 1 and runner.groups[0].owners == [1]
     table = runner.model.blocks[1].mixer.position.table.cpu()
@@ -196,6 +210,36 @@ def test_toy_parts_are_registered_built_loaded_and_stepped(tmp_path):
     eng.close_request("c")
     # and generation through the scheduler works with these parts too
     outs = eng.generate([a[:20], b[:9]], max_new_tokens=5, ignore_eos=True)
-    seq = a[:20] + outs[0]["output_ids"]
-    ref = toy_oracle(w, seq[:-1], table)
-    assert [int(ref[19 + i].argmax()) for i in range(5)] == outs[0]["output_ids"]
+    assert oracle_greedy(w, table, a[:20], outs[0]["output_ids"])
+    assert oracle_greedy(w, table, b[:9], outs[1]["output_ids"])
+
+
+def test_state_keeping_mixer_with_cuda_graphs_asked_for(tmp_path):
+    """With per-request state in the model the engine steps eagerly even when CUDA graphs are on (a
+    graph's padding rows would share slot 0 with a live request, and capturing runs a step more than
+    once): generation with graphs and asynchronous scheduling asked for gives the restatement's tokens."""
+    eng, w = toy_engine(tmp_path, cuda_graphs=True, async_scheduling=True, max_num_seqs=4)
+    table = eng.runner.model.blocks[1].mixer.position.table.cpu()
+    rng = np.random.RandomState(11)
+    prompts = [rng.randint(0, V, n).tolist() for n in (20, 9, 33, 14)]
+    outs = eng.generate(prompts, max_new_tokens=12, ignore_eos=True)
+    assert eng.runner.num_graph_steps == 0 and eng.runner.num_eager_steps > 0
+    for p, o in zip(prompts, outs):
+        assert oracle_greedy(w, table, p, o["output_ids"]), o["id"]
+
+
+def test_state_keeping_mixer_under_recompute_preemption(tmp_path):
+    """A pool of 160 tokens for four requests that grow to 70 each: the newest are preempted, their
+    pages and state slots given back, and later recomputed from prompt + generated tokens.  A slot
+    that is handed out again starts from zero, so the recomputed state is the restatement's."""
+    eng, w = toy_engine(tmp_path, kv_cache_tokens=160, max_num_seqs=4, max_num_batched_tokens=64,
+                        async_scheduling=True)
+    table = eng.runner.model.blocks[1].mixer.position.table.cpu()
+    rng = np.random.RandomState(12)
+    prompts = [rng.randint(0, V, n).tolist() for n in (40, 38, 35, 30)]
+    outs = eng.generate(prompts, max_new_tokens=30, ignore_eos=True)
+    assert eng.num_preemptions > 0 and sum(o["num_preemptions"] for o in outs) > 0
+    for p, o in zip(prompts, outs):
+        assert len(o["output_ids"]) == 30 and oracle_greedy(w, table, p, o["output_ids"]), o["id"]
+    assert eng.runner.cache.num_open() == 0
+    eng.runner.cache.check_invariants()
