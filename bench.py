@@ -11,12 +11,14 @@ of 4,096).  One JSON line is printed:
   e2e       the same K-step measure by the wall clock through the Python entry point:
             every step uploads its metadata from pinned host memory and the host reads
             the sampled tokens back
-  prefill   one 2,048-token prompt in one step: tokens/s and the fraction of the
-            measured bf16 tensor-core peak that its FLOPs reach
+  prefill   one 2,048-token prompt alone on an idle GPU, host preparation included:
+            tokens/s and the fraction of the measured bf16 tensor-core peak that its
+            FLOPs reach ("back_to_back_ms": per prompt when prompts follow one another)
   roofline  bytes a decode step has to read (every weight once, the cache of the
             live requests) / its time, against the measured copy bandwidth
-  points    decode tokens/s at batch 1 and 64 (512-token prompts, the reference's
-            decode workload)
+  points    decode tokens/s at batch 1, 8 and 64 with 512-token prompts (the metric's
+            decode workload), each with its step time and its fraction of the copy
+            bandwidth (the same byte count at its batch and context)
 
 Weights are random (N(0, 0.02^2)), token ids uniform random: the sizes are what is
 measured.  ``--impl reference`` runs the unmodified reference (built by
@@ -128,6 +130,23 @@ class ClockSampler:
         sm.sort()
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx or None,
                 "reasons": sorted(reasons), "samples": len(sm), "widened": widened}
+
+
+def bench_config(cfg: Dict[str, Any], steps: int, warmup: int, peaks_source: str) -> Dict[str, Any]:
+    """The ``config`` of the JSON line: every size, flat.  Both arms print the same dictionary."""
+    return {
+        "model": "llama-3.2-1b-sizes", "layers": cfg["num_hidden_layers"], "layers_full": 16,
+        "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
+        "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
+        "global_batch": BATCH, "seq_len": CONTEXT, "context_at_timing": timed_prompt(steps, warmup) + warmup + steps // 2,
+        "page_size": 16, "parallelism": "single-gpu", "l2": "step reads weights + cache >> L2, no flush",
+        "points_prompt": POINT_PROMPT, "prefill_tokens": PREFILL_TOKENS, "peaks": peaks_source,
+    }
+
+
+def timed_prompt(steps: int, warmup: int) -> int:
+    """Prompt length of the headline run: the requests reach the context limit just after the timed steps."""
+    return CONTEXT - (warmup + 2 * steps + 34)
 
 
 def model_numbers(cfg: Dict[str, Any]) -> Dict[str, float]:
@@ -358,14 +377,17 @@ def run_ours(args) -> Dict[str, Any]:
         nums = model_numbers(cfg)
         sampler.start()
         K, W = args.steps, args.warmup
-        prompt = CONTEXT - (W + 2 * K + 34)
-        main = decode_run(model, BATCH, prompt, K, W, sampler, CONTEXT)
+        main = decode_run(model, BATCH, timed_prompt(K, W), K, W, sampler, CONTEXT)
         pre = prefill_run(model, PREFILL_TOKENS)
         pts = {}
-        for b in (1, 64):
+        hbm = pk.get("hbm_gbs", FALLBACK_PEAKS["hbm_gbs"])
+        for b in (1, 8, 64):
             r = decode_run(model, b, POINT_PROMPT, min(K, 64), W, sampler, 1024)
+            bytes_b = nums["weight_bytes"] + b * r["ctx_mid"] * nums["kv_bytes_per_token"]
             pts[f"decode_b{b}"] = round(r["tok_s"], 1)
             pts[f"decode_b{b}_e2e"] = round(r["e2e_tok_s"], 1)
+            pts[f"decode_b{b}_ms"] = round(r["ms_per_step"], 4)
+            pts[f"decode_b{b}_frac"] = round(bytes_b / (r["ms_per_step"] / 1e3) / 1e9 / hbm, 4)
     finally:
         sampler.stop()
         shutil.rmtree(tmp, ignore_errors=True)
@@ -379,36 +401,49 @@ def run_ours(args) -> Dict[str, Any]:
         "ms_per_step": round(main["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic (random weights, uniform random token ids)",
         "impl": "ours",
-        "config": {
-            "model": "llama-3.2-1b-sizes", "layers": cfg["num_hidden_layers"], "layers_full": 16,
-            "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
-            "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
-            "global_batch": BATCH, "seq_len": CONTEXT, "context_at_timing": main["ctx_mid"], "page_size": 16,
-            "parallelism": "single-gpu", "l2": "step reads weights + cache >> L2, no flush", "cuda_graph": main["cuda_graph"],
-            "points_prompt": POINT_PROMPT, "peaks": pk["source"],
-        },
+        "config": bench_config(cfg, K, W, pk["source"]), "cuda_graph": main["cuda_graph"],
         "e2e": {"value": round(main["e2e_tok_s"], 1), "unit": "tok/s", "h2d_bytes_per_step": main["h2d_bytes"],
                 "d2h_bytes_per_step": main["d2h_bytes"], "ms_per_step": round(main["e2e_ms_per_step"], 4),
                 "host_ms_p50": round(main["host_ms_p50"], 4)},
         "gpu_launches": int(main["launches"]),
         "clocks": main["clocks"],
-        "prefill": {"value": round(PREFILL_TOKENS / (pre["ms"] / 1e3), 1), "tokens": PREFILL_TOKENS,
-                    "ms": round(pre["ms"], 3), "frac": round(pf / (pre["ms"] / 1e3) / (peak_tflops * 1e12), 4),
-                    "latency_ms": round(pre["latency_ms"], 3)},
+        "prefill": {"value": round(PREFILL_TOKENS / (pre["latency_ms"] / 1e3), 1), "tokens": PREFILL_TOKENS,
+                    "ms": round(pre["latency_ms"], 3),
+                    "frac": round(pf / (pre["latency_ms"] / 1e3) / (peak_tflops * 1e12), 4),
+                    "back_to_back_ms": round(pre["ms"], 3)},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk.get("hbm_gbs"), "unit": "GB/s",
                      "frac": round(achieved / pk.get("hbm_gbs", FALLBACK_PEAKS["hbm_gbs"]), 4)},
         "points": pts,
     }
 
 
+def full_width_steps(trace: Dict[str, Any], batch: int) -> List[Dict[str, float]]:
+    """The pure-decode steps of a reference trace (its ``redline-trace-v1`` format: ``step_fields`` names
+    the columns of ``steps``) that hold all ``batch`` sequences, in order, as dicts with gpu_ms and the
+    time since the step before finished."""
+    col = {name: i for i, name in enumerate(trace["step_fields"])}
+    out, prev_done = [], None
+    for row in trace["steps"]:
+        done = row[col["t_done_ms"]]
+        if row[col["kind"]] == "decode" and row[col["seqs"]] == batch:
+            out.append({"gpu_ms": row[col["gpu_ms"]],
+                        "wall_ms": done - prev_done if prev_done is not None else row[col["gpu_ms"]]})
+        prev_done = done
+    return out
+
+
 def run_reference(args) -> Dict[str, Any]:
-    """The unmodified reference on the same workload through its own redline_bench."""
+    """The unmodified reference on the same workload through its own redline_bench.  Its report sums
+    over every decode step, also those while requests are still being admitted or have already
+    finished; to time what the other arm times, the per-step trace it writes is read and only steps
+    that hold all BATCH sequences count: W of them are skipped, the next K are the timed ones."""
     ref = os.path.join(ROOT, "baseline", "_ref")
     binary = os.path.join(ref, "build", "redline_bench")
     if not os.path.exists(binary):
         return {"impl": "reference", "unavailable": "baseline/_ref/build/redline_bench is not built "
                                                     "(run baseline/build_reference.sh on the build machine)"}
     tmp = tempfile.mkdtemp(prefix="redline_ref_")
+    K, W = args.steps, args.warmup
     try:
         model = write_model(tmp, None)
         rlm = os.path.join(tmp, "model.rlm")
@@ -416,26 +451,40 @@ def run_reference(args) -> Dict[str, Any]:
         r = subprocess.run([sys.executable, "-m", "redline.convert", "--model", model, "--out", rlm, "--device", "cpu"], env=env, capture_output=True, text=True)
         if r.returncode != 0:
             return {"impl": "reference", "unavailable": "the reference's converter failed: " + r.stderr.strip()[-300:]}
-        K, W = args.steps, args.warmup
-        prompt = CONTEXT - (W + 2 * K + 34)
-        out = os.path.join(tmp, "report.json")
-        cmd = [binary, "--model", rlm, "--synthetic", f"{BATCH},{prompt},{W + K}", "--max-seqs", str(BATCH),
-               "--max-seq-len", str(CONTEXT), "--out", out]
+        prompt = timed_prompt(K, W)
+        # long enough that W + K steps hold every sequence: the first sequences decode while the
+        # prompts of the later ones are still being prefilled, and finish that much earlier
+        new_tokens = min(W + K + 4 * BATCH + 8, CONTEXT - prompt - 1)
+        out, trace_path = os.path.join(tmp, "report.json"), os.path.join(tmp, "trace.json")
+        cmd = [binary, "--model", rlm, "--synthetic", f"{BATCH},{prompt},{new_tokens}", "--max-seqs", str(BATCH),
+               "--max-seq-len", str(CONTEXT), "--out", out, "--trace-out", trace_path]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             return {"impl": "reference", "unavailable": "redline_bench failed: " + r.stderr.strip()[-300:]}
         with open(out) as f:
             rep = json.load(f)
+        with open(trace_path) as f:
+            full = full_width_steps(json.load(f), BATCH)
     finally:
         shutil.rmtree(tmp, ignore_errors=True)
-    step_ms = rep["decode_step_gpu_ms"]["mean"]
+    timed = full[W:W + K] if len(full) > W else full
+    if not timed:
+        return {"impl": "reference", "unavailable": f"its trace has no decode step with all {BATCH} sequences"}
+    gpu_ms = sum(t["gpu_ms"] for t in timed) / len(timed)
+    wall_ms = sum(t["wall_ms"] for t in timed) / len(timed)
     return {
         "metric": "decode tok/s at batch 8, context 4096 (Llama 3.2 1B sizes)", "impl": "reference",
-        "value": round(rep["decode_throughput_gpu_tok_s"], 1), "unit": "tok/s", "n_gpus": 1, "steps": K, "warmup": W,
-        "ms_per_step": round(step_ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "value": round(BATCH / (gpu_ms / 1e3), 1), "unit": "tok/s", "n_gpus": 1, "steps": K, "warmup": W,
+        "ms_per_step": round(gpu_ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "fp16", "data": "synthetic (random weights, uniform random token ids)",
-        "config": {"model": "llama-3.2-1b-sizes", "global_batch": BATCH, "seq_len": CONTEXT, "parallelism": "single-gpu"},
-        "e2e": {"value": round(rep["decode_throughput_tok_s"], 1), "unit": "tok/s"},
+        "config": bench_config(BENCH_CONFIG, K, W, peaks()["source"]),
+        "timed_steps": len(timed), "seqs_per_timed_step": BATCH, "full_width_decode_steps": len(full),
+        "e2e": {"value": round(BATCH / (wall_ms / 1e3), 1), "unit": "tok/s", "ms_per_step": round(wall_ms, 4),
+                "note": "host tokens in and out every step through the reference's own engine loop; it does "
+                        "not report the bytes it copies"},
+        "whole_run": {"decode_tok_s_gpu": round(rep["decode_throughput_gpu_tok_s"], 1),
+                      "decode_tok_s": round(rep["decode_throughput_tok_s"], 1),
+                      "decode_step_gpu_ms_mean": round(rep["decode_step_gpu_ms"]["mean"], 4)},
         "prefill": {"value": round(rep["prefill_throughput_gpu_tok_s"], 1)},
     }
 
