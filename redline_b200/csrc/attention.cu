@@ -1007,7 +1007,7 @@ prefill_attn_mma_kernel(const PrefillArgs<bf16> a) {
 #endif  // tensor-core prefill
 
 }  // namespace rl
-#if RL_HEAD_DIM == 64
+#if RL_HEAD_DIM == 64 || RL_HEAD_DIM == 128
 #include "prefill_tc.cuh"
 #define RL_HAVE_TC_PREFILL 1
 #endif
@@ -1207,7 +1207,7 @@ int launch_prefill(const void* q, int q_stride, const void* kc, const void* vc, 
         tsms_of[dev] = n > 0 ? n : 1;
       }
       const int tsms = tsms_of[dev];
-      const long long items = static_cast<long long>(tiles) * hq;
+      const long long items = static_cast<long long>(tiles) * hkv * ((hq / hkv + 1) / 2);   // (tile, kv head, pair of heads)
       const int ctas = static_cast<int>(items < tsms ? items : tsms);      // persistent: one CTA per SM
       launch_kernel(prefill_attn_tc_kernel, dim3(ctas), dim3(kTcThreads), kPrefillTcSmem, stream, a, tiles, status);
       return static_cast<int>(cudaGetLastError());

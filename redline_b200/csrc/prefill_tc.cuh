@@ -1,25 +1,34 @@
-// Prompt-portion attention on the fifth-generation tensor cores (bfloat16, head size 64).
+// Prompt-portion attention on the fifth-generation tensor cores (bfloat16, head size 64 or 128).
 //
 // Included by attention.cu.  An item of work is a tile of up to 128 consecutive query rows of one
-// sequence for one query head; persistent CTAs (one per SM) take items one after another, longest
-// first, and the pipeline below runs on across items (the next item's Q and first keys are on their
-// way while the rows of this one finish).  Per item the keys come in tiles of 128:
-//   S = Q K^T      tcgen05.mma, 128 x 128, K = 64, accumulator in tensor memory (two S buffers)
-//   softmax        two threads per query row read the row of S from TMEM (tcgen05.ld), keep the
-//                  running maximum and denominator in float32, writes P as bfloat16 into shared
-//                  memory in the K-major 128-byte-swizzled layout that the MMA reads
-//   O_tile = P V   tcgen05.mma, 128 x 64, K = 128; V is read as it lies in the cache (a key's 64
-//                  values contiguous: the B operand in MN-major form); fresh accumulator per key
-//                  tile (two O buffers), which the row's thread adds into its float32 running sum
-//                  after scaling that by 2^(old max - new max)
-// Warp roles: warps 0-7 are the row threads, two to a row (warp w owns TMEM lanes 32 (w % 4) .., the
-// keys 64 (w / 4) .. of an S tile and the columns 32 (w / 4) .. of O), warp 8 brings Q once and
-// the K tiles, warp 9 the V tiles, from the paged cache with 16-byte cp.async copies (two stages
-// each, zero-filled outside the live keys), lane 0 of warp 10 issues the MMAs, the S product of tile
-// i + 1 before the O product of tile i so that the tensor core works while the rows of tile i are
-// in their softmax.  Everything is handed over through mbarriers; every wait is bounded
-// (kSpinLimit polls), after which the CTA raises an abort flag, all roles leave their loops, the
-// copies in flight are waited for, TMEM is freed and bit 2 of *status is set.
+// sequence for TWO query heads of one kv head (the last pair of an odd group has one): the two
+// heads are the CTA's two "slots", they attend to the same keys and values, so a K tile and a V
+// tile are brought into shared memory once for both.  Persistent CTAs (one per SM) take items
+// one after another, longest first, and the pipeline runs on across items.  Per item the keys
+// come in tiles of 128; for each slot and key tile:
+//   S = Q K^T      tcgen05.mma, 128 x 128, k = head size, accumulator in tensor memory
+//   softmax        ONE thread per query row (four warps per slot) reads its row of S from tensor
+//                  memory, keeps the running maximum and denominator in float32 and writes P as
+//                  bfloat16 back into tensor memory, over the columns of S it has read
+//   O += P V       tcgen05.mma with P as the A operand from tensor memory and V as it lies in the
+//                  cache (a key's values contiguous: the B operand in MN-major form); O stays in
+//                  tensor memory for the whole item and is accumulated by the tensor core
+// The running maximum that P is scaled by is moved (and O and the denominator rescaled, by the
+// row's own thread, between two products) only when a warp sees a row's maximum grow by more
+// than 2^8 over it: P stays below 256, which bfloat16 holds as well as numbers below 1, and the
+// rescaling of O, a round trip through registers, becomes rare after a row's first tiles.  The
+// result is the same sum: every term of a row carries the same factor, which the division by
+// the denominator takes out.
+// While the rows of one slot are in their softmax, the tensor core works on the other slot's
+// products: per key tile the MMA thread issues  O0 += P0 V, S0' = Q0 K', O1 += P1 V, S1' = Q1 K'.
+// Tensor memory: S0 at column 0, S1 at 128 (P over the first 64 columns of each), O0 at 256,
+// O1 at 256 + head size.
+// Warp roles: warps 0-3 rows of slot 0, warps 4-7 rows of slot 1 (warp w owns TMEM lanes
+// 32 (w % 4) ..), warp 8 brings both Q tiles once per item and the K tiles, warp 9 the V tiles,
+// from the paged cache with 16-byte cp.async copies (zero-filled outside the live keys), lane 0
+// of warp 10 issues the MMAs.  Everything is handed over through mbarriers; every wait is
+// bounded (kSpinLimit polls), after which the CTA raises an abort flag, all roles leave their
+// loops, the copies in flight are waited for, TMEM is freed and bit 2 of *status is set.
 #pragma once
 
 #include "umma.cuh"
@@ -27,36 +36,42 @@
 namespace rl {
 
 constexpr int kTcRows = 128, kTcKeys = 128;
-constexpr int kTcThreads = 352;                     // 8 row warps, two loaders, the MMA warp
-constexpr int kTcTileBytes = kTcKeys * 128;          // a 128 x 64 bfloat16 tile: K, V, Q or half of P
-constexpr int kTcTmemCols = 512;                     // S0 0.., S1 128.., O0 256.., O1 320..
+constexpr int kTcThreads = 352;                        // 8 row warps, two loaders, the MMA warp
+constexpr int kTcHalves = kD / 64;                      // a head's columns in halves of 64 (128 bytes)
+constexpr int kTcHalfBytes = 128 * 128;                 // 128 rows x 64 bfloat16, 128-byte swizzled
+constexpr int kTcTileBytes = kTcHalves * kTcHalfBytes;  // a Q, K or V tile
+constexpr int kTcStages = kD == 64 ? 3 : 2;             // K and V stages
+constexpr int kTcTmemCols = 512;
+constexpr int kTcColO = 256;                            // O of slot s at kTcColO + s * kD
+constexpr float kTcGrow = 8.f;                          // log2 of the growth of a row's maximum that moves the reference
 
 struct PrefillTcShared {
-  uint64_t q_full[2], q_free[2];      // Q of an item has landed / its last S product has read it
-  uint64_t k_full[2], v_full[2];      // one arrival by the loader warp (after all its lanes' copies have landed)
-  uint64_t qk_done[2], pv_done[2];    // MMA commits: S of the tile is ready / K stage free; O of the tile ready / V, P free
-  uint64_t s_free[2], o_free[2];      // the 8 row warps have read the buffer
-  uint64_t p_ready[2];                // the 8 row warps have written P
-  uint64_t pair[4];                   // the two warps of a quarter of rows exchange a value (2 arrivals a phase)
-  float xchg[2][2][kTcRows];          // [phase parity][half][row]
+  uint64_t q_full[2], q_free[2];                  // per slot: Q of an item has landed / its last S product has read it
+  uint64_t k_full[kTcStages], k_free[kTcStages];  // loader's arrival / the tile's last S product is done
+  uint64_t v_full[kTcStages], v_free[kTcStages];  // loader's arrival / the tile's last O product is done
+  uint64_t qk_done[2], pv_done[2];                // per slot, MMA commits: S of the tile is ready / its O product is done
+  uint64_t p_ready[2];                            // per slot: its four row warps have written P
+  uint64_t o_free[2];                             // per slot: its four row warps have read the item's O
   uint32_t tmem_base;
   volatile int abort;
 };
-constexpr size_t kPrefillTcSmem = 1024 + 10 * kTcTileBytes + sizeof(PrefillTcShared);   // 2 Q, 2 K, 2 V, 2 x 2 P
+constexpr size_t kPrefillTcSmem = 1024 + (2 + 2 * kTcStages) * kTcTileBytes + sizeof(PrefillTcShared);
 
-// One item of a CTA's work: a tile of query rows for one query head.
+// One item of a CTA's work: a tile of query rows for up to two query heads of one kv head.
 struct TcItem {
-  int seq, tok0, rows, head, kvh;
+  int seq, tok0, rows, head0, kvh;
+  bool two;                            // the second slot has a head (head0 + 1)
   int pos0, k_end, lo0, k_begin, nt;   // first position, keys [lo0, k_end) are live, nt key tiles from k_begin
 };
 
-// Items are numbered longest first (a later tile of a sequence attends to more keys), the heads of a
-// tile next to each other, so that CTAs that run together share K and V in L2.
-__device__ __forceinline__ TcItem tc_item(const PrefillArgs<bf16>& a, int item, int tiles) {
+// Item `rem` of a tile of query rows: kv head rem / pairs, pair of heads rem % pairs.
+__device__ __forceinline__ TcItem tc_item(const PrefillArgs<bf16>& a, int tile, int rem, int pairs) {
   TcItem w;
-  const int tile = tiles - 1 - item / a.hq;
-  w.head = item - (item / a.hq) * a.hq;
-  w.kvh = w.head / (a.hq / a.hkv);
+  const int G = a.hq / a.hkv;
+  w.kvh = rem / pairs;
+  const int p = rem - w.kvh * pairs;
+  w.head0 = w.kvh * G + 2 * p;
+  w.two = 2 * p + 1 < G;
   w.seq = a.tile_seq[tile];
   w.tok0 = a.tile_tok[tile];
   w.rows = a.tile_rows[tile];
@@ -80,6 +95,37 @@ __device__ __forceinline__ uint64_t umma_desc_mn(uint32_t smem_addr) {
   return d;
 }
 
+// D (tensor memory) += A (tensor memory: a row per lane, two bfloat16 of k per 32-bit column) x B (shared memory).
+__device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
+      "}\n"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// 16 consecutive 32-bit columns of this thread's TMEM lane, load (no wait) and store.
+__device__ __forceinline__ void tmem_ld16_issue(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
 // The items of a CTA: in round k the CTAs take items k G .. k G + G - 1 (G CTAs), in odd rounds in
 // reverse order, so that the CTA with the longest item of one round has the shortest of the next.
 // Gives the CTA's next item and moves `round` on; -1 when there is none.
@@ -93,34 +139,69 @@ __device__ __forceinline__ int tc_next_item(int& round, int n_items) {
   return -1;
 }
 
+// A role's walk over the CTA's items.  Every role walks the same list and keeps the same counts:
+// `it` items so far, `g` key tiles of all items so far (tile g uses K / V stage g % kTcStages in
+// its (g / kTcStages)-th use), and the same two counts for the second slot, which sits out the
+// items that have one head only (its barriers then see no phase).
+struct TcWalk {
+  int round = 0, item = -1;
+  int it = 0, g = 0, it1 = 0, g1 = 0;
+  TcItem w;
+  __device__ __forceinline__ bool first(const PrefillArgs<bf16>& a, int n_items, int pairs, int tiles) {
+    item = tc_next_item(round, n_items);
+    if (item < 0) return false;
+    w = load(a, item, pairs, tiles);
+    return true;
+  }
+  // moves to the CTA's next item; false when there is none
+  __device__ __forceinline__ bool next(const PrefillArgs<bf16>& a, int n_items, int pairs, int tiles) {
+    ++it;
+    g += w.nt;
+    if (w.two) {
+      ++it1;
+      g1 += w.nt;
+    }
+    return first(a, n_items, pairs, tiles);
+  }
+  // Items are numbered longest first (a later tile of a sequence attends to more keys), the kv heads and
+  // pairs of a tile next to each other, so that CTAs that run together share K and V in L2.
+  static __device__ __forceinline__ TcItem load(const PrefillArgs<bf16>& a, int item, int pairs, int tiles) {
+    const int per_tile = a.hkv * pairs;
+    const int t = item / per_tile;
+    return tc_item(a, tiles - 1 - t, item - t * per_tile, pairs);
+  }
+};
+
 __global__ void __launch_bounds__(kTcThreads, 1)
 prefill_attn_tc_kernel(const PrefillArgs<bf16> a, int tiles, int* status) {
-  static_assert(kD == 64, "this kernel is written for head size 64");
+  static_assert(kD == 64 || kD == 128, "this kernel is written for head sizes 64 and 128");
   constexpr float kLog2e = 1.4426950408889634f;
   extern __shared__ unsigned char smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   unsigned char* base = smem_raw + ((1024u - (raw & 1023u)) & 1023u);
-  unsigned char* q_s = base;                             // two buffers
-  unsigned char* k_s = base + 2 * kTcTileBytes;          // two stages
-  unsigned char* v_s = base + 4 * kTcTileBytes;          // two stages
-  unsigned char* p_s = base + 6 * kTcTileBytes;          // two buffers of two 64-key halves
-  PrefillTcShared* sh = reinterpret_cast<PrefillTcShared*>(base + 10 * kTcTileBytes);
+  unsigned char* q_s = base;                                        // one tile per slot
+  unsigned char* k_s = base + 2 * kTcTileBytes;                     // kTcStages tiles
+  unsigned char* v_s = base + (2 + kTcStages) * kTcTileBytes;       // kTcStages tiles
+  PrefillTcShared* sh = reinterpret_cast<PrefillTcShared*>(base + (2 + 2 * kTcStages) * kTcTileBytes);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n_items = tiles * a.hq;
+  const int pairs = (a.hq / a.hkv + 1) / 2;
+  const int n_items = tiles * a.hkv * pairs;
 
   if (threadIdx.x == 0) {
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(&sh->q_full[b], 1);
-      mbar_init(&sh->q_free[b], 1);
-      mbar_init(&sh->k_full[b], 1);
-      mbar_init(&sh->v_full[b], 1);
-      mbar_init(&sh->qk_done[b], 1);
-      mbar_init(&sh->pv_done[b], 1);
-      mbar_init(&sh->s_free[b], 8);       // one arrival per row warp (its lanes meet first)
-      mbar_init(&sh->o_free[b], 8);
-      mbar_init(&sh->p_ready[b], 8);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&sh->q_full[s], 1);
+      mbar_init(&sh->q_free[s], 1);
+      mbar_init(&sh->qk_done[s], 1);
+      mbar_init(&sh->pv_done[s], 1);
+      mbar_init(&sh->p_ready[s], 4);      // one arrival per row warp (its lanes meet first)
+      mbar_init(&sh->o_free[s], 4);
     }
-    for (int qq = 0; qq < 4; ++qq) mbar_init(&sh->pair[qq], 2);
+    for (int b = 0; b < kTcStages; ++b) {
+      mbar_init(&sh->k_full[b], 1);
+      mbar_init(&sh->k_free[b], 1);
+      mbar_init(&sh->v_full[b], 1);
+      mbar_init(&sh->v_free[b], 1);
+    }
     sh->abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -137,63 +218,71 @@ prefill_attn_tc_kernel(const PrefillArgs<bf16> a, int tiles, int* status) {
   pdl_launch();
   pdl_wait();        // q and the newest keys come from the kernels before this one
 
-  // Every role walks the same list of items (blockIdx.x, + gridDim.x, ...) and counts the key tiles of
-  // all its items in one sequence g: tile g uses stage / buffer g & 1 in its ((g >> 1) & 1)-th use, item
-  // number `it` of the CTA uses Q buffer it & 1.  A role reads an item's description one item ahead.
   if (warp == 8 || warp == 9) {
-    // ------------------------------------------------------------------ loaders: warp 8 K (and Q), warp 9 V
+    // ------------------------------------------------------------------ loaders: warp 8 K (and both Q), warp 9 V
     const bool is_v = warp == 9;
     const int ps_shift = __ffs(a.page_size) - 1, ps_mask = a.page_size - 1;
     const size_t head_stride = static_cast<size_t>(a.page_size) * kD;
-    const int c = lane & 7, r4 = lane >> 3;            // chunk of a row, row within a round of four rows
+    constexpr int CPR = kD / 8;                          // 16-byte chunks of a row
+    constexpr int RPI = 32 / CPR;                        // rows that the warp's lanes cover at once
+    const int c = lane % CPR, rr = lane / CPR;           // chunk of a row, row within a round of RPI rows
+    // a row's chunk c lies in half c / 8 at 16-byte position (c % 8) ^ (row % 8) of the row's 128 bytes
+    const uint32_t c_half = static_cast<uint32_t>(c >> 3) * kTcHalfBytes;
+    const int c7 = c & 7;
     const bf16* cache = is_v ? a.vcache : a.kcache;
     const uint32_t stage0 = smem_u32(is_v ? v_s : k_s);
     uint64_t* full = is_v ? sh->v_full : sh->k_full;
-    uint64_t* freed = is_v ? sh->pv_done : sh->qk_done;   // the product that read the stage two tiles back
+    uint64_t* freed = is_v ? sh->v_free : sh->k_free;
     const int rpp = min(a.page_size, kTcKeys);            // rows of a page that lie in a tile
     const int pages = kTcKeys / rpp;                      // pages per tile (at most eight: pages of 16 keys or more)
-    const uint32_t lane_src = static_cast<uint32_t>(r4 * kD + c * 8);
+    const uint32_t lane_src = static_cast<uint32_t>(rr * kD + c * 8);
     // Before the warp blocks on a stage or a Q buffer, what it has copied so far is handed over: the
     // reader of a stage never waits for a tile that waits for that reader.
     bool ok = true;
-    int pending = -1, q_pending = -1;                     // a tile (a Q buffer) copied but not handed over
+    int pending = -1;                                     // a tile copied but not handed over (its stage)
+    int q_pending = 0;                                    // bit s: Q of slot s copied but not handed over
     auto hand_over = [&](bool all) {
       if (all) cp_async_wait<0>(); else cp_async_wait<1>();
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
       if (lane == 0) {
-        if (q_pending >= 0) mbar_arrive(&sh->q_full[q_pending]);
-        if (pending >= 0) mbar_arrive(&full[pending & 1]);
+        if (q_pending & 1) mbar_arrive(&sh->q_full[0]);
+        if (q_pending & 2) mbar_arrive(&sh->q_full[1]);
+        if (pending >= 0) mbar_arrive(&full[pending]);
       }
-      q_pending = -1;
+      q_pending = 0;
       pending = -1;
     };
-    int g = 0, it = 0, round = 0;
-    for (int item = tc_next_item(round, n_items); item >= 0 && ok; item = tc_next_item(round, n_items), ++it) {
-      const TcItem w = tc_item(a, item, tiles);
+    TcWalk wk;
+    for (bool more = wk.first(a, n_items, pairs, tiles); more && ok; more = wk.next(a, n_items, pairs, tiles)) {
+      const TcItem& w = wk.w;
       const int32_t* bt = a.block_table + static_cast<size_t>(w.seq) * a.max_blocks;
       if (!is_v) {
-        const int qb = it & 1;
-        if (!mbar_try_wait(&sh->q_free[qb], ((it >> 1) & 1) ^ 1)) {
-          hand_over(true);
-          ok = mbar_wait(&sh->q_free[qb], ((it >> 1) & 1) ^ 1, &sh->abort);
+        for (int s = 0; s < (w.two ? 2 : 1) && ok; ++s) {
+          const int n = s == 0 ? wk.it : wk.it1;          // the slot's items so far
+          if (!mbar_try_wait(&sh->q_free[s], (n & 1) ^ 1)) {
+            hand_over(true);
+            ok = mbar_wait(&sh->q_free[s], (n & 1) ^ 1, &sh->abort);
+          }
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          if (pending >= 0) hand_over(true);              // (keeps the groups of Q and of a tile apart)
+          const uint32_t q_u = smem_u32(q_s) + s * kTcTileBytes;
+          for (int j = 0; j < kTcRows / RPI; ++j) {
+            const int r = j * RPI + rr;
+            const bool live = r < w.rows;
+            const bf16* src = a.q + static_cast<size_t>(w.tok0 + (live ? r : 0)) * a.q_stride + (w.head0 + s) * kD + c * 8;
+            cp_async16_s(q_u + c_half + r * 128 + ((c7 ^ (r & 7)) << 4), src, live);
+          }
+          cp_async_commit();
+          q_pending |= 1 << s;
         }
-        ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-        if (pending >= 0) hand_over(true);                // (keeps the groups of Q and of a tile apart)
-        const uint32_t q_u = smem_u32(q_s) + qb * kTcTileBytes;
-        for (int j = 0; j < kTcRows / 4; ++j) {
-          const int r = j * 4 + r4;
-          const bool live = r < w.rows;
-          const bf16* src = a.q + static_cast<size_t>(w.tok0 + (live ? r : 0)) * a.q_stride + w.head * kD + c * 8;
-          cp_async16_s(q_u + r * 128 + ((c ^ (r & 7)) << 4), src, live);
-        }
-        cp_async_commit();
-        q_pending = qb;
       }
-      for (int i = 0; i < w.nt; ++i, ++g) {
-        const int b = g & 1;
-        const uint32_t par = (((g >> 1) & 1) ^ 1);        // a fresh barrier passes a wait on parity 1
+      for (int i = 0; i < w.nt; ++i) {
+        const int g = wk.g + i;
+        const int b = g % kTcStages;
+        const uint32_t par = ((g / kTcStages) & 1) ^ 1;   // a fresh barrier passes a wait on parity 1
         const int k0 = w.k_begin + i * kTcKeys;
         // the tile's pages: lane l < pages holds the id of page l, 0 for one without a live key
         int my_page = 0;
@@ -208,7 +297,7 @@ prefill_attn_tc_kernel(const PrefillArgs<bf16> a, int tiles, int* status) {
         }
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-        const uint32_t dst = stage0 + b * kTcTileBytes;
+        const uint32_t dst = stage0 + b * kTcTileBytes + c_half;
         const bool whole = k0 >= w.lo0 && k0 + kTcKeys <= w.k_end;    // every key of the tile is live
         const int in_page = k0 & ps_mask;                              // the tile's first row within its page (pages > 128 keys)
         for (int pg = 0; pg < pages; ++pg) {
@@ -217,21 +306,21 @@ prefill_attn_tc_kernel(const PrefillArgs<bf16> a, int tiles, int* status) {
           const int row0 = pg * rpp;
           if (whole) {
 #pragma unroll 4
-            for (int jj = 0; jj < rpp; jj += 4) {
-              const int key = row0 + jj + r4;
-              cp_async16_s(dst + key * 128 + ((c ^ (key & 7)) << 4), src + jj * kD);
+            for (int jj = 0; jj < rpp; jj += RPI) {
+              const int key = row0 + jj + rr;
+              cp_async16_s(dst + key * 128 + ((c7 ^ (key & 7)) << 4), src + jj * kD);
             }
           } else {
 #pragma unroll 4
-            for (int jj = 0; jj < rpp; jj += 4) {
-              const int key = row0 + jj + r4, ka = k0 + key;
-              cp_async16_s(dst + key * 128 + ((c ^ (key & 7)) << 4), src + jj * kD, ka < w.k_end && ka >= w.lo0);
+            for (int jj = 0; jj < rpp; jj += RPI) {
+              const int key = row0 + jj + rr, ka = k0 + key;
+              cp_async16_s(dst + key * 128 + ((c7 ^ (key & 7)) << 4), src + jj * kD, ka < w.k_end && ka >= w.lo0);
             }
           }
         }
         cp_async_commit();
-        if (pending >= 0 || q_pending >= 0) hand_over(false);   // the tile before (and Q): landed by now, or nearly
-        pending = g;
+        if (pending >= 0 || q_pending) hand_over(false);   // the tile before (and Q): landed by now, or nearly
+        pending = b;
       }
     }
     hand_over(true);
@@ -239,230 +328,193 @@ prefill_attn_tc_kernel(const PrefillArgs<bf16> a, int tiles, int* status) {
     // ------------------------------------------------------------------ MMA issue
     if (lane == 0 && blockIdx.x < n_items) {
       const uint32_t idesc_qk = umma_idesc(kTcRows, kTcKeys);
-      const uint32_t idesc_pv = umma_idesc(kTcRows, kD) | (1u << 16);          // B (V) is MN-major
-      const uint32_t q_u = smem_u32(q_s), k_u = smem_u32(k_s), v_u = smem_u32(v_s), p_u = smem_u32(p_s);
-      struct Tile { int item, it, i, nt, g; };                                  // a key tile of an item of this CTA
+      const uint32_t idesc_pv = umma_idesc(kTcRows, 64) | (1u << 16);          // B (V) is MN-major; 64 columns of O at a time
+      const uint32_t q_u = smem_u32(q_s), k_u = smem_u32(k_s), v_u = smem_u32(v_s);
+      // a key tile of an item of this CTA, with the counts of the walk at it
+      struct Tile { int it, it1, g, g1, i, nt; bool two; };
       bool ok = true;
-      auto issue_qk = [&](const Tile& t) {
-        const int b = t.g & 1;
-        if (t.i == 0) ok = ok && mbar_wait(&sh->q_full[t.it & 1], (t.it >> 1) & 1, &sh->abort);
-        ok = ok && mbar_wait(&sh->k_full[b], (t.g >> 1) & 1, &sh->abort) &&
-             mbar_wait(&sh->s_free[b], ((t.g >> 1) & 1) ^ 1, &sh->abort);
+      auto issue_qk = [&](const Tile& t, int s) {
+        const int b = t.g % kTcStages;
+        const int n_it = s == 0 ? t.it : t.it1, n_g = s == 0 ? t.g : t.g1;     // the slot's own counts
+        if (t.i == 0) ok = ok && mbar_wait(&sh->q_full[s], n_it & 1, &sh->abort);
+        if (s == 0) ok = ok && mbar_wait(&sh->k_full[b], (t.g / kTcStages) & 1, &sh->abort);
+        // S lies where the slot's P of the tile before was: its O product must be done
+        if (n_g > 0) ok = ok && mbar_wait(&sh->pv_done[s], (n_g - 1) & 1, &sh->abort);
         if (!ok) return;
         tc_fence_after();
 #pragma unroll
-        for (int k = 0; k < kD / 16; ++k)
-          umma_bf16(tmem + b * kTcKeys, umma_desc(q_u + (t.it & 1) * kTcTileBytes + k * 32),
-                    umma_desc(k_u + b * kTcTileBytes + k * 32), idesc_qk, k != 0);
-        umma_commit(&sh->qk_done[b]);
-        if (t.i == t.nt - 1) umma_commit(&sh->q_free[t.it & 1]);             // the item's Q has been read
+        for (int k = 0; k < kD / 16; ++k) {
+          const uint32_t off = (k >> 2) * kTcHalfBytes + (k & 3) * 32;
+          umma_bf16(tmem + s * kTcKeys, umma_desc(q_u + s * kTcTileBytes + off), umma_desc(k_u + b * kTcTileBytes + off),
+                    idesc_qk, k != 0);
+        }
+        umma_commit(&sh->qk_done[s]);
+        if (s == 1 || !t.two) umma_commit(&sh->k_free[b]);                     // both slots have read the K tile
+        if (t.i == t.nt - 1) umma_commit(&sh->q_free[s]);                      // the item's Q has been read
       };
-      auto issue_pv = [&](const Tile& t) {
-        const int b = t.g & 1;
-        ok = ok && mbar_wait(&sh->v_full[b], (t.g >> 1) & 1, &sh->abort) &&
-             mbar_wait(&sh->p_ready[b], (t.g >> 1) & 1, &sh->abort) &&
-             mbar_wait(&sh->o_free[b], ((t.g >> 1) & 1) ^ 1, &sh->abort);
+      auto issue_pv = [&](const Tile& t, int s) {
+        const int b = t.g % kTcStages;
+        const int n_it = s == 0 ? t.it : t.it1, n_g = s == 0 ? t.g : t.g1;
+        ok = ok && mbar_wait(&sh->p_ready[s], n_g & 1, &sh->abort);
+        if (s == 0) ok = ok && mbar_wait(&sh->v_full[b], (t.g / kTcStages) & 1, &sh->abort);
+        // the first product of an item overwrites O: the rows of the item before must have read theirs
+        if (t.i == 0) ok = ok && mbar_wait(&sh->o_free[s], (n_it & 1) ^ 1, &sh->abort);
         if (!ok) return;
         tc_fence_after();
 #pragma unroll
         for (int k = 0; k < kTcKeys / 16; ++k)
-          umma_bf16(tmem + 2 * kTcKeys + b * kD,
-                    umma_desc(p_u + b * 2 * kTcTileBytes + (k >> 2) * kTcTileBytes + (k & 3) * 32),
-                    umma_desc_mn(v_u + b * kTcTileBytes + k * 2048), idesc_pv, k != 0);
-        umma_commit(&sh->pv_done[b]);
+#pragma unroll
+          for (int h = 0; h < kTcHalves; ++h)
+            umma_bf16_ts(tmem + kTcColO + s * kD + h * 64, tmem + s * kTcKeys + k * 8,
+                         umma_desc_mn(v_u + b * kTcTileBytes + h * kTcHalfBytes + k * 2048), idesc_pv,
+                         (t.i != 0 || k != 0) ? 1u : 0u);
+        umma_commit(&sh->pv_done[s]);
+        if (s == 1 || !t.two) umma_commit(&sh->v_free[b]);                     // both slots have read the V tile
       };
-      // the S product of the next tile (of this item or the next) is issued before the O product of this one
-      int round = 0;
-      Tile cur;
-      cur.item = tc_next_item(round, n_items);
-      cur.it = 0;
-      cur.i = 0;
-      cur.g = 0;
-      cur.nt = tc_item(a, cur.item, tiles).nt;
-      issue_qk(cur);
-      int item_after = -1, nt_after = 0;                  // the item after cur's and its key tiles (read at cur's start)
+      TcWalk wk;
+      wk.first(a, n_items, pairs, tiles);
+      Tile cur = {0, 0, 0, 0, 0, wk.w.nt, wk.w.two};
+      issue_qk(cur, 0);
+      if (cur.two) issue_qk(cur, 1);
       while (ok) {
-        if (cur.i == 0) {
-          item_after = tc_next_item(round, n_items);
-          nt_after = item_after >= 0 ? tc_item(a, item_after, tiles).nt : 0;
-        }
+        // the tile after cur: of this item, or the first of the CTA's next item
         Tile nxt = cur;
+        bool more = true;
         ++nxt.g;
+        if (cur.two) ++nxt.g1;
         if (++nxt.i == cur.nt) {
-          nxt.item = item_after;
-          ++nxt.it;
-          nxt.i = 0;
-          nxt.nt = nt_after;
+          more = wk.next(a, n_items, pairs, tiles);
+          nxt = {wk.it, wk.it1, wk.g, wk.g1, 0, more ? wk.w.nt : 0, more && wk.w.two};
         }
-        const bool more = nxt.item >= 0;
-        if (more) issue_qk(nxt);
-        issue_pv(cur);
+        issue_pv(cur, 0);
+        if (more) issue_qk(nxt, 0);
+        if (cur.two) issue_pv(cur, 1);
+        if (more && nxt.two) issue_qk(nxt, 1);
         if (!more) break;
         cur = nxt;
       }
     }
   } else {
-    // ------------------------------------------------------------------ the row threads, two to a row
-    // Warp w < 8: rows 32 (w % 4) .. + 32 (the TMEM lanes a warp may touch), keys 64 (w / 4) .. + 64 of
-    // every S tile and columns 32 (w / 4) .. + 32 of O.  Both threads of a row take the maximum over the
-    // whole row; each keeps the denominator of its own keys, and the two are added at the end (one
-    // exchange through shared memory, an mbarrier per quarter of rows, 2 arrivals).
-    const int q = warp & 3, h = warp >> 2;
+    // ------------------------------------------------------------------ the row threads, one to a row
+    // Warp w < 8: slot w / 4, rows 32 (w % 4) .. + 32 of the slot's tile (the TMEM lanes a warp may touch).
+    const int s = warp >> 2, q = warp & 3;
     const int r = q * 32 + lane;                         // row of the tile = TMEM lane
     const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
+    const uint32_t s_addr = tmem + lane_addr + s * kTcKeys;           // S, and P over its first 64 columns
+    const uint32_t o_addr = tmem + lane_addr + kTcColO + s * kD;
     const float sc = a.scale * kLog2e;
-    const uint32_t p_u = smem_u32(p_s);
     bool ok = true;
-    int xphase = 0;                                       // exchanges done so far (parity of the pair's mbarrier)
-    auto exchange = [&](float mine) -> float {            // gives the partner's value
-      sh->xchg[xphase & 1][h][r] = mine;
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&sh->pair[q]);           // (release: the values are visible to who sees the phase)
-      ok = ok && mbar_wait(&sh->pair[q], xphase & 1, &sh->abort);
-      const float other = sh->xchg[xphase & 1][h ^ 1][r];
-      ++xphase;
-      return other;
-    };
-    float acc[32];
-    auto add_o = [&](int g, float alpha) {                // acc = acc * alpha + O_tile(g), this thread's 32 columns
-      const int b = g & 1;
-      ok = ok && mbar_wait(&sh->pv_done[b], (g >> 1) & 1, &sh->abort);
-      if (!ok) return;
-      tc_fence_after();
-      float o[32];
-      tmem_ld32(tmem + lane_addr + 2 * kTcKeys + b * kD + h * 32, o);
-#pragma unroll
-      for (int d = 0; d < 32; ++d) acc[d] = fmaf(acc[d], alpha, o[d]);
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&sh->o_free[b]);
-    };
-    int g = 0, round = 0;
-    int item = tc_next_item(round, n_items);
-    TcItem w;
-    if (item >= 0) w = tc_item(a, item, tiles);
-    for (; item >= 0 && ok;) {
-      const int item_next = tc_next_item(round, n_items);
-      TcItem w_next = w;
-      if (item_next >= 0) w_next = tc_item(a, item_next, tiles);   // on its way during this item
+    TcWalk wk;
+    for (bool more = wk.first(a, n_items, pairs, tiles); more && ok; more = wk.next(a, n_items, pairs, tiles)) {
+      const TcItem& w = wk.w;
+      if (s == 1 && !w.two) continue;                     // this slot sits the item out
+      const int g_base = s == 0 ? wk.g : wk.g1;           // the slot's key tiles so far
       const int rows = w.rows, pos0 = w.pos0;
       const int pos_r = pos0 + r;
       const int win_r = (a.window > 0 && pos_r + 1 > a.window) ? pos_r + 1 - a.window : 0;
-#pragma unroll
-      for (int d = 0; d < 32; ++d) acc[d] = 0.f;
-      float m = -INFINITY, l = 0.f, alpha_prev = 0.f;
-      for (int i = 0; i < w.nt && ok; ++i, ++g) {
-        const int b = g & 1;
+      float m_ref = -INFINITY, l = 0.f;                   // the maximum that P is scaled by (log2 units), the denominator
+      for (int i = 0; i < w.nt && ok; ++i) {
+        const int n = g_base + i;
         const int t0 = w.k_begin + i * kTcKeys;
-        const int k0 = t0 + h * 64;                       // this thread's first key of the tile
-        ok = mbar_wait(&sh->qk_done[b], (g >> 1) & 1, &sh->abort);
+        ok = mbar_wait(&sh->qk_done[s], n & 1, &sh->abort);
+        ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
+        uint32_t sr[kTcKeys];
+#pragma unroll
+        for (int cc = 0; cc < kTcKeys / 16; ++cc) tmem_ld16_issue(s_addr + cc * 16, sr + cc * 16);
+        tmem_wait_ld();
         // only tiles that reach past the first row's position, before the last row's window or past the
         // tile's rows need the masks (the same for the whole CTA)
         const bool masked = (t0 + kTcKeys - 1 > pos0) || (a.window > 0 && t0 < pos0 + kTcRows - a.window) || (rows < kTcRows);
-        // the row's maximum over all 128 keys: the other thread's half is read too (and dropped), which is
-        // cheaper than an exchange between the two threads
-        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-        {
-          const int ko = t0 + (h ^ 1) * 64;
-#pragma unroll
-          for (int c0 = 0; c0 < 64; c0 += 32) {
-            float o[32];
-            tmem_ld32(tmem + lane_addr + b * kTcKeys + (h ^ 1) * 64 + c0, o);
-            if (masked) {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) {
-                const int key = ko + c0 + j;
-                if (!(key <= pos_r && key >= win_r && r < rows)) o[j] = -INFINITY;
-              }
-            }
-#pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-              mx0 = fmaxf(mx0, o[j]);
-              mx1 = fmaxf(mx1, o[j + 1]);
-              mx2 = fmaxf(mx2, o[j + 2]);
-              mx3 = fmaxf(mx3, o[j + 3]);
-            }
-          }
-        }
-        float s[64];
-        tmem_ld32(tmem + lane_addr + b * kTcKeys + h * 64, s);
-        tmem_ld32(tmem + lane_addr + b * kTcKeys + h * 64 + 32, s + 32);
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&sh->s_free[b]);         // S of this tile has been read
         if (masked) {
 #pragma unroll
-          for (int j = 0; j < 64; ++j) {
-            const int key = k0 + j;
-            if (!(key <= pos_r && key >= win_r && r < rows)) s[j] = -INFINITY;
+          for (int j = 0; j < kTcKeys; ++j) {
+            const int key = t0 + j;
+            if (!(key <= pos_r && key >= win_r && r < rows)) sr[j] = 0xff800000u;      // -inf
           }
         }
+        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-        for (int j = 0; j < 64; j += 4) {
-          mx0 = fmaxf(mx0, s[j]);
-          mx1 = fmaxf(mx1, s[j + 1]);
-          mx2 = fmaxf(mx2, s[j + 2]);
-          mx3 = fmaxf(mx3, s[j + 3]);
+        for (int j = 0; j < kTcKeys; j += 4) {
+          mx0 = fmaxf(mx0, __uint_as_float(sr[j]));
+          mx1 = fmaxf(mx1, __uint_as_float(sr[j + 1]));
+          mx2 = fmaxf(mx2, __uint_as_float(sr[j + 2]));
+          mx3 = fmaxf(mx3, __uint_as_float(sr[j + 3]));
         }
-        const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-        const float m_new = fmaxf(m, mx * sc);               // in units of log2 of the scaled scores
-        const float m_use = m_new == -INFINITY ? 0.f : m_new;  // a row without a live key so far
-        const float alpha = ex2_approx(m - m_use);           // 2^(-inf) = 0 the first time
+        const float m_new = fmaxf(m_ref, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * sc);   // in units of log2 of the scaled scores
+        if (i == 0) {
+          m_ref = m_new;
+        } else if (__any_sync(0xffffffffu, m_new > m_ref + kTcGrow)) {
+          // the reference moves for the whole warp: the denominator and the row of O follow.  (O is at
+          // rest: the product that made S waited for the O product of the tile before.)
+          const float alpha = m_new == m_ref ? 1.f : ex2_approx(m_ref - m_new);            // 2^(-inf) = 0
+          l *= alpha;
+          m_ref = m_new;
+#pragma unroll
+          for (int c0 = 0; c0 < kD; c0 += 32) {
+            uint32_t o[32];
+            tmem_ld16_issue(o_addr + c0, o);
+            tmem_ld16_issue(o_addr + c0 + 16, o + 16);
+            tmem_wait_ld();
+#pragma unroll
+            for (int d = 0; d < 32; ++d) o[d] = __float_as_uint(__uint_as_float(o[d]) * alpha);
+            tmem_st16(o_addr + c0, o);
+            tmem_st16(o_addr + c0 + 16, o + 16);
+          }
+        }
+        const float m_use = m_ref == -INFINITY ? 0.f : m_ref;  // a row without a live key so far
         float sm0 = 0.f, sm1 = 0.f, sm2 = 0.f, sm3 = 0.f;
 #pragma unroll
-        for (int j = 0; j < 64; j += 4) {
-          s[j] = ex2_approx(fmaf(s[j], sc, -m_use));
-          s[j + 1] = ex2_approx(fmaf(s[j + 1], sc, -m_use));
-          s[j + 2] = ex2_approx(fmaf(s[j + 2], sc, -m_use));
-          s[j + 3] = ex2_approx(fmaf(s[j + 3], sc, -m_use));
-          sm0 += s[j];
-          sm1 += s[j + 1];
-          sm2 += s[j + 2];
-          sm3 += s[j + 3];
+        for (int j = 0; j < kTcKeys; j += 4) {
+          const float p0 = ex2_approx(fmaf(__uint_as_float(sr[j]), sc, -m_use));
+          const float p1 = ex2_approx(fmaf(__uint_as_float(sr[j + 1]), sc, -m_use));
+          const float p2 = ex2_approx(fmaf(__uint_as_float(sr[j + 2]), sc, -m_use));
+          const float p3 = ex2_approx(fmaf(__uint_as_float(sr[j + 3]), sc, -m_use));
+          sm0 += p0;
+          sm1 += p1;
+          sm2 += p2;
+          sm3 += p3;
+          const __nv_bfloat162 lo = __floats2bfloat162_rn(p0, p1), hi = __floats2bfloat162_rn(p2, p3);
+          sr[j >> 1] = *reinterpret_cast<const uint32_t*>(&lo);       // (columns j / 2: behind the ones still to be read)
+          sr[(j >> 1) + 1] = *reinterpret_cast<const uint32_t*>(&hi);
         }
-        l = l * alpha + ((sm0 + sm1) + (sm2 + sm3));
-        m = m_new;
-        // ---- the P buffer must be free: the O product of two tiles back has read it
-        ok = mbar_wait(&sh->pv_done[b], ((g >> 1) & 1) ^ 1, &sh->abort);
-        if (!ok) break;
-        // this thread's 64 keys are the row's eight 16-byte chunks of the 64-key half h
-        const uint32_t prow = p_u + b * 2 * kTcTileBytes + h * kTcTileBytes + r * 128;
+        l += (sm0 + sm1) + (sm2 + sm3);
+        // P: two keys per 32-bit column, over the first 64 columns of S
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          uint32_t wd[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const __nv_bfloat162 hh = __floats2bfloat162_rn(s[c * 8 + 2 * e], s[c * 8 + 2 * e + 1]);
-            wd[e] = *reinterpret_cast<const uint32_t*>(&hh);
-          }
-          asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(prow + ((c ^ (r & 7)) << 4)), "r"(wd[0]),
-                       "r"(wd[1]), "r"(wd[2]), "r"(wd[3])
-                       : "memory");
-        }
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P is read by the tensor core
+        for (int cc = 0; cc < kTcKeys / 32; ++cc) tmem_st16(s_addr + cc * 16, sr + cc * 16);
+        tmem_wait_st();
+        tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&sh->p_ready[b]);
-        // ---- while the O product of this tile runs: add the one of the tile before
-        if (i > 0) add_o(g - 1, alpha_prev);
-        alpha_prev = alpha;
+        if (lane == 0) mbar_arrive(&sh->p_ready[s]);
       }
-      if (ok && w.nt > 0) add_o(g - 1, alpha_prev);
-      const float l_all = l + exchange(l);
-      if (ok && r < rows) {
-        const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
-        bf16* dst = a.out + static_cast<size_t>(w.tok0 + r) * a.out_stride + w.head * kD + h * 32;
+      if (!ok) break;
+      // ---- the item's rows: O / denominator, once its last product is done
+      ok = mbar_wait(&sh->pv_done[s], (g_base + w.nt - 1) & 1, &sh->abort);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      bf16* dst = a.out + static_cast<size_t>(w.tok0 + (r < rows ? r : 0)) * a.out_stride + (w.head0 + s) * kD;
 #pragma unroll
-        for (int d = 0; d < 32; d += 8) {
-          float v[8];
+      for (int c0 = 0; c0 < kD; c0 += 32) {
+        uint32_t o[32];
+        tmem_ld16_issue(o_addr + c0, o);
+        tmem_ld16_issue(o_addr + c0 + 16, o + 16);
+        tmem_wait_ld();
+        if (r < rows) {
 #pragma unroll
-          for (int e = 0; e < 8; ++e) v[e] = acc[d + e] * inv;
-          store16(dst + d, v);
+          for (int d = 0; d < 32; d += 8) {
+            float v[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(o[d + e]) * inv;
+            store16(dst + c0 + d, v);
+          }
         }
       }
-      w = w_next;
-      item = item_next;
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sh->o_free[s]);
     }
   }
   tc_fence_before();

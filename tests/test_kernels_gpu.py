@@ -250,19 +250,39 @@ def test_attention_prefill_tensor_core_kernel(Hq, Hkv, D, page_size):
                       prefill_impl=2)
 
 
-@pytest.mark.parametrize("Hq,Hkv", [(4, 2), (32, 8), (5, 5), (3, 1)])
+@pytest.mark.parametrize("Hq,Hkv,D", [(4, 2, 64), (32, 8, 64), (5, 5, 64), (3, 1, 64), (24, 8, 128), (3, 1, 128),
+                                      (4, 4, 128), (16, 1, 64)])
 @pytest.mark.parametrize("page_size", [16, 32, 64])
-def test_attention_prefill_tcgen05_kernel(Hq, Hkv, page_size):
-    """impl 3 insists on the tcgen05 kernel (head size 64): portions that start and end anywhere relative
-    to its 128-row and 128-key tiles, pasts of every alignment, several key tiles per query tile (both S
-    and O buffers and both stages in use again), every page size, and windows."""
-    D = 64
+def test_attention_prefill_tcgen05_kernel(Hq, Hkv, D, page_size):
+    """impl 3 insists on the tcgen05 kernel (head sizes 64 and 128): portions that start and end anywhere
+    relative to its 128-row and 128-key tiles, pasts of every alignment, many key tiles per query tile
+    (every stage and the S, P and O columns of tensor memory in use again and again, a row's reference
+    maximum moved and O rescaled on the way), groups of one, two, three and more heads (pairs of heads
+    share a CTA; the last head of an odd group has one alone), every page size, and windows."""
     run_attention("bfloat16", Hq, Hkv, D, [0, 0, 0, 0], [2, 127, 128, 129], page_size=page_size, seed=41, prefill_impl=3)
     run_attention("bfloat16", Hq, Hkv, D, [0, 1, 127, 128, 500], [600, 257, 2, 130, 131], page_size=page_size, seed=42,
                   prefill_impl=3)
     for window in (1, 20, 128, 200, 600):
         run_attention("bfloat16", Hq, Hkv, D, [0, 90, 590], [300, 35, 130], page_size=page_size, window=window, seed=43,
                       prefill_impl=3)
+    assert int(kernels.tc_status(torch.device(DEV)).item()) == 0
+
+
+def test_attention_prefill_tcgen05_kernel_long_rows_with_a_growing_maximum():
+    """2,100 keys per row, with queries and keys made so that a row's largest score keeps growing with
+    the key's position (every later tile raises the maximum by far more than 2^8): the reference maximum
+    moves and O is rescaled in tensor memory at nearly every tile; then the opposite, the largest score
+    at the row's first key.  More items than SMs at Hq = 32, so CTAs take several items each."""
+    def growing(sign):
+        def sharp(seqs, cos, sin):
+            for x in seqs:
+                T = x.shape[0]
+                ramp = torch.arange(T, dtype=torch.float32)[:, None] * (sign * 0.02)
+                x[:, 32 * 64:(32 + 8) * 64] += ramp          # the keys drift along one direction ...
+                x[:, :32 * 64] += 1.0                        # ... that every query has a share of
+        return sharp
+    for sign in (1.0, -1.0):
+        run_attention("bfloat16", 32, 8, 64, [0, 1000], [2100, 700], seed=45, sharp=growing(sign), prefill_impl=3)
     assert int(kernels.tc_status(torch.device(DEV)).item()) == 0
 
 
