@@ -20,13 +20,17 @@
 // result is the same sum: every term of a row carries the same factor, which the division by
 // the denominator takes out.
 // While the rows of one slot are in their softmax, the tensor core works on the other slot's
-// products: per key tile the MMA thread issues  O0 += P0 V, S0' = Q0 K', O1 += P1 V, S1' = Q1 K'.
-// Tensor memory: S0 at column 0, S1 at 128 (P over the first 64 columns of each), O0 at 256,
-// O1 at 256 + head size.
+// products.  Tensor memory (512 columns): S0 at column 0, S1 at 128, O0 at 256, O1 at 256 + head
+// size.  At head size 64 that leaves 128 columns, and P has columns of its own (P0 at 384, P1 at
+// 448): the S product of the next key tile is issued as soon as the rows have READ this tile's S
+// into registers, so it is done before they have finished with this tile, and the rows never wait
+// for the tensor core.  At head size 128 the columns are all taken: P lies over the first 64
+// columns of its S, and the next S product has to wait for the O product that reads P.
 // Warp roles: warps 0-3 rows of slot 0, warps 4-7 rows of slot 1 (warp w owns TMEM lanes
 // 32 (w % 4) ..), warp 8 brings both Q tiles once per item and the K tiles, warp 9 the V tiles,
 // from the paged cache with 16-byte cp.async copies (zero-filled outside the live keys), lane 0
-// of warp 10 issues the MMAs.  Everything is handed over through mbarriers; every wait is
+// of warp 10 issues the MMAs of slot 0 and lane 0 of warp 11 those of slot 1 (a slot's products
+// never wait for the other slot's rows).  Everything is handed over through mbarriers; every wait is
 // bounded (kSpinLimit polls), after which the CTA raises an abort flag, all roles leave their
 // loops, the copies in flight are waited for, TMEM is freed and bit 2 of *status is set.
 #pragma once
@@ -36,13 +40,15 @@
 namespace rl {
 
 constexpr int kTcRows = 128, kTcKeys = 128;
-constexpr int kTcThreads = 352;                        // 8 row warps, two loaders, the MMA warp
+constexpr int kTcThreads = 384;                        // 8 row warps, two loaders, two MMA warps
 constexpr int kTcHalves = kD / 64;                      // a head's columns in halves of 64 (128 bytes)
 constexpr int kTcHalfBytes = 128 * 128;                 // 128 rows x 64 bfloat16, 128-byte swizzled
 constexpr int kTcTileBytes = kTcHalves * kTcHalfBytes;  // a Q, K or V tile
 constexpr int kTcStages = kD == 64 ? 3 : 2;             // K and V stages
 constexpr int kTcTmemCols = 512;
 constexpr int kTcColO = 256;                            // O of slot s at kTcColO + s * kD
+constexpr bool kTcOwnP = kD == 64;                      // P has tensor-memory columns of its own (else: over S)
+constexpr int kTcColP = 384;                            // with columns of its own: P of slot s at kTcColP + s * 64
 constexpr float kTcGrow = 8.f;                          // log2 of the growth of a row's maximum that moves the reference
 
 struct PrefillTcShared {
@@ -51,6 +57,8 @@ struct PrefillTcShared {
   uint64_t v_full[kTcStages], v_free[kTcStages];  // loader's arrival / the tile's last O product is done
   uint64_t qk_done[2], pv_done[2];                // per slot, MMA commits: S of the tile is ready / its O product is done
   uint64_t p_ready[2];                            // per slot: its four row warps have written P
+  uint64_t s_free[2];                             // per slot: its four row warps have read S (used if P has its own columns)
+  uint64_t exp_done[2];                           // per slot: its four row warps have done a tile's exponentials
   uint64_t o_free[2];                             // per slot: its four row warps have read the item's O
   uint32_t tmem_base;
   volatile int abort;
@@ -116,6 +124,13 @@ __device__ __forceinline__ void tmem_ld16_issue(uint32_t taddr, uint32_t* r) {
         "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
       : "r"(taddr));
 }
+// 64 consecutive 32-bit columns of this thread's TMEM lane in one instruction (no wait).
+__device__ __forceinline__ void tmem_ld64_issue(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x64.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, %48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]), "=r"(r[32]), "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]), "=r"(r[40]), "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]), "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]), "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63])
+      : "r"(taddr));
+}
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
@@ -125,6 +140,31 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
 }
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// Two floats in one 64-bit register and the packed arithmetic on them (one instruction for two lanes).
+__device__ __forceinline__ uint64_t f32x2(float lo, float hi) {
+  uint64_t v;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "f"(lo), "f"(hi));
+  return v;
+}
+__device__ __forceinline__ void f32x2_split(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
 
 // The items of a CTA: in round k the CTAs take items k G .. k G + G - 1 (G CTAs), in odd rounds in
 // reverse order, so that the CTA with the longest item of one round has the shortest of the next.
@@ -194,13 +234,15 @@ prefill_attn_tc_kernel(const PrefillArgs<bf16> a, int tiles, int* status) {
       mbar_init(&sh->qk_done[s], 1);
       mbar_init(&sh->pv_done[s], 1);
       mbar_init(&sh->p_ready[s], 4);      // one arrival per row warp (its lanes meet first)
+      mbar_init(&sh->s_free[s], 4);
+      mbar_init(&sh->exp_done[s], 4);
       mbar_init(&sh->o_free[s], 4);
     }
     for (int b = 0; b < kTcStages; ++b) {
       mbar_init(&sh->k_full[b], 1);
-      mbar_init(&sh->k_free[b], 1);
+      mbar_init(&sh->k_free[b], 2);       // one commit per slot (a lone slot commits twice)
       mbar_init(&sh->v_full[b], 1);
-      mbar_init(&sh->v_free[b], 1);
+      mbar_init(&sh->v_free[b], 2);
     }
     sh->abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -324,74 +366,94 @@ prefill_attn_tc_kernel(const PrefillArgs<bf16> a, int tiles, int* status) {
       }
     }
     hand_over(true);
-  } else if (warp == 10) {
-    // ------------------------------------------------------------------ MMA issue
+  } else if (warp >= 10) {
+    // ------------------------------------------------------------------ MMA issue: lane 0 of warp 10 for slot 0, of warp 11 for slot 1
+    // Each slot has an issuing thread of its own, so that neither slot's products ever wait for the
+    // other slot's rows.  With columns of its own for P a slot's products go  S(0), S(1), O += P(0) V,
+    // S(2), O += P(1) V, ...: the S product runs one key tile ahead of the rows; with P over S:
+    // S(0), O += P(0) V, S(1), O += P(1) V, ...
+    const int s = warp - 10;
     if (lane == 0 && blockIdx.x < n_items) {
       const uint32_t idesc_qk = umma_idesc(kTcRows, kTcKeys);
       const uint32_t idesc_pv = umma_idesc(kTcRows, 64) | (1u << 16);          // B (V) is MN-major; 64 columns of O at a time
-      const uint32_t q_u = smem_u32(q_s), k_u = smem_u32(k_s), v_u = smem_u32(v_s);
-      // a key tile of an item of this CTA, with the counts of the walk at it
-      struct Tile { int it, it1, g, g1, i, nt; bool two; };
+      const uint32_t q_u = smem_u32(q_s) + s * kTcTileBytes, k_u = smem_u32(k_s), v_u = smem_u32(v_s);
+      const uint32_t s_col = tmem + s * kTcKeys, o_col = tmem + kTcColO + s * kD;
+      const uint32_t p_col = kTcOwnP ? tmem + kTcColP + s * 64 : s_col;
+      // a key tile of an item of this slot: g counts the CTA's key tiles (its K / V stage), n and it the
+      // slot's own key tiles and items (the parities of its barriers)
+      struct Tile { int g, n, it, i, nt; bool two; };
       bool ok = true;
-      auto issue_qk = [&](const Tile& t, int s) {
+      auto issue_qk = [&](const Tile& t) {
         const int b = t.g % kTcStages;
-        const int n_it = s == 0 ? t.it : t.it1, n_g = s == 0 ? t.g : t.g1;     // the slot's own counts
-        if (t.i == 0) ok = ok && mbar_wait(&sh->q_full[s], n_it & 1, &sh->abort);
-        if (s == 0) ok = ok && mbar_wait(&sh->k_full[b], (t.g / kTcStages) & 1, &sh->abort);
-        // S lies where the slot's P of the tile before was: its O product must be done
-        if (n_g > 0) ok = ok && mbar_wait(&sh->pv_done[s], (n_g - 1) & 1, &sh->abort);
+        if (t.i == 0) ok = ok && mbar_wait(&sh->q_full[s], t.it & 1, &sh->abort);
+        ok = ok && mbar_wait(&sh->k_full[b], (t.g / kTcStages) & 1, &sh->abort);
+        if (t.n > 0) {
+          if (kTcOwnP)     // the rows have read the S of the tile before
+            ok = ok && mbar_wait(&sh->s_free[s], (t.n - 1) & 1, &sh->abort);
+          else             // S lies where the slot's P of the tile before was: its O product must be done
+            ok = ok && mbar_wait(&sh->pv_done[s], (t.n - 1) & 1, &sh->abort);
+        }
         if (!ok) return;
         tc_fence_after();
 #pragma unroll
         for (int k = 0; k < kD / 16; ++k) {
           const uint32_t off = (k >> 2) * kTcHalfBytes + (k & 3) * 32;
-          umma_bf16(tmem + s * kTcKeys, umma_desc(q_u + s * kTcTileBytes + off), umma_desc(k_u + b * kTcTileBytes + off),
-                    idesc_qk, k != 0);
+          umma_bf16(s_col, umma_desc(q_u + off), umma_desc(k_u + b * kTcTileBytes + off), idesc_qk, k != 0);
         }
         umma_commit(&sh->qk_done[s]);
-        if (s == 1 || !t.two) umma_commit(&sh->k_free[b]);                     // both slots have read the K tile
+        umma_commit(&sh->k_free[b]);                                           // this slot has read the K tile;
+        if (!t.two) umma_commit(&sh->k_free[b]);                               // and there is no other slot to wait for
         if (t.i == t.nt - 1) umma_commit(&sh->q_free[s]);                      // the item's Q has been read
       };
-      auto issue_pv = [&](const Tile& t, int s) {
+      auto issue_pv = [&](const Tile& t) {
         const int b = t.g % kTcStages;
-        const int n_it = s == 0 ? t.it : t.it1, n_g = s == 0 ? t.g : t.g1;
-        ok = ok && mbar_wait(&sh->p_ready[s], n_g & 1, &sh->abort);
-        if (s == 0) ok = ok && mbar_wait(&sh->v_full[b], (t.g / kTcStages) & 1, &sh->abort);
+        ok = ok && mbar_wait(&sh->p_ready[s], t.n & 1, &sh->abort);
+        ok = ok && mbar_wait(&sh->v_full[b], (t.g / kTcStages) & 1, &sh->abort);
         // the first product of an item overwrites O: the rows of the item before must have read theirs
-        if (t.i == 0) ok = ok && mbar_wait(&sh->o_free[s], (n_it & 1) ^ 1, &sh->abort);
+        if (t.i == 0) ok = ok && mbar_wait(&sh->o_free[s], (t.it & 1) ^ 1, &sh->abort);
         if (!ok) return;
         tc_fence_after();
 #pragma unroll
         for (int k = 0; k < kTcKeys / 16; ++k)
 #pragma unroll
           for (int h = 0; h < kTcHalves; ++h)
-            umma_bf16_ts(tmem + kTcColO + s * kD + h * 64, tmem + s * kTcKeys + k * 8,
+            umma_bf16_ts(o_col + h * 64, p_col + k * 8,
                          umma_desc_mn(v_u + b * kTcTileBytes + h * kTcHalfBytes + k * 2048), idesc_pv,
                          (t.i != 0 || k != 0) ? 1u : 0u);
         umma_commit(&sh->pv_done[s]);
-        if (s == 1 || !t.two) umma_commit(&sh->v_free[b]);                     // both slots have read the V tile
+        umma_commit(&sh->v_free[b]);
+        if (!t.two) umma_commit(&sh->v_free[b]);
       };
+      // the slot's items: slot 1 skips those with one head
       TcWalk wk;
-      wk.first(a, n_items, pairs, tiles);
-      Tile cur = {0, 0, 0, 0, 0, wk.w.nt, wk.w.two};
-      issue_qk(cur, 0);
-      if (cur.two) issue_qk(cur, 1);
-      while (ok) {
-        // the tile after cur: of this item, or the first of the CTA's next item
-        Tile nxt = cur;
-        bool more = true;
-        ++nxt.g;
-        if (cur.two) ++nxt.g1;
-        if (++nxt.i == cur.nt) {
-          more = wk.next(a, n_items, pairs, tiles);
-          nxt = {wk.it, wk.it1, wk.g, wk.g1, 0, more ? wk.w.nt : 0, more && wk.w.two};
+      auto seek = [&](bool more) {
+        while (more && s == 1 && !wk.w.two) more = wk.next(a, n_items, pairs, tiles);
+        return more;
+      };
+      auto tile0 = [&]() { return Tile{wk.g, s == 0 ? wk.g : wk.g1, s == 0 ? wk.it : wk.it1, 0, wk.w.nt, wk.w.two}; };
+      if (seek(wk.first(a, n_items, pairs, tiles))) {
+        Tile cur = tile0();
+        issue_qk(cur);
+        while (ok) {
+          // the tile after cur: of this item, or the first of the slot's next item
+          Tile nxt = cur;
+          bool more = true;
+          ++nxt.g;
+          ++nxt.n;
+          if (++nxt.i == cur.nt) {
+            more = seek(wk.next(a, n_items, pairs, tiles));
+            if (more) nxt = tile0();
+          }
+          if (kTcOwnP) {
+            if (more) issue_qk(nxt);
+            issue_pv(cur);
+          } else {
+            issue_pv(cur);
+            if (more) issue_qk(nxt);
+          }
+          if (!more) break;
+          cur = nxt;
         }
-        issue_pv(cur, 0);
-        if (more) issue_qk(nxt, 0);
-        if (cur.two) issue_pv(cur, 1);
-        if (more && nxt.two) issue_qk(nxt, 1);
-        if (!more) break;
-        cur = nxt;
       }
     }
   } else {
@@ -400,7 +462,8 @@ prefill_attn_tc_kernel(const PrefillArgs<bf16> a, int tiles, int* status) {
     const int s = warp >> 2, q = warp & 3;
     const int r = q * 32 + lane;                         // row of the tile = TMEM lane
     const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
-    const uint32_t s_addr = tmem + lane_addr + s * kTcKeys;           // S, and P over its first 64 columns
+    const uint32_t s_addr = tmem + lane_addr + s * kTcKeys;           // S
+    const uint32_t p_addr = kTcOwnP ? tmem + lane_addr + kTcColP + s * 64 : s_addr;   // P: own columns, or over S's first 64
     const uint32_t o_addr = tmem + lane_addr + kTcColO + s * kD;
     const float sc = a.scale * kLog2e;
     bool ok = true;
@@ -422,8 +485,13 @@ prefill_attn_tc_kernel(const PrefillArgs<bf16> a, int tiles, int* status) {
         tc_fence_after();
         uint32_t sr[kTcKeys];
 #pragma unroll
-        for (int cc = 0; cc < kTcKeys / 16; ++cc) tmem_ld16_issue(s_addr + cc * 16, sr + cc * 16);
+        for (int cc = 0; cc < kTcKeys / 64; ++cc) tmem_ld64_issue(s_addr + cc * 64, sr + cc * 64);
         tmem_wait_ld();
+        if (kTcOwnP) {                                     // S is in registers: the next S product may overwrite it
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&sh->s_free[s]);
+        }
         // only tiles that reach past the first row's position, before the last row's window or past the
         // tile's rows need the masks (the same for the whole CTA)
         const bool masked = (t0 + kTcKeys - 1 > pos0) || (a.window > 0 && t0 < pos0 + kTcRows - a.window) || (rows < kTcRows);
@@ -434,23 +502,69 @@ prefill_attn_tc_kernel(const PrefillArgs<bf16> a, int tiles, int* status) {
             if (!(key <= pos_r && key >= win_r && r < rows)) sr[j] = 0xff800000u;      // -inf
           }
         }
-        float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+        float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
         for (int j = 0; j < kTcKeys; j += 4) {
-          mx0 = fmaxf(mx0, __uint_as_float(sr[j]));
-          mx1 = fmaxf(mx1, __uint_as_float(sr[j + 1]));
-          mx2 = fmaxf(mx2, __uint_as_float(sr[j + 2]));
-          mx3 = fmaxf(mx3, __uint_as_float(sr[j + 3]));
+          mx0 = max3(mx0, __uint_as_float(sr[j]), __uint_as_float(sr[j + 1]));
+          mx1 = max3(mx1, __uint_as_float(sr[j + 2]), __uint_as_float(sr[j + 3]));
         }
-        const float m_new = fmaxf(m_ref, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * sc);   // in units of log2 of the scaled scores
+        const float m_new = fmaxf(m_ref, fmaxf(mx0, mx1) * sc);   // in units of log2 of the scaled scores
+        // The reference moves for the whole warp or not at all; the denominator follows at once, the row of
+        // O below, when O is at rest.
+        float alpha = 1.f;
+        bool moved = false;
         if (i == 0) {
           m_ref = m_new;
         } else if (__any_sync(0xffffffffu, m_new > m_ref + kTcGrow)) {
-          // the reference moves for the whole warp: the denominator and the row of O follow.  (O is at
-          // rest: the product that made S waited for the O product of the tile before.)
-          const float alpha = m_new == m_ref ? 1.f : ex2_approx(m_ref - m_new);            // 2^(-inf) = 0
+          alpha = m_new == m_ref ? 1.f : ex2_approx(m_ref - m_new);                       // 2^(-inf) = 0
           l *= alpha;
           m_ref = m_new;
+          moved = true;
+        }
+        const float m_use = m_ref == -INFINITY ? 0.f : m_ref;  // a row without a live key so far
+        // The two slots take turns at the exponentials (they share the SM's special-function units, and what
+        // else a tile needs is done while the other slot has them): slot 1 goes after slot 0's of the same
+        // tile, slot 0 after slot 1's of the tile before.  e counts the tiles of the items that have both.
+        const int e = wk.g1 + i;
+        if (w.two && (s == 1 || e > 0)) {
+          ok = mbar_wait(&sh->exp_done[s ^ 1], (s == 1 ? e : e - 1) & 1, &sh->abort);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+        }
+        const uint64_t sc2 = f32x2(sc, sc), nm2 = f32x2(-m_use, -m_use);
+        uint64_t sum_a = f32x2(0.f, 0.f), sum_b = sum_a;
+#pragma unroll
+        for (int j = 0; j < kTcKeys; j += 4) {
+          float x0, x1, x2, x3;
+          f32x2_split(fma_f32x2(f32x2(__uint_as_float(sr[j]), __uint_as_float(sr[j + 1])), sc2, nm2), x0, x1);
+          f32x2_split(fma_f32x2(f32x2(__uint_as_float(sr[j + 2]), __uint_as_float(sr[j + 3])), sc2, nm2), x2, x3);
+          const float p0 = ex2_approx(x0), p1 = ex2_approx(x1), p2 = ex2_approx(x2), p3 = ex2_approx(x3);
+          sum_a = add_f32x2(sum_a, f32x2(p0, p1));
+          sum_b = add_f32x2(sum_b, f32x2(p2, p3));
+          const __nv_bfloat162 lo = __floats2bfloat162_rn(p0, p1), hi = __floats2bfloat162_rn(p2, p3);
+          sr[j >> 1] = *reinterpret_cast<const uint32_t*>(&lo);       // (columns j / 2: behind the ones still to be read)
+          sr[(j >> 1) + 1] = *reinterpret_cast<const uint32_t*>(&hi);
+        }
+        if (w.two) {
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&sh->exp_done[s]);
+        }
+        {
+          float s0, s1, s2, s3;
+          f32x2_split(sum_a, s0, s1);
+          f32x2_split(sum_b, s2, s3);
+          l += (s0 + s1) + (s2 + s3);
+        }
+        if (kTcOwnP && n > 0) {
+          // P of the tile before must have been read, and O must be at rest, before this tile's P and a
+          // rescaled O are written (long done by now: that product was issued a whole tile ago)
+          ok = mbar_wait(&sh->pv_done[s], (n - 1) & 1, &sh->abort);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after();
+        }
+        if (moved) {
+          // (with P over S, O is at rest too: the product that made S waited for the O product of the tile before)
 #pragma unroll
           for (int c0 = 0; c0 < kD; c0 += 32) {
             uint32_t o[32];
@@ -463,26 +577,9 @@ prefill_attn_tc_kernel(const PrefillArgs<bf16> a, int tiles, int* status) {
             tmem_st16(o_addr + c0 + 16, o + 16);
           }
         }
-        const float m_use = m_ref == -INFINITY ? 0.f : m_ref;  // a row without a live key so far
-        float sm0 = 0.f, sm1 = 0.f, sm2 = 0.f, sm3 = 0.f;
+        // P: two keys per 32-bit column
 #pragma unroll
-        for (int j = 0; j < kTcKeys; j += 4) {
-          const float p0 = ex2_approx(fmaf(__uint_as_float(sr[j]), sc, -m_use));
-          const float p1 = ex2_approx(fmaf(__uint_as_float(sr[j + 1]), sc, -m_use));
-          const float p2 = ex2_approx(fmaf(__uint_as_float(sr[j + 2]), sc, -m_use));
-          const float p3 = ex2_approx(fmaf(__uint_as_float(sr[j + 3]), sc, -m_use));
-          sm0 += p0;
-          sm1 += p1;
-          sm2 += p2;
-          sm3 += p3;
-          const __nv_bfloat162 lo = __floats2bfloat162_rn(p0, p1), hi = __floats2bfloat162_rn(p2, p3);
-          sr[j >> 1] = *reinterpret_cast<const uint32_t*>(&lo);       // (columns j / 2: behind the ones still to be read)
-          sr[(j >> 1) + 1] = *reinterpret_cast<const uint32_t*>(&hi);
-        }
-        l += (sm0 + sm1) + (sm2 + sm3);
-        // P: two keys per 32-bit column, over the first 64 columns of S
-#pragma unroll
-        for (int cc = 0; cc < kTcKeys / 32; ++cc) tmem_st16(s_addr + cc * 16, sr + cc * 16);
+        for (int cc = 0; cc < kTcKeys / 32; ++cc) tmem_st16(p_addr + cc * 16, sr + cc * 16);
         tmem_wait_st();
         tc_fence_before();
         __syncwarp();

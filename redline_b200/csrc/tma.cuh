@@ -64,6 +64,20 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   return false;
 }
 
+// The same for waits on the critical path of a pipeline: polls without a sleep hint (a poll still
+// blocks in the instruction for a short, hardware-chosen time), so that the waiter goes on at once
+// when the phase completes.  Bounded alike: the limit is a matter of seconds.
+__device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity, volatile int* abort) {
+  for (int i = 0; i < (kSpinLimit >> 4); ++i) {
+#pragma unroll 1
+    for (int j = 0; j < 64; ++j)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (*abort) return false;
+  }
+  *abort = 1;
+  return false;
+}
+
 __device__ __forceinline__ void tma_load_2d(void* smem, const CUtensorMap* map, uint64_t* bar, int x, int y) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
