@@ -7,9 +7,10 @@
 // one after another, longest first, and the pipeline runs on across items.  Per item the keys
 // come in tiles of 128; for each slot and key tile:
 //   S = Q K^T      tcgen05.mma, 128 x 128, k = head size, accumulator in tensor memory
-//   softmax        ONE thread per query row (four warps per slot) reads its row of S from tensor
-//                  memory, keeps the running maximum and denominator in float32 and writes P as
-//                  bfloat16 back into tensor memory, over the columns of S it has read
+//   softmax        two threads per query row (eight warps per slot, so that every scheduler of the SM
+//                  has four row warps to choose from) read the row of S from tensor memory, each
+//                  keeps the running maximum of the row and the denominator of its 64 keys in
+//                  float32 and writes their P as bfloat16 back into tensor memory
 //   O += P V       tcgen05.mma with P as the A operand from tensor memory and V as it lies in the
 //                  cache (a key's values contiguous: the B operand in MN-major form); O stays in
 //                  tensor memory for the whole item and is accumulated by the tensor core
@@ -26,10 +27,10 @@
 // into registers, so it is done before they have finished with this tile, and the rows never wait
 // for the tensor core.  At head size 128 the columns are all taken: P lies over the first 64
 // columns of its S, and the next S product has to wait for the O product that reads P.
-// Warp roles: warps 0-3 rows of slot 0, warps 4-7 rows of slot 1 (warp w owns TMEM lanes
-// 32 (w % 4) ..), warp 8 brings both Q tiles once per item and the K tiles, warp 9 the V tiles,
+// Warp roles: warps 0-7 rows of slot 0, warps 8-15 rows of slot 1 (warp w owns TMEM lanes
+// 32 (w % 4) ..), warp 16 brings both Q tiles once per item and the K tiles, warp 17 the V tiles,
 // from the paged cache with 16-byte cp.async copies (zero-filled outside the live keys), lane 0
-// of warp 10 issues the MMAs of slot 0 and lane 0 of warp 11 those of slot 1 (a slot's products
+// of warp 18 issues the MMAs of slot 0 and lane 0 of warp 19 those of slot 1 (a slot's products
 // never wait for the other slot's rows).  Everything is handed over through mbarriers; every wait is
 // bounded (kSpinLimit polls), after which the CTA raises an abort flag, all roles leave their
 // loops, the copies in flight are waited for, TMEM is freed and bit 2 of *status is set.
@@ -40,7 +41,8 @@
 namespace rl {
 
 constexpr int kTcRows = 128, kTcKeys = 128;
-constexpr int kTcThreads = 384;                        // 8 row warps, two loaders, two MMA warps
+constexpr int kTcRowWarps = 16;                        // two threads to a row: 8 warps per slot
+constexpr int kTcThreads = (kTcRowWarps + 4) * 32;      // the row warps, two loaders, two MMA warps
 constexpr int kTcHalves = kD / 64;                      // a head's columns in halves of 64 (128 bytes)
 constexpr int kTcHalfBytes = 128 * 128;                 // 128 rows x 64 bfloat16, 128-byte swizzled
 constexpr int kTcTileBytes = kTcHalves * kTcHalfBytes;  // a Q, K or V tile
@@ -58,7 +60,8 @@ struct PrefillTcShared {
   uint64_t qk_done[2], pv_done[2];                // per slot, MMA commits: S of the tile is ready / its O product is done
   uint64_t p_ready[2];                            // per slot: its four row warps have written P
   uint64_t s_free[2];                             // per slot: its four row warps have read S (used if P has its own columns)
-  uint64_t exp_done[2];                           // per slot: its four row warps have done a tile's exponentials
+  uint64_t pair[2][4];                            // per slot and quarter of rows: the two warps that share the rows meet (2 arrivals)
+  float l_half[2][2][kTcRows];                    // [slot][half][row]: a thread's part of the row's denominator
   uint64_t o_free[2];                             // per slot: its four row warps have read the item's O
   uint32_t tmem_base;
   volatile int abort;
@@ -233,10 +236,10 @@ prefill_attn_tc_kernel(const PrefillArgs<bf16> a, int tiles, int* status) {
       mbar_init(&sh->q_free[s], 1);
       mbar_init(&sh->qk_done[s], 1);
       mbar_init(&sh->pv_done[s], 1);
-      mbar_init(&sh->p_ready[s], 4);      // one arrival per row warp (its lanes meet first)
-      mbar_init(&sh->s_free[s], 4);
-      mbar_init(&sh->exp_done[s], 4);
-      mbar_init(&sh->o_free[s], 4);
+      mbar_init(&sh->p_ready[s], 8);      // one arrival per row warp of the slot (its lanes meet first)
+      mbar_init(&sh->s_free[s], 8);
+      mbar_init(&sh->o_free[s], 8);
+      for (int qq = 0; qq < 4; ++qq) mbar_init(&sh->pair[s][qq], 2);
     }
     for (int b = 0; b < kTcStages; ++b) {
       mbar_init(&sh->k_full[b], 1);
@@ -247,7 +250,7 @@ prefill_attn_tc_kernel(const PrefillArgs<bf16> a, int tiles, int* status) {
     sh->abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 10) {   // TMEM allocation is a whole-warp operation
+  if (warp == kTcRowWarps + 2) {   // TMEM allocation is a whole-warp operation
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh->tmem_base)),
                  "r"(kTcTmemCols)
                  : "memory");
@@ -260,9 +263,9 @@ prefill_attn_tc_kernel(const PrefillArgs<bf16> a, int tiles, int* status) {
   pdl_launch();
   pdl_wait();        // q and the newest keys come from the kernels before this one
 
-  if (warp == 8 || warp == 9) {
+  if (warp == kTcRowWarps || warp == kTcRowWarps + 1) {
     // ------------------------------------------------------------------ loaders: warp 8 K (and both Q), warp 9 V
-    const bool is_v = warp == 9;
+    const bool is_v = warp == kTcRowWarps + 1;
     const int ps_shift = __ffs(a.page_size) - 1, ps_mask = a.page_size - 1;
     const size_t head_stride = static_cast<size_t>(a.page_size) * kD;
     constexpr int CPR = kD / 8;                          // 16-byte chunks of a row
@@ -366,13 +369,13 @@ prefill_attn_tc_kernel(const PrefillArgs<bf16> a, int tiles, int* status) {
       }
     }
     hand_over(true);
-  } else if (warp >= 10) {
+  } else if (warp >= kTcRowWarps + 2) {
     // ------------------------------------------------------------------ MMA issue: lane 0 of warp 10 for slot 0, of warp 11 for slot 1
     // Each slot has an issuing thread of its own, so that neither slot's products ever wait for the
     // other slot's rows.  With columns of its own for P a slot's products go  S(0), S(1), O += P(0) V,
     // S(2), O += P(1) V, ...: the S product runs one key tile ahead of the rows; with P over S:
     // S(0), O += P(0) V, S(1), O += P(1) V, ...
-    const int s = warp - 10;
+    const int s = warp - (kTcRowWarps + 2);
     if (lane == 0 && blockIdx.x < n_items) {
       const uint32_t idesc_qk = umma_idesc(kTcRows, kTcKeys);
       const uint32_t idesc_pv = umma_idesc(kTcRows, 64) | (1u << 16);          // B (V) is MN-major; 64 columns of O at a time
@@ -457,16 +460,22 @@ prefill_attn_tc_kernel(const PrefillArgs<bf16> a, int tiles, int* status) {
       }
     }
   } else {
-    // ------------------------------------------------------------------ the row threads, one to a row
-    // Warp w < 8: slot w / 4, rows 32 (w % 4) .. + 32 of the slot's tile (the TMEM lanes a warp may touch).
-    const int s = warp >> 2, q = warp & 3;
+    // ------------------------------------------------------------------ the row threads, two to a row
+    // Warp w < 16: slot w / 8, half h = (w / 4) % 2, rows 32 (w % 4) .. + 32 of the slot's tile (the TMEM
+    // lanes a warp may touch).  A thread has the keys 64 h .. + 64 of every S tile, writes their P, and has
+    // the columns h D / 2 .. + D / 2 of O.  Both threads of a row take the maximum over the whole row (the
+    // other half is read from tensor memory for that alone, which is cheaper than an exchange), so both
+    // come to the same reference and the same decisions; each keeps the denominator of its own keys, and
+    // the two are added at the item's end (one exchange through shared memory).
+    const int s = warp >> 3, h = (warp >> 2) & 1, q = warp & 3;
     const int r = q * 32 + lane;                         // row of the tile = TMEM lane
     const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
     const uint32_t s_addr = tmem + lane_addr + s * kTcKeys;           // S
-    const uint32_t p_addr = kTcOwnP ? tmem + lane_addr + kTcColP + s * 64 : s_addr;   // P: own columns, or over S's first 64
-    const uint32_t o_addr = tmem + lane_addr + kTcColO + s * kD;
+    const uint32_t p_addr = (kTcOwnP ? tmem + lane_addr + kTcColP + s * 64 : s_addr) + h * 32;   // this thread's 32 columns of P
+    const uint32_t o_addr = tmem + lane_addr + kTcColO + s * kD + h * (kD / 2);
     const float sc = a.scale * kLog2e;
     bool ok = true;
+    int xphase = 0;                                       // exchanges done so far (parity of the pair's mbarrier)
     TcWalk wk;
     for (bool more = wk.first(a, n_items, pairs, tiles); more && ok; more = wk.next(a, n_items, pairs, tiles)) {
       const TcItem& w = wk.w;
@@ -475,7 +484,7 @@ prefill_attn_tc_kernel(const PrefillArgs<bf16> a, int tiles, int* status) {
       const int rows = w.rows, pos0 = w.pos0;
       const int pos_r = pos0 + r;
       const int win_r = (a.window > 0 && pos_r + 1 > a.window) ? pos_r + 1 - a.window : 0;
-      float m_ref = -INFINITY, l = 0.f;                   // the maximum that P is scaled by (log2 units), the denominator
+      float m_ref = -INFINITY, l = 0.f;                   // the maximum that P is scaled by (log2 units), this thread's part of the denominator
       for (int i = 0; i < w.nt && ok; ++i) {
         const int n = g_base + i;
         const int t0 = w.k_begin + i * kTcKeys;
@@ -483,34 +492,51 @@ prefill_attn_tc_kernel(const PrefillArgs<bf16> a, int tiles, int* status) {
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
-        uint32_t sr[kTcKeys];
+        // only tiles that reach past the first row's position, before the last row's window or past the
+        // tile's rows need the masks (the same for the whole CTA)
+        const bool masked = (t0 + kTcKeys - 1 > pos0) || (a.window > 0 && t0 < pos0 + kTcRows - a.window) || (rows < kTcRows);
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+        uint32_t sr[64];
+        {   // the other thread's keys, for the maximum; then this thread's own
+          tmem_ld64_issue(s_addr + (h ^ 1) * 64, sr);
+          tmem_wait_ld();
+          if (masked) {
+            const int k0 = t0 + (h ^ 1) * 64;
 #pragma unroll
-        for (int cc = 0; cc < kTcKeys / 64; ++cc) tmem_ld64_issue(s_addr + cc * 64, sr + cc * 64);
+            for (int j = 0; j < 64; ++j) {
+              const int key = k0 + j;
+              if (!(key <= pos_r && key >= win_r && r < rows)) sr[j] = 0xff800000u;      // -inf
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < 64; j += 4) {
+            mx0 = max3(mx0, __uint_as_float(sr[j]), __uint_as_float(sr[j + 1]));
+            mx1 = max3(mx1, __uint_as_float(sr[j + 2]), __uint_as_float(sr[j + 3]));
+          }
+        }
+        tmem_ld64_issue(s_addr + h * 64, sr);
         tmem_wait_ld();
         if (kTcOwnP) {                                     // S is in registers: the next S product may overwrite it
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(&sh->s_free[s]);
         }
-        // only tiles that reach past the first row's position, before the last row's window or past the
-        // tile's rows need the masks (the same for the whole CTA)
-        const bool masked = (t0 + kTcKeys - 1 > pos0) || (a.window > 0 && t0 < pos0 + kTcRows - a.window) || (rows < kTcRows);
         if (masked) {
+          const int k0 = t0 + h * 64;
 #pragma unroll
-          for (int j = 0; j < kTcKeys; ++j) {
-            const int key = t0 + j;
+          for (int j = 0; j < 64; ++j) {
+            const int key = k0 + j;
             if (!(key <= pos_r && key >= win_r && r < rows)) sr[j] = 0xff800000u;      // -inf
           }
         }
-        float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
-        for (int j = 0; j < kTcKeys; j += 4) {
+        for (int j = 0; j < 64; j += 4) {
           mx0 = max3(mx0, __uint_as_float(sr[j]), __uint_as_float(sr[j + 1]));
           mx1 = max3(mx1, __uint_as_float(sr[j + 2]), __uint_as_float(sr[j + 3]));
         }
         const float m_new = fmaxf(m_ref, fmaxf(mx0, mx1) * sc);   // in units of log2 of the scaled scores
-        // The reference moves for the whole warp or not at all; the denominator follows at once, the row of
-        // O below, when O is at rest.
+        // The reference moves for the whole warp or not at all (the other warp of these rows sees the same
+        // maxima and decides the same); the denominator follows at once, the row of O below, when O is at rest.
         float alpha = 1.f;
         bool moved = false;
         if (i == 0) {
@@ -522,19 +548,10 @@ prefill_attn_tc_kernel(const PrefillArgs<bf16> a, int tiles, int* status) {
           moved = true;
         }
         const float m_use = m_ref == -INFINITY ? 0.f : m_ref;  // a row without a live key so far
-        // The two slots take turns at the exponentials (they share the SM's special-function units, and what
-        // else a tile needs is done while the other slot has them): slot 1 goes after slot 0's of the same
-        // tile, slot 0 after slot 1's of the tile before.  e counts the tiles of the items that have both.
-        const int e = wk.g1 + i;
-        if (w.two && (s == 1 || e > 0)) {
-          ok = mbar_wait(&sh->exp_done[s ^ 1], (s == 1 ? e : e - 1) & 1, &sh->abort);
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) break;
-        }
         const uint64_t sc2 = f32x2(sc, sc), nm2 = f32x2(-m_use, -m_use);
         uint64_t sum_a = f32x2(0.f, 0.f), sum_b = sum_a;
 #pragma unroll
-        for (int j = 0; j < kTcKeys; j += 4) {
+        for (int j = 0; j < 64; j += 4) {
           float x0, x1, x2, x3;
           f32x2_split(fma_f32x2(f32x2(__uint_as_float(sr[j]), __uint_as_float(sr[j + 1])), sc2, nm2), x0, x1);
           f32x2_split(fma_f32x2(f32x2(__uint_as_float(sr[j + 2]), __uint_as_float(sr[j + 3])), sc2, nm2), x2, x3);
@@ -544,10 +561,6 @@ prefill_attn_tc_kernel(const PrefillArgs<bf16> a, int tiles, int* status) {
           const __nv_bfloat162 lo = __floats2bfloat162_rn(p0, p1), hi = __floats2bfloat162_rn(p2, p3);
           sr[j >> 1] = *reinterpret_cast<const uint32_t*>(&lo);       // (columns j / 2: behind the ones still to be read)
           sr[(j >> 1) + 1] = *reinterpret_cast<const uint32_t*>(&hi);
-        }
-        if (w.two) {
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&sh->exp_done[s]);
         }
         {
           float s0, s1, s2, s3;
@@ -563,10 +576,22 @@ prefill_attn_tc_kernel(const PrefillArgs<bf16> a, int tiles, int* status) {
           if (!ok) break;
           tc_fence_after();
         }
+        if (!kTcOwnP) {
+          // P goes over columns of S that the other thread of the row reads too (its own keys, or this
+          // thread's for the maximum): both must have read S before either writes P
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&sh->pair[s][q]);
+          ok = mbar_wait(&sh->pair[s][q], xphase & 1, &sh->abort);
+          ++xphase;
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after();
+        }
         if (moved) {
           // (with P over S, O is at rest too: the product that made S waited for the O product of the tile before)
 #pragma unroll
-          for (int c0 = 0; c0 < kD; c0 += 32) {
+          for (int c0 = 0; c0 < kD / 2; c0 += 32) {
             uint32_t o[32];
             tmem_ld16_issue(o_addr + c0, o);
             tmem_ld16_issue(o_addr + c0 + 16, o + 16);
@@ -577,24 +602,33 @@ prefill_attn_tc_kernel(const PrefillArgs<bf16> a, int tiles, int* status) {
             tmem_st16(o_addr + c0 + 16, o + 16);
           }
         }
-        // P: two keys per 32-bit column
-#pragma unroll
-        for (int cc = 0; cc < kTcKeys / 32; ++cc) tmem_st16(p_addr + cc * 16, sr + cc * 16);
+        // P: two keys per 32-bit column; this thread's 64 keys are 32 columns
+        tmem_st16(p_addr, sr);
+        tmem_st16(p_addr + 16, sr + 16);
         tmem_wait_st();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&sh->p_ready[s]);
       }
       if (!ok) break;
+      // ---- the row's denominator: this thread's part and the other's
+      sh->l_half[s][h][r] = l;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sh->pair[s][q]);        // (release: the values are visible to who sees the phase)
+      ok = mbar_wait(&sh->pair[s][q], xphase & 1, &sh->abort);
+      ++xphase;
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      const float l_all = l + sh->l_half[s][h ^ 1][r];
       // ---- the item's rows: O / denominator, once its last product is done
       ok = mbar_wait(&sh->pv_done[s], (g_base + w.nt - 1) & 1, &sh->abort);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      const float inv = l > 0.f ? 1.f / l : 0.f;
-      bf16* dst = a.out + static_cast<size_t>(w.tok0 + (r < rows ? r : 0)) * a.out_stride + (w.head0 + s) * kD;
+      const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
+      bf16* dst = a.out + static_cast<size_t>(w.tok0 + (r < rows ? r : 0)) * a.out_stride + (w.head0 + s) * kD + h * (kD / 2);
 #pragma unroll
-      for (int c0 = 0; c0 < kD; c0 += 32) {
+      for (int c0 = 0; c0 < kD / 2; c0 += 32) {
         uint32_t o[32];
         tmem_ld16_issue(o_addr + c0, o);
         tmem_ld16_issue(o_addr + c0 + 16, o + 16);
@@ -616,7 +650,7 @@ prefill_attn_tc_kernel(const PrefillArgs<bf16> a, int tiles, int* status) {
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 10) {
+  if (warp == kTcRowWarps + 2) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTcTmemCols) : "memory");
   }
