@@ -207,7 +207,8 @@ def bench_attn_prefill(args) -> None:
         kernels.attn_prefill(qkv, qkv.shape[1], k, v, bt, tile_seq, tile_tok, tile_rows, pos, out, nt, Hq, Hkv, D, ps,
                              0, 1.0 / math.sqrt(D), args.impl)
 
-    us = graph_time_us(fn, 2, replays=5, use_graph=not args.no_graph)
+    # (16 launches to a graph: the launch of the graph itself then hardly counts)
+    us = graph_time_us(fn, 16 if T <= 4096 else 2, replays=5, use_graph=not args.no_graph)
     flops = Hq * 4.0 * D * (T * (T + 1) / 2.0)
     pk = peaks()
     print(json.dumps({"kernel": "attn_prefill", "impl": args.impl, "tokens": T, "heads": Hq, "kv_heads": Hkv, "head_dim": D,

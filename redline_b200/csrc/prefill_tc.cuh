@@ -169,6 +169,20 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   return d;
 }
 
+// Sets the scores of 64 keys that a row may not see to -inf: key j of them is live if jmin <= j <= jmax.
+// Without a window (the same for all threads) there is no lower limit to test.
+__device__ __forceinline__ void tc_mask64(uint32_t* sr, int jmax, int jmin, bool window) {
+  if (!window) {
+#pragma unroll
+    for (int j = 0; j < 64; ++j)
+      if (j > jmax) sr[j] = 0xff800000u;
+  } else {
+#pragma unroll
+    for (int j = 0; j < 64; ++j)
+      if (j > jmax || j < jmin) sr[j] = 0xff800000u;
+  }
+}
+
 // The items of a CTA: in round k the CTAs take items k G .. k G + G - 1 (G CTAs), in odd rounds in
 // reverse order, so that the CTA with the longest item of one round has the shortest of the next.
 // Gives the CTA's next item and moves `round` on; -1 when there is none.
@@ -484,6 +498,7 @@ prefill_attn_tc_kernel(const PrefillArgs<bf16> a, int tiles, int* status) {
       const int rows = w.rows, pos0 = w.pos0;
       const int pos_r = pos0 + r;
       const int win_r = (a.window > 0 && pos_r + 1 > a.window) ? pos_r + 1 - a.window : 0;
+      const int lim_r = r < rows ? pos_r : -1;             // the row's live keys are win_r .. lim_r (none for a row past the tile's rows)
       float m_ref = -INFINITY, l = 0.f;                   // the maximum that P is scaled by (log2 units), this thread's part of the denominator
       for (int i = 0; i < w.nt && ok; ++i) {
         const int n = g_base + i;
@@ -500,14 +515,7 @@ prefill_attn_tc_kernel(const PrefillArgs<bf16> a, int tiles, int* status) {
         {   // the other thread's keys, for the maximum; then this thread's own
           tmem_ld64_issue(s_addr + (h ^ 1) * 64, sr);
           tmem_wait_ld();
-          if (masked) {
-            const int k0 = t0 + (h ^ 1) * 64;
-#pragma unroll
-            for (int j = 0; j < 64; ++j) {
-              const int key = k0 + j;
-              if (!(key <= pos_r && key >= win_r && r < rows)) sr[j] = 0xff800000u;      // -inf
-            }
-          }
+          if (masked) tc_mask64(sr, lim_r - (t0 + (h ^ 1) * 64), win_r - (t0 + (h ^ 1) * 64), a.window > 0);
 #pragma unroll
           for (int j = 0; j < 64; j += 4) {
             mx0 = max3(mx0, __uint_as_float(sr[j]), __uint_as_float(sr[j + 1]));
@@ -521,14 +529,7 @@ prefill_attn_tc_kernel(const PrefillArgs<bf16> a, int tiles, int* status) {
           __syncwarp();
           if (lane == 0) mbar_arrive(&sh->s_free[s]);
         }
-        if (masked) {
-          const int k0 = t0 + h * 64;
-#pragma unroll
-          for (int j = 0; j < 64; ++j) {
-            const int key = k0 + j;
-            if (!(key <= pos_r && key >= win_r && r < rows)) sr[j] = 0xff800000u;      // -inf
-          }
-        }
+        if (masked) tc_mask64(sr, lim_r - (t0 + h * 64), win_r - (t0 + h * 64), a.window > 0);
 #pragma unroll
         for (int j = 0; j < 64; j += 4) {
           mx0 = max3(mx0, __uint_as_float(sr[j]), __uint_as_float(sr[j + 1]));

@@ -9,6 +9,9 @@
 
 namespace rl {
 
+#ifndef RL_MBAR_SLEEP_NS
+#define RL_MBAR_SLEEP_NS 1000u
+#endif
 // Polls of an mbarrier before a waiter gives up (and raises the CTA's abort flag).
 constexpr int kSpinLimit = 1 << 22;
 
@@ -57,7 +60,7 @@ __device__ __forceinline__ bool mbar_try_wait_sleep(uint64_t* bar, uint32_t pari
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort) {
   if (mbar_try_wait(bar, parity)) return true;
   for (int i = 0; i < kSpinLimit; ++i) {
-    if (mbar_try_wait_sleep(bar, parity, 1000u)) return true;
+    if (mbar_try_wait_sleep(bar, parity, RL_MBAR_SLEEP_NS)) return true;
     if (*abort) return false;
   }
   *abort = 1;
