@@ -23,6 +23,8 @@ def main(argv: Optional[List[str]] = None) -> int:
     ap.add_argument("--warmup", type=int, default=2, help="warm-up requests")
     ap.add_argument("--per-request", action="store_true", help="include per-request metrics")
     ap.add_argument("--trace-out", help="step-by-step trace file")
+    ap.add_argument("--profile-ops", action="store_true",
+                    help="per-op GPU time breakdown with roofline fractions (runs eagerly; skews throughput)")
     ap.add_argument("--tag", default="redline_b200", help="label stored in the report")
     args = ap.parse_args(argv)
     try:
@@ -42,22 +44,26 @@ def main(argv: Optional[List[str]] = None) -> int:
             workloads.append((w.name, w))
         peaks = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))),
                              "MEASURED_PEAKS.json")
-        hbm = 0.0
+        hbm = tflops = 0.0
         if os.path.exists(peaks):
             with open(peaks) as f:
-                hbm = float(json.load(f).get("hbm_gbs", 0.0))
+                pk = json.load(f)
+            hbm, tflops = float(pk.get("hbm_gbs", 0.0)), float(pk.get("bf16_tflops", 0.0))
         if args.out_dir:
             os.makedirs(args.out_dir, exist_ok=True)
         reports = []
         for name, w in workloads:
             opts = BenchOptions(online=args.online, warmup_requests=args.warmup, keep_per_request=args.per_request,
-                                hbm_gbs=hbm)
+                                hbm_gbs=hbm, bf16_tflops=tflops, profile_ops=args.profile_ops)
             if args.trace_out:
                 opts.trace_path = args.trace_out if len(workloads) == 1 else \
                     args.trace_out.replace(".json", "") + f"__{name}.json"
             rep = run_benchmark(engine, w, opts)
             rep["tag"], rep["system"] = args.tag, "redline_b200"
             print(format_report_summary(rep), file=sys.stderr)
+            if args.profile_ops:
+                from ..engine.profiler import format_op_profile
+                print(format_op_profile(rep["op_profile"]), file=sys.stderr, end="")
             if args.out_dir:
                 with open(os.path.join(args.out_dir, f"{args.tag}__{name}.json"), "w") as f:
                     json.dump(rep, f, indent=1)

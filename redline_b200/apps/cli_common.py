@@ -29,6 +29,8 @@ def add_engine_options(ap: argparse.ArgumentParser) -> None:
     g.add_argument("--no-cuda-graphs", action="store_true", help="disable CUDA graph replay for decode")
     g.add_argument("--no-async", action="store_true", help="disable asynchronous (pipelined) scheduling")
     g.add_argument("--no-mixed-batches", action="store_true", help="do not mix prefill chunks with decode tokens")
+    g.add_argument("--nvtx-layers", action="store_true", help="emit one NVTX range per step and per layer call")
+    g.add_argument("--track-memory", action="store_true", help="sample device memory every step (peak in the report)")
     g.add_argument("--device", type=int, default=0, help="CUDA device")
 
 
@@ -39,7 +41,8 @@ def engine_options(args: argparse.Namespace, default_utilization: float = 0.9) -
         max_seq_len=args.max_seq_len, max_logit_rows=args.max_logit_rows, block_size=args.block_size,
         kv_cache_tokens=args.kv_cache_tokens, gpu_memory_utilization=util,
         cuda_graphs=not args.no_cuda_graphs, async_scheduling=not args.no_async,
-        mix_prefill_decode=not args.no_mixed_batches, device=args.device)
+        mix_prefill_decode=not args.no_mixed_batches, nvtx_layers=args.nvtx_layers,
+        track_memory=args.track_memory, device=args.device)
 
 
 def resolve_model(args: argparse.Namespace) -> str:

@@ -121,6 +121,8 @@ class BenchOptions:
     keep_per_request: bool = False
     trace_path: str = ""
     hbm_gbs: float = 0.0          # > 0: report decode steps against this bandwidth
+    bf16_tflops: float = 0.0      # > 0: with profile_ops, report compute-bound ops against this peak
+    profile_ops: bool = False     # per-op device time breakdown (steps run eagerly; skews throughput)
 
 
 def _warmup(engine, w: Workload, opts: BenchOptions) -> None:
@@ -141,7 +143,10 @@ def run_benchmark(engine, workload: Workload, opts: Optional[BenchOptions] = Non
     _warmup(engine, workload, opts)
     engine.records.clear()
     engine.record_steps = True
-    torch.cuda.reset_peak_memory_stats(engine.runner.device)
+    engine.reset_peak_memory()
+    if opts.profile_ops:
+        engine.set_op_profiling(True)
+        engine.reset_op_profile()
     order = sorted(workload.requests, key=lambda r: r.arrival_time if opts.online else 0.0)
     wave = int(workload.settings.get("batch_size", 0)) if not opts.online else 0
     outputs: List[Dict[str, Any]] = []
@@ -234,6 +239,9 @@ def run_benchmark(engine, workload: Workload, opts: Optional[BenchOptions] = Non
                                      "weights_only_frac_p50": wb / (percentile(decode_step_gpu, 50) / 1e3) / 1e9 / opts.hbm_gbs}
     if opts.keep_per_request:
         report["requests"] = per_request
+    if opts.profile_ops:
+        report["op_profile"] = engine.op_profile(opts.hbm_gbs, opts.bf16_tflops)
+        engine.set_op_profiling(False)
     if opts.trace_path:
         with open(opts.trace_path, "w") as f:
             json.dump({"report": {k: v for k, v in report.items() if k != "requests"},

@@ -27,6 +27,8 @@ class EngineConfig:
     async_scheduling: bool = True
     mix_prefill_decode: bool = True
     admission_watermark: float = 0.01
+    nvtx_layers: bool = False          # one NVTX range per step and per layer call (for nsys timelines)
+    track_memory: bool = False         # sample the device's used memory every step (peak in memory_report)
     device: int = 0
 
     # names the reference's Python entry point and command line use for the same options

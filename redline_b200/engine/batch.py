@@ -144,6 +144,7 @@ class StepContext:
     has_src: bool = False
     any_sampling: bool = False
     host: Optional["HostBatch"] = None
+    profiler: Optional[object] = None          # engine.profiler.OpProfiler while per-op profiling is on
     # a norm handed over between parts (parts.base.NormHandover); set and cleared by the block
     next_norm: Optional[object] = None         # the norm applied to the stream after the running part
     hand_in: Optional[object] = None           # what the part before left for the running part's norm

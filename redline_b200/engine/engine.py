@@ -108,6 +108,8 @@ class Engine:
         self.record_steps = False
         self.records: List[StepRecord] = []
         self.num_preemptions = 0
+        self.peak_device_used = 0                  # with track_memory: the most device memory seen in use after a step
+        self._op_profile_rows: List[Dict[str, Any]] = []
         self._replay_pos: Dict[object, int] = {}
         # Called after every launched step with ([(request id, position)] of the rows whose logits
         # the step computed, in row order, and the float32 logits [rows, vocab] on the device, valid
@@ -194,11 +196,18 @@ class Engine:
                 sample_rows.append(-1)
         slot = step % 2
         graphs_before = self.runner.num_graph_steps
+        if self.cfg.nvtx_layers:
+            torch.cuda.nvtx.range_push(f"step {step}: {plan.num_prefill_tokens} prompt + {plan.num_decode_tokens} decode tokens")
         if self.record_steps:
             self._ev_start[slot].record()
         logits, _ = self.runner.run(segments, sample=True)
         if self.record_steps:
             self._ev_stop[slot].record()
+        if self.cfg.nvtx_layers:
+            torch.cuda.nvtx.range_pop()
+        if self.cfg.track_memory:
+            free, total = torch.cuda.mem_get_info(self.runner.device)
+            self.peak_device_used = max(self.peak_device_used, total - free)
         if self.on_logits is not None and row > 0:
             self.on_logits([(e.seq.id, e.start_pos + e.num_tokens - 1) for e in plan.seqs if e.sample], logits[:row])
         if row > 0:
@@ -403,11 +412,32 @@ class Engine:
         return out
 
     # --------------------------------------------------------------- reports
+    def set_op_profiling(self, on: bool) -> None:
+        """Per-op device time of every step from now on (reference: Engine::set_op_profiling,
+        src/cuda/engine/engine.h:120-124).  Steps run eagerly meanwhile, which skews throughput."""
+        self.runner.set_op_profiling(on)
+
+    def reset_op_profile(self) -> None:
+        if self.runner.profiler is not None:
+            self.runner.profiler.reset()
+
+    def op_profile(self, hbm_gbs: float = 0.0, tflops: float = 0.0) -> List[Dict[str, Any]]:
+        """Rows of the per-op table (engine.profiler.OpProfiler.report), with roofline fractions against
+        the given peaks."""
+        return self.runner.profiler.report(hbm_gbs, tflops) if self.runner.profiler is not None else []
+
+    def reset_peak_memory(self) -> None:
+        free, total = torch.cuda.mem_get_info(self.runner.device)
+        self.peak_device_used = total - free
+        torch.cuda.reset_peak_memory_stats(self.runner.device)
+
     def memory_report(self) -> Dict[str, Any]:
         rep: Dict[str, Any] = dict(self.runner.memory_report())
         free, total = torch.cuda.mem_get_info(self.runner.device)
         rep["device_total"] = total
         rep["device_used"] = total - free
+        self.peak_device_used = max(self.peak_device_used, total - free)
+        rep["peak_device_used_bytes"] = self.peak_device_used
         rep["torch_peak"] = torch.cuda.max_memory_allocated(self.runner.device)
         return rep
 
@@ -420,7 +450,8 @@ class Engine:
             "dtype": self.cfg.dtype,
             "config": {k: getattr(self.cfg, k) for k in (
                 "max_num_seqs", "max_num_batched_tokens", "max_seq_len", "block_size", "kv_cache_tokens",
-                "gpu_memory_utilization", "cuda_graphs", "async_scheduling", "mix_prefill_decode")},
+                "gpu_memory_utilization", "cuda_graphs", "async_scheduling", "mix_prefill_decode", "nvtx_layers",
+                "track_memory")},
             "cache_groups": [{"kind": g.spec.kind, "window": g.spec.window, "layers": len(g.owners),
                               "tensors": {t.name: list(t.shape) for t in g.spec.tensors},
                               "pages": c.num_total_pages(i)} for i, g in enumerate(c.groups)],

@@ -13,7 +13,7 @@ import torch
 
 from ..cache.manager import GroupInfo
 from ..parts import base as parts_base
-from ..parts.base import Block, Runtime, build_part, lookup
+from ..parts.base import Block, Runtime, build_part, lookup, op_mark
 from ..parts.spec import CacheSpec, ModelSpec, StateSpec, TensorSpec
 from ..weights import loader
 from ..weights.safetensors_io import CheckpointReader
@@ -33,6 +33,7 @@ class DecoderModel:
                                          build_part("ffn", ls.ffn, rt) if ls.ffn is not None else None, rt))
         self.final_norm = build_part("norm", spec.final_norm, rt)
         self.head = build_part("head", spec.head, rt)
+        self.nvtx_layers = False           # one NVTX range per layer call (set by the runner from the engine's options)
         self._check_order()
 
     # -------------------------------------------------------------- layout
@@ -102,13 +103,23 @@ class DecoderModel:
 
     def load_weights(self, reader: CheckpointReader) -> None:
         rt = self.rt
-        tensors = loader.load(reader, self.expected_tensors(), rt.dtype, rt.device)
-        for part in self._named_parts():
+        parts = list(self._named_parts())
+        fused = {}                       # "<part number>:<fused name>" -> checkpoint names of its members
+        for pi, part in enumerate(parts):
+            for fname, members in part.fused().items():
+                names = [part.spec.names.get(m) for m in members]
+                if all(n is not None for n in names):
+                    fused[f"{pi}:{fname}"] = names
+        tensors = loader.load(reader, self.expected_tensors(), rt.dtype, rt.device, fused=fused)
+        for pi, part in enumerate(parts):
             mine = {}
             for local in part.tensors():
                 name = part.spec.names.get(local)
                 if name is not None and name in tensors:
                     mine[local] = tensors[name]
+            for fname in part.fused():
+                if f"{pi}:{fname}" in tensors:
+                    mine[fname] = tensors[f"{pi}:{fname}"]
             part.load(mine)
         if self.head.wants_table():
             # no head tensor in use: the head shares the embedding table
@@ -126,18 +137,26 @@ class DecoderModel:
         ws = rt.workspace
         residual = ws.get("residual", (rt.max_tokens, self.spec.hidden_size), torch.float32)[:T]
         self.embedding.forward(ctx, residual)
+        op_mark(ctx, "embed", nbytes=T * self.spec.hidden_size * (4.0 + (2 if rt.dtype == torch.bfloat16 else 4)))
         pending = None
         order = self.spec.order
         ctx.block_hand = None
         for i, call in enumerate(order):
             # (the block after this one may take over its first norm from this block's last kernel)
             ctx.block_next_norm = self.blocks[order[i + 1].layer].first_norm() if i + 1 < len(order) else None
+            if self.nvtx_layers:
+                torch.cuda.nvtx.range_push(f"layer call {i} (layer {call.layer})")
             pending = self.blocks[call.layer].forward(residual, pending, ctx, caches[i], states[i])
+            if self.nvtx_layers:
+                torch.cuda.nvtx.range_pop()
         ctx.block_hand = ctx.block_next_norm = None
+        head_w = getattr(self.head, "weight", None)
         if R > 0 and pending is None and self.head.forward_from(residual, self.final_norm, ctx.logit_rows, R, logits):
-            pass
+            op_mark(ctx, "final_norm+lm_head", head_w, R, nbytes=R * logits.shape[1] * 2.0)
         elif R > 0:
             xr = ws.get("head.in", (logits.shape[0], self.spec.hidden_size), rt.dtype)[:R]
             self.final_norm.add_norm(residual, pending, xr, rows_idx=ctx.logit_rows, rows=R)
+            op_mark(ctx, "final_norm", nbytes=R * self.spec.hidden_size * 6.0)
             self.head.forward(xr, R, logits)
+            op_mark(ctx, "lm_head", head_w, R, nbytes=R * logits.shape[1] * 2.0)     # (the logits are float32: 2 more bytes each)
         return logits[:R]

@@ -97,6 +97,8 @@ class ModelRunner:
             else:
                 self._caches.append(self.storage.of_owner(call.cache_of, False))
         self._states = [self.states.of_call(i) for i in range(len(order))]
+        self.model.nvtx_layers = cfg.nvtx_layers
+        self.profiler = None                       # engine.profiler.OpProfiler while per-op profiling is on
         self._graphs: Dict[int, torch.cuda.CUDAGraph] = {}
         self._graph_kernels: Dict[int, int] = {}   # kernels of this package in each captured graph
         self.num_kernel_launches = 0               # kernels of this package run by steps so far
@@ -136,8 +138,13 @@ class ModelRunner:
         been reserved.  Returns (logits[:R], ctx); with ``sample`` the sampler's
         ``tokens[:R]`` / ``logprobs[:R]`` are filled too.  A segment with ``src_row`` >= 0
         takes its token from that row of the sampler's tokens as the previous step left them."""
-        bucket = self._graph_bucket(segments) if (allow_graph and self.cfg.cuda_graphs and sample) else 0
+        profiling = self.profiler is not None          # (a graph cannot be cut into ops: profiled steps are eager)
+        bucket = self._graph_bucket(segments) if (allow_graph and self.cfg.cuda_graphs and sample and not profiling) else 0
         ctx = self.builder.build(segments, pad_to=bucket)
+        if profiling:
+            single = sum(1 for s in segments if len(s.tokens) == 1)
+            ctx.profiler = self.profiler
+            self.profiler.begin("decode" if single == len(segments) else ("prefill" if single == 0 else "mixed"))
         if bucket:
             g = self._graphs.get(bucket)
             if g is None:
@@ -151,6 +158,8 @@ class ModelRunner:
             self._forward(ctx, sample, ctx.has_src)
             self.num_eager_steps += 1
             self.num_kernel_launches += kernels.LAUNCHES - before
+            if profiling:
+                self.profiler.end()
         return self.logits[:ctx.R], ctx
 
     def _forward(self, ctx: StepContext, sample: bool, resolve: bool) -> None:
@@ -159,6 +168,8 @@ class ModelRunner:
         self.model.forward(ctx, self._caches, self._states, self.logits)
         if sample and ctx.R > 0:
             self.sampler.sample(self.logits, ctx)
+            if ctx.profiler is not None:
+                ctx.profiler.mark("sample", ctx.R * self.vocab_size * 4.0, 0.0)
 
     def _graph_bucket(self, segments: Sequence[Segment]) -> int:
         """The padded size at which this step is replayed as a CUDA graph, or 0 for an eager step.
@@ -210,6 +221,14 @@ class ModelRunner:
             if tc_code & 8:
                 what.append("a wait inside the tcgen05 product for few rows that ran out")
             raise EngineError("a kernel met " + " and ".join(what))
+
+    def set_op_profiling(self, on: bool) -> None:
+        """Per-op device times of every step from now on (steps then run eagerly), or off."""
+        from .profiler import OpProfiler
+        if on and self.profiler is None:
+            self.profiler = OpProfiler()
+        elif not on:
+            self.profiler = None
 
     def memory_report(self) -> Dict[str, int]:
         return {

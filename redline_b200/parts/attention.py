@@ -18,7 +18,7 @@ import torch
 
 from ..ops import kernels
 from ..ops.linear import linear
-from .base import LayerCache, Mixer, build_part, norm_handover, register
+from .base import LayerCache, Mixer, build_part, norm_handover, op_mark, register
 from .spec import CacheSpec, PartSpec, TensorSpec
 
 
@@ -72,10 +72,16 @@ class GQAttention(Mixer):
         }
         return t
 
+    def fused(self) -> Dict[str, list]:
+        return {"qkv": ["q", "k", "v"]}
+
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
-        q, k, v = tensors["q"], tensors["k"], tensors["v"]
-        dt = torch.float32 if torch.float32 in (q.dtype, k.dtype, v.dtype) else q.dtype
-        self.w_qkv = torch.cat([q.to(dt), k.to(dt), v.to(dt)], dim=0).contiguous()
+        if "qkv" in tensors:                       # the loader has laid q, k and v one after another
+            self.w_qkv = tensors["qkv"]
+        else:
+            q, k, v = tensors["q"], tensors["k"], tensors["v"]
+            dt = torch.float32 if torch.float32 in (q.dtype, k.dtype, v.dtype) else q.dtype
+            self.w_qkv = torch.cat([q.to(dt), k.to(dt), v.to(dt)], dim=0).contiguous()
         self.w_o = tensors["o"]
         self.b_qkv = None
         if all(n in tensors for n in ("q_bias", "k_bias", "v_bias")):
@@ -93,11 +99,13 @@ class GQAttention(Mixer):
         T = ctx.T
         qkv = rt.workspace.get("attn.qkv", (rt.max_tokens, self.qkv_size), rt.dtype)[:T]
         linear(x, self.w_qkv, qkv)
+        op_mark(ctx, "qkv_proj", self.w_qkv, T)
         attn = self._attend(qkv, ctx, cache)
         out = rt.workspace.get("mixer.out", (rt.max_tokens, p.hidden_size), rt.dtype)[:T]
         linear(attn, self.w_o, out)
         if self.b_o is not None:
             kernels.add_bias(out, self.b_o)
+        op_mark(ctx, "o_proj", self.w_o, T)
         return out
 
     def forward_into(self, residual, norm, ctx, cache: Optional[LayerCache], state=None) -> bool:
@@ -120,10 +128,12 @@ class GQAttention(Mixer):
             kernels.gemm_skinny(self.w_qkv, qkv, kernels.EPI_BF16, T, x=xn)
         else:
             kernels.gemm_skinny(self.w_qkv, qkv, kernels.EPI_BF16, T, residual=residual, norm_w=rms[0], eps=rms[1])
+        op_mark(ctx, "norm+qkv_proj", self.w_qkv, T)
         attn = self._attend(qkv, ctx, cache)
         out = norm_handover(self, "attn", ctx, residual.shape[1], kernels.SKINNY_UNSTAGED_ROWS) if small else None
         kernels.gemm_skinny(self.w_o, residual, kernels.EPI_ADD_RESIDUAL, T, x=attn,
                             hand_out=None if out is None else (out.norm.rms_params()[0], out.xw, out.sums))
+        op_mark(ctx, "o_proj+add", self.w_o, T)
         ctx.hand_out = out
         return True
 
@@ -163,19 +173,34 @@ class GQAttention(Mixer):
                                          ctx.num_decode, p.num_heads, p.num_kv_heads, p.head_dim, rt.page_size,
                                          p.window, self.scale, tables[0], tables[1], self.q_size,
                                          self.q_size + self.kv_size, ctx.status)
+                self._mark_attention(ctx, "rope+kv_write+attention_decode", "decode")
                 return attn
         if tables is None:
             self.position.apply(qkv, p.num_heads, p.num_kv_heads, p.head_dim, ctx)
         cos, sin = tables if tables is not None else (None, None)
         kernels.rope_kv_write(qkv, ctx.positions, g.slots if cache.write else None, cos, sin, cache.k, cache.v,
                               p.num_heads, p.num_kv_heads, p.head_dim, rt.page_size, ctx.status, tokens=T)
+        if ctx.profiler is not None:
+            elem = qkv.element_size()
+            ctx.profiler.mark("rope+kv_write", T * (2.0 * (self.q_size + self.kv_size) + 3.0 * self.kv_size) * elem, 0.0)
         if ctx.num_decode > 0:
             kernels.attn_decode(qkv, self.qkv_size, cache.k, cache.v, g.block_table, ctx.decode_info,
                                 part_o, part_ml, ctx.decode_parts, self._counters(ctx.max_items), attn,
                                 ctx.num_decode, p.num_heads, p.num_kv_heads, p.head_dim, rt.page_size,
                                 p.window, self.scale)
+            self._mark_attention(ctx, "attention_decode", "decode")
         if ctx.num_tiles > 0:
             kernels.attn_prefill(qkv, self.qkv_size, cache.k, cache.v, g.block_table, ctx.tile_seq,
                                  ctx.tile_tok, ctx.tile_rows, ctx.positions, attn, ctx.num_tiles, p.num_heads,
                                  p.num_kv_heads, p.head_dim, rt.page_size, p.window, self.scale)
+            self._mark_attention(ctx, "attention_prefill", "prefill")
         return attn
+
+    def _mark_attention(self, ctx, op: str, which: str) -> None:
+        if ctx.profiler is None:
+            return
+        from ..engine.profiler import attention_work
+        p = self.params
+        elem = 2 if self.rt.dtype == torch.bfloat16 else 4
+        nbytes, flops = attention_work(ctx.host, p.num_heads, p.num_kv_heads, p.head_dim, p.window, elem)[which]
+        ctx.profiler.mark(op, nbytes, flops)

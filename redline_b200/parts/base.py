@@ -122,8 +122,15 @@ class Part:
         """Own tensor name -> what is expected of it."""
         return {}
 
+    def fused(self) -> Dict[str, List[str]]:
+        """Own name of a fused tensor -> the names (of ``tensors()``) whose tensors the part uses as one,
+        laid one after another along their first axis.  The loader then puts them so on the device and
+        ``load`` receives the fused name in place of the members (if the checkpoint has all of them)."""
+        return {}
+
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
-        """Receives the tensors of ``tensors()`` that the checkpoint had, on the device."""
+        """Receives the tensors of ``tensors()`` that the checkpoint had, on the device (and those of
+        ``fused()`` in place of their members)."""
 
     def nbytes(self) -> int:
         return 0
@@ -172,6 +179,22 @@ def norm_handover(part: "Part", name: str, ctx, width: int, rows: int) -> Option
     ws = part.rt.workspace
     return NormHandover(norm, ws.get(name + ".hand_xw", (rows, width), torch.bfloat16),
                         ws.get(name + ".hand_sums", (rows, (width + 15) // 16), torch.float32))
+
+
+def op_mark(ctx, op: str, weight: Optional[torch.Tensor] = None, rows: int = 0, nbytes: float = 0.0,
+            flops: float = 0.0) -> None:
+    """Tells the step's per-op profiler (``ctx.profiler``, None unless per-op profiling is on) that ``op``
+    has been enqueued.  For a product with ``weight`` [N, K] over ``rows`` rows the bytes and operations are
+    worked out here; other ops pass their own."""
+    prof = getattr(ctx, "profiler", None)
+    if prof is None:
+        return
+    if weight is not None:
+        n, k = weight.shape
+        elem = weight.element_size()
+        nbytes += float(weight.numel() * elem + rows * (n + k) * elem)
+        flops += 2.0 * rows * n * k
+    prof.mark(op, nbytes, flops)
 
 
 class PositionEncoding(Part):

@@ -4,7 +4,7 @@ feed-forward stops after the first half."""
 
 from __future__ import annotations
 
-from .base import Block, register
+from .base import Block, op_mark, register
 
 
 @register("block", "prenorm")
@@ -43,6 +43,7 @@ class PreNormBlock(Block):
             hand = None
             x = rt.workspace.get("block.normed", (rt.max_tokens, residual.shape[1]), rt.dtype)[:T]
             self.mixer_norm.add_norm(residual, pending, x, rows=T)
+            op_mark(ctx, "add+rmsnorm", nbytes=self._norm_bytes(residual, pending, x))
             a = self.mixer.forward(x, ctx, cache, state)
         if self.ffn is None:               # a layer with a mixer only: its output is what is left to add
             ctx.block_hand = hand if a is None else None
@@ -56,4 +57,14 @@ class PreNormBlock(Block):
         if x is None:
             x = rt.workspace.get("block.normed", (rt.max_tokens, residual.shape[1]), rt.dtype)[:T]
         self.ffn_norm.add_norm(residual, a, x, rows=T)
+        op_mark(ctx, "add+rmsnorm", nbytes=self._norm_bytes(residual, a, x))
         return self.ffn.forward(x, ctx)
+
+    @staticmethod
+    def _norm_bytes(residual, delta, out) -> float:
+        """The stream read (and written back when something is added), the addend read, the normed rows written."""
+        n = residual.numel() * residual.element_size() * (2 if delta is not None else 1)
+        n += out.numel() * out.element_size()
+        if delta is not None:
+            n += delta.numel() * delta.element_size()
+        return float(n)

@@ -11,7 +11,7 @@ import torch
 
 from ..ops import kernels
 from ..ops.linear import linear
-from .base import FeedForward, norm_handover, register
+from .base import FeedForward, norm_handover, op_mark, register
 from .spec import TensorSpec
 
 
@@ -40,10 +40,16 @@ class SwiGLUMLP(FeedForward):
             "down_bias": TensorSpec((p.hidden_size,), optional=not p.bias),
         }
 
+    def fused(self) -> Dict[str, list]:
+        return {"gate_up": ["gate", "up"]}
+
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
-        g, u = tensors["gate"], tensors["up"]
-        dt = torch.float32 if torch.float32 in (g.dtype, u.dtype) else g.dtype
-        self.w_gate_up = torch.cat([g.to(dt), u.to(dt)], dim=0).contiguous()
+        if "gate_up" in tensors:                   # the loader has laid gate and up one after another
+            self.w_gate_up = tensors["gate_up"]
+        else:
+            g, u = tensors["gate"], tensors["up"]
+            dt = torch.float32 if torch.float32 in (g.dtype, u.dtype) else g.dtype
+            self.w_gate_up = torch.cat([g.to(dt), u.to(dt)], dim=0).contiguous()
         self.w_down = tensors["down"]
         self.b_gate_up = None
         if "gate_bias" in tensors and "up_bias" in tensors:
@@ -68,10 +74,12 @@ class SwiGLUMLP(FeedForward):
             if self.b_gate_up is not None:
                 kernels.add_bias(gu, self.b_gate_up)
             kernels.swiglu(gu, act)
+        op_mark(ctx, "gate_up+swiglu", self.w_gate_up, T)
         out = ws.get("ffn.out", (rt.max_tokens, p.hidden_size), rt.dtype)[:T]
         linear(act, self.w_down, out)
         if self.b_down is not None:
             kernels.add_bias(out, self.b_down)
+        op_mark(ctx, "down_proj", self.w_down, T)
         return out
 
     def forward_into(self, residual, norm, ctx) -> bool:
@@ -97,8 +105,10 @@ class SwiGLUMLP(FeedForward):
         else:
             kernels.gemm_skinny(self.w_gate_up, act, kernels.EPI_SWIGLU, T, residual=residual, norm_w=rms[0],
                                 eps=rms[1])
+        op_mark(ctx, "norm+gate_up+swiglu", self.w_gate_up, T)
         out = norm_handover(self, "ffn", ctx, residual.shape[1], kernels.SKINNY_UNSTAGED_ROWS) if small else None
         kernels.gemm_skinny(self.w_down, residual, kernels.EPI_ADD_RESIDUAL, T, x=act,
                             hand_out=None if out is None else (out.norm.rms_params()[0], out.xw, out.sums))
+        op_mark(ctx, "down_proj+add", self.w_down, T)
         ctx.hand_out = out
         return True

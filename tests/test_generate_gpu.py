@@ -194,6 +194,60 @@ def test_benchmark_harness_report(models, tmp_path):
     assert rep["workload"] == "synthetic_n3_in16_out6" and rep["output_tokens"] == 18 and len(rep["requests"]) == 3
 
 
+@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
+def test_per_op_profile_of_engine_steps(dtype, models, tmp_path):
+    """--profile-ops: CUDA events between the ops of eager steps give a table per kind of step with
+    every op of a layer, their calls per step, shares that add up, and roofline fractions; the tokens
+    are those of an unprofiled run; NVTX ranges and memory tracking can be on meanwhile (reference:
+    src/cuda/op_profiler.h:21-103, apps/redline_bench.cpp:39-49, apps/cli_common.cpp:89-90)."""
+    from redline_b200.apps.harness import BenchOptions, parse_workload, run_benchmark
+    from redline_b200.engine.engine import Engine
+    from redline_b200.engine.profiler import format_op_profile
+    d, _ = models["tiny_a"]
+    layers = C.TINY_A["num_hidden_layers"]
+    doc = {"name": "t", "requests": [{"prompt_len": 20 + 7 * i, "max_new_tokens": 10} for i in range(5)]}
+    outs = {}
+    for profile in (False, True):
+        eng = Engine(d, dtype=dtype, max_num_seqs=4, max_num_batched_tokens=64, max_seq_len=256, kv_cache_tokens=1024,
+                     nvtx_layers=profile, track_memory=profile)
+        w = parse_workload(doc, eng.vocab_size)
+        rep = run_benchmark(eng, w, BenchOptions(warmup_requests=1, profile_ops=profile, hbm_gbs=6500.0, bf16_tflops=1600.0))
+        outs[profile] = rep
+        if not profile:
+            assert "op_profile" not in rep and rep["cuda_graph_step_fraction"] > 0
+            continue
+        assert rep["cuda_graph_step_fraction"] == 0                    # profiled steps are eager
+        assert rep["memory"]["peak_device_used_bytes"] >= rep["memory"]["weights"]
+        rows = rep["op_profile"]
+        by_scope = {}
+        for r in rows:
+            scope, op = r["op"].split("/", 1)
+            by_scope.setdefault(scope, {})[op] = r
+            assert r["ms_per_pass"] > 0 and r["calls_per_pass"] > 0
+        assert "decode" in by_scope and ("prefill" in by_scope or "mixed" in by_scope)
+        for scope, ops in by_scope.items():
+            assert abs(sum(r["pct"] for r in ops.values()) - 100.0) < 1e-6
+            assert ops["embed"]["calls_per_pass"] == 1 and ops["sample"]["calls_per_pass"] == 1
+            per_layer = [o for o in ops if "qkv_proj" in o or "o_proj" in o or "gate_up" in o or "down_proj" in o]
+            assert len(per_layer) == 4 and all(ops[o]["calls_per_pass"] == layers for o in per_layer), (scope, list(ops))
+            assert any("attention" in o for o in ops) and any("lm_head" in o for o in ops)
+            products = [ops[o] for o in per_layer]
+            assert all(r["gflop_per_pass"] > 0 and r["gbytes_per_pass"] > 0 and 0 < r["roofline_frac"] < 1.5 for r in products)
+        text = format_op_profile(rows)
+        assert "decode: per-op device time" in text and "of roofline" in text
+    assert outs[True]["output_tokens"] == outs[False]["output_tokens"] == 50
+    # the program's flag
+    out = tmp_path / "rep.json"
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "redline_bench"), "--model", d, "--synthetic", "3,16,6",
+                        "--max-seqs", "4", "--max-seq-len", "128", "--kv-cache-tokens", "512", "--out", str(out),
+                        "--profile-ops", "--nvtx-layers", "--track-memory", "--dtype", dtype],
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert "per-op device time" in r.stderr
+    rep = json.loads(out.read_text())
+    assert rep["op_profile"] and rep["engine"]["config"]["nvtx_layers"] and rep["engine"]["config"]["track_memory"]
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["tiny_a", "tiny_b"])
 def test_logits_of_generation_with_graphs_and_tokens_fed_on_the_device(name, dtype, tmp_path):

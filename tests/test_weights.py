@@ -108,6 +108,31 @@ def test_dtypes_kept_and_head_tied(tmp_path):
     assert ma.head.weight.data_ptr() == ma.embedding.weight.data_ptr()
 
 
+def test_weights_lie_in_one_allocation_with_fused_tensors_side_by_side(tmp_path):
+    """Every weight is a view of one allocation; q, k and v (and gate and up) are laid one after another
+    there, so the fused tensors a layer multiplies by cost no second copy; a member stored in 32-bit
+    makes its fused tensor 32-bit."""
+    w = P.random_weights(C.TINY_B, 2, dtype=torch.bfloat16)
+    w["model.layers.1.self_attn.k_proj.weight"] = w["model.layers.1.self_attn.k_proj.weight"].float()
+    P.write_model_dir(str(tmp_path), C.TINY_B, w)
+    m = cpu_model(C.TINY_B)
+    m.load_weights(CheckpointReader(str(tmp_path)))
+    tensors = [m.embedding.weight, m.final_norm.weight]
+    for i, b in enumerate(m.blocks):
+        p = f"model.layers.{i}."
+        qkv = torch.cat([w[p + f"self_attn.{n}_proj.weight"].float() for n in "qkv"])
+        assert torch.equal(b.mixer.w_qkv.float(), qkv)
+        gu = torch.cat([w[p + f"mlp.{n}_proj.weight"] for n in ("gate", "up")])
+        assert torch.equal(b.ffn.w_gate_up, gu)
+        assert b.mixer.w_qkv.dtype == (torch.float32 if i == 1 else torch.bfloat16)
+        tensors += [b.mixer.w_qkv, b.mixer.w_o, b.ffn.w_gate_up, b.ffn.w_down, b.mixer_norm.weight, b.ffn_norm.weight]
+    base = tensors[0].untyped_storage().data_ptr()
+    assert all(t.untyped_storage().data_ptr() == base for t in tensors)
+    assert all((t.data_ptr() - base) % 256 == 0 and t.is_contiguous() for t in tensors)
+    spans = sorted((t.data_ptr(), t.data_ptr() + t.numel() * t.element_size()) for t in tensors)
+    assert all(a[1] <= b[0] for a, b in zip(spans, spans[1:]))          # no two tensors overlap
+
+
 def test_random_weights_mode_writes_a_loadable_folder(tmp_path):
     c = config_from_dict(C.TINY_A)
     d = write_random_model(str(tmp_path / "m"), c, seed=3)
