@@ -243,3 +243,131 @@ def test_state_keeping_mixer_under_recompute_preemption(tmp_path):
         assert len(o["output_ids"]) == 30 and oracle_greedy(w, table, p, o["output_ids"]), o["id"]
     assert eng.runner.cache.num_open() == 0
     eng.runner.cache.check_invariants()
+
+
+# ---------------------------------------------------------------------------------------------
+# A mixer whose cache is not keys and values: ONE latent vector per token.
+
+Z = 24
+
+
+def register_latent_toy():
+    from redline_b200.parts import CacheSpec, CacheTensor, Mixer, TensorSpec, register
+
+    @register("mixer", "toy_latent_mean")
+    class LatentMean(Mixer):
+        """z_t = W x_t is cached (one tensor "z" of Z numbers per token, no heads); y_t = U mean_{j <= t} z_j."""
+
+        def cache_spec(self):
+            return CacheSpec("full", (CacheTensor("z", (Z,)),))
+
+        def tensors(self):
+            return {"w": TensorSpec((Z, H)), "u": TensorSpec((H, Z))}
+
+        def load(self, tensors):
+            self.w, self.u = tensors["w"].float(), tensors["u"].float()
+
+        def forward(self, x, ctx, cache, state):
+            g = ctx.groups[cache.group]
+            zc = cache.tensors["z"]                                    # [pages, page_size, Z]
+            assert zc.shape[1:] == (self.rt.page_size, Z) and "k" not in cache.tensors
+            T = ctx.T
+            z = x.float() @ self.w.T
+            flat = zc.view(-1, Z)
+            flat[g.slots[:T].long()] = z.to(zc.dtype)
+            out = torch.empty_like(x)
+            for si, (start, n, p) in enumerate(zip(ctx.host.q_start, ctx.host.q_len, ctx.host.start_pos)):
+                blocks = (p + n + self.rt.page_size - 1) // self.rt.page_size
+                seen = zc[g.block_table[si, :blocks].long()].reshape(-1, Z)[:p + n].float()
+                mean = seen.cumsum(0)[p:] / torch.arange(p + 1, p + n + 1, device=x.device)[:, None]
+                out[start:start + n] = (mean @ self.u.T).to(x.dtype)
+            return out
+
+
+def latent_spec():
+    from redline_b200.parts import LayerCall, LayerSpec, ModelSpec, PartSpec
+    from redline_b200.parts.attention import AttentionParams
+    from redline_b200.parts.embedding import EmbeddingParams, HeadParams
+    from redline_b200.parts.mlp import GatedMLPParams
+    from redline_b200.parts.rmsnorm import RMSNormParams
+    from redline_b200.parts.rope import RotaryParams
+    from redline_b200.config.model_config import RopeScaling
+
+    def norm(name):
+        return PartSpec("rmsnorm", RMSNormParams(H, 1e-5), {"weight": name})
+
+    mlp = lambda i: PartSpec("swiglu_mlp", GatedMLPParams(H, I), {n: f"l{i}.mlp.{n}" for n in ("gate", "up", "down")})  # noqa: E731
+    l0 = LayerSpec("prenorm", norm("l0.n1"), PartSpec("toy_latent_mean", None, {"w": "l0.mix.w", "u": "l0.mix.u"}),
+                   norm("l0.n2"), mlp(0))
+    att = AttentionParams(H, HQ, HKV, D, PartSpec("rope", RotaryParams(D, 1e4, RopeScaling(), 256)))
+    l1 = LayerSpec("prenorm", norm("l1.n1"), PartSpec("gqa_attention", att, {n: f"l1.att.{n}" for n in "qkvo"}))   # no feed-forward
+    return ModelSpec(H, V, 256, PartSpec("token_embedding", EmbeddingParams(V, H), {"weight": "emb"}),
+                     (l0, l1), (LayerCall(0), LayerCall(1)), norm("fn"),
+                     PartSpec("lm_head", HeadParams(V, H, True), {"weight": "head"}))
+
+
+def latent_oracle(w, toks):
+    T = len(toks)
+    h = w["emb"][toks].double()
+    z = P.rmsnorm(h, w["l0.n1"], 1e-5) @ w["l0.mix.w"].double().T
+    mean = z.cumsum(0) / torch.arange(1, T + 1, dtype=torch.float64)[:, None]
+    h = h + mean @ w["l0.mix.u"].double().T
+    x = P.rmsnorm(h, w["l0.n2"], 1e-5)
+    h = h + P.linear(P.swiglu(P.linear(x, w["l0.mlp.gate"]), P.linear(x, w["l0.mlp.up"])), w["l0.mlp.down"])
+    x = P.rmsnorm(h, w["l1.n1"], 1e-5)
+    pc = P.PlainConfig(V, H, I, 2, HQ, HKV, D, 1e-5, 1e4, None, True, 256)
+    cos, sin = P.rope_tables(pc, T)
+    q = P.rope_rotate(P.linear(x, w["l1.att.q"]).view(T, HQ, D), cos, sin)
+    k = P.rope_rotate(P.linear(x, w["l1.att.k"]).view(T, HKV, D), cos, sin)
+    v = P.linear(x, w["l1.att.v"]).view(T, HKV, D)
+    h = h + P.linear(P.causal_attention(q, k, v, D ** -0.5).reshape(T, -1), w["l1.att.o"])     # the layer has no feed-forward
+    return (P.rmsnorm(h, w["fn"], 1e-5) @ w["emb"].double().T).numpy()                         # tied head
+
+
+def test_a_cache_that_is_not_keys_and_values_and_a_layer_without_a_feed_forward(tmp_path):
+    """Two cache groups with tensors of different shapes in one model (a latent vector per token beside
+    keys and values), each with pages and block tables of its own; a layer that has a mixer only; a head
+    tied to the embedding.  Stepped in portions beside single tokens in a pool so small that pages are
+    handed out again, against a restatement in float64."""
+    from redline_b200.config import EngineConfig
+    from redline_b200.config.model_config import ModelConfig
+    from redline_b200.engine.engine import Engine
+    from redline_b200.engine.runner import ModelRunner
+    register_latent_toy()
+    g = torch.Generator().manual_seed(7)
+    r = lambda *s: (torch.randn(*s, generator=g) * 0.2).to(torch.bfloat16).float()  # noqa: E731
+    n = lambda: (1 + 0.1 * torch.randn(H, generator=g)).to(torch.bfloat16).float()  # noqa: E731
+    w = {"emb": r(V, H), "fn": n(), "l0.n1": n(), "l0.n2": n(), "l1.n1": n(), "l0.mix.w": r(Z, H), "l0.mix.u": r(H, Z),
+         "l0.mlp.gate": r(I, H), "l0.mlp.up": r(I, H), "l0.mlp.down": r(H, I),
+         "l1.att.q": r(HQ * D, H) * 4, "l1.att.k": r(HKV * D, H) * 4, "l1.att.v": r(HKV * D, H), "l1.att.o": r(H, HQ * D)}
+    d = str(tmp_path / "latent")
+    os.makedirs(d)
+    P.write_safetensors(os.path.join(d, "model.safetensors"), w)
+    cfg = EngineConfig.from_options(d, dict(dtype="float32", kv_cache_tokens=192, max_seq_len=160, max_num_seqs=3,
+                                            max_num_batched_tokens=128, max_logit_rows=128, cuda_graphs=False,
+                                            async_scheduling=False))
+    runner = ModelRunner(cfg, ModelConfig("LatentToyForTests", V, H, 256, -1, ()), latent_spec())
+    eng = Engine.from_runner(runner)
+    assert [[(t.name, t.shape) for t in grp.spec.tensors] for grp in runner.groups] == \
+        [[("z", (Z,))], [("k", (HKV, D)), ("v", (HKV, D))]]
+    assert runner.model.blocks[1].ffn is None and runner.model.head.weight.data_ptr() == runner.model.embedding.weight.data_ptr()
+    rng = np.random.RandomState(5)
+    seqs = {k: rng.randint(0, V, n_).tolist() for k, n_ in (("a", 90), ("b", 61), ("c", 70))}
+    refs = {k: latent_oracle(w, t) for k, t in seqs.items()}
+    got = {k: [] for k in seqs}
+    pos = {k: 0 for k in seqs}
+    for step in [{"a": 33, "b": 1}, {"a": 2, "b": 1}, {"a": 1, "b": 17}, {"a": 40, "b": 1}, {"a": 14, "b": 41}]:
+        out = eng.step_tokens([(k, seqs[k][pos[k]:pos[k] + m], list(range(m))) for k, m in step.items()]).cpu().numpy()
+        at = 0
+        for k, m in step.items():
+            got[k].append(out[at:at + m])
+            at += m
+            pos[k] += m
+    eng.close_request("a"), eng.close_request("b")
+    out = eng.step_tokens([("c", seqs["c"], list(range(70)))]).cpu().numpy()       # on pages that a and b gave back
+    got["c"].append(out)
+    eng.close_request("c")
+    for k in seqs:
+        assert rel_max(np.concatenate(got[k]), refs[k]) < 1e-4, k
+    runner.cache.check_invariants()
+    assert runner.cache.num_open() == 0
