@@ -103,6 +103,28 @@ def test_linear_bfloat16(M, N, K):
     close(linear(x, w, yf), ref, 1e-4)
 
 
+@pytest.mark.parametrize("M,N,K", [(64, 2048, 8192), (2048, 2048, 2048), (24, 3072, 2048), (300, 8192, 2048)])
+def test_library_products_accumulate_in_float32(M, N, K):
+    """Products of more than 16 rows are library calls.  The engine pins them to float32 accumulation all
+    the way (no bfloat16 reduction of the parts of a split k dimension, no TF32): the float32 result is the
+    float64 product to within float32 sums, and the bfloat16 result is the ROUNDED float64 product in all
+    but the few elements whose value lies on a rounding boundary (a reduction in bfloat16 would move one
+    element in ten)."""
+    from redline_b200.engine.runner import pin_library_products
+    pin_library_products()
+    g = torch.Generator(device="cuda").manual_seed(M + N + K)
+    x = torch.randn(M, K, device=DEV, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, device=DEV, generator=g) * 0.02).to(torch.bfloat16)
+    ref = x.double() @ w.double().T
+    yf = torch.empty(M, N, device=DEV, dtype=torch.float32)
+    close(linear(x, w, yf), ref, 2e-6 * math.sqrt(K / 2048) + 2e-6)
+    y = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    linear(x, w, y)
+    moved = (y != ref.to(torch.bfloat16)).float().mean().item()
+    assert moved < 2e-3, f"{moved:.2%} of the bfloat16 results are not the rounded exact product"
+    assert not torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction and not torch.backends.cuda.matmul.allow_tf32
+
+
 def plain_rope_tables(D, theta, num_pos, scaling=None):
     """cos / sin [num_pos, D / 2] in float32 from the oracle's own table builder (not the product's)."""
     pc = P.PlainConfig(vocab_size=0, hidden_size=0, intermediate_size=0, num_layers=0, num_heads=0, num_kv_heads=0,
