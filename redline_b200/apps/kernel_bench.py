@@ -165,19 +165,25 @@ def bench_gemm_tc(args) -> None:
 def bench_gemm_mid(args) -> None:
     dev = "cuda"
     M, N, K = args.rows, args.n, args.k
-    epi = {"bf16": kernels.EPI_BF16, "swiglu": kernels.EPI_SWIGLU}[args.epilogue]
+    epi = {"bf16": kernels.EPI_BF16, "swiglu": kernels.EPI_SWIGLU, "residual": kernels.EPI_ADD_RESIDUAL}[args.epilogue]
     wn = 2 * N if epi == kernels.EPI_SWIGLU else N
     copies = max(2, min(args.copies, int(1e9 // (wn * K * 2))))
     ws = [(torch.randn(wn, K, device=dev) * 0.02).to(torch.bfloat16) for _ in range(copies)]
     x = torch.randn(M, K, device=dev).to(torch.bfloat16)
     y = torch.zeros(M, N, device=dev, dtype=torch.bfloat16)
     yl = torch.empty(M, wn, device=dev, dtype=torch.bfloat16)
+    res = torch.zeros(M, N, device=dev)
+    nw = torch.ones(N, device=dev, dtype=torch.bfloat16)
+    out = (nw,) + kernels.mid_handover_buffers(N, dev) if args.hand_out else None
+    sums_in = torch.ones(M, kernels.mid_sum_columns(K), device=dev) if args.hand_in else None
 
     def fn(i):
         if args.library:
             torch.mm(x, ws[i % copies].t(), out=yl)
+        elif epi == kernels.EPI_ADD_RESIDUAL:
+            kernels.gemm_mid(x, ws[i % copies], None, epi, residual=res, hand_out=out)
         else:
-            kernels.gemm_mid(x, ws[i % copies], y, epi)
+            kernels.gemm_mid(x, ws[i % copies], y, epi, hand_in=sums_in, eps=1e-5)
 
     us = graph_time_us(fn, copies, use_graph=not args.no_graph)
     nbytes = wn * K * 2
@@ -254,7 +260,9 @@ def main() -> int:
             p.add_argument("--rows", type=int, default=64)
             p.add_argument("--n", type=int, default=3072)
             p.add_argument("--k", type=int, default=2048)
-            p.add_argument("--epilogue", default="bf16", choices=["bf16", "swiglu"])
+            p.add_argument("--epilogue", default="bf16", choices=["bf16", "swiglu", "residual"])
+            p.add_argument("--hand-out", action="store_true", help="with --epilogue residual: hand the next norm over")
+            p.add_argument("--hand-in", action="store_true", help="take a norm that was handed over")
             p.add_argument("--library", action="store_true", help="time the library product instead")
     args = ap.parse_args()
     if not torch.cuda.is_available():

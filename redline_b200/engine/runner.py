@@ -29,7 +29,8 @@ from ..weights.safetensors_io import CheckpointReader
 from .batch import BatchBuilder, Segment, StepContext
 from .model import DecoderModel
 
-GRAPH_BUCKETS = (1, 2, 4, 8, 12, 16, 24, 32, 48, 64, 96, 128, 160, 192, 256)
+GRAPH_BUCKETS = (1, 2, 4, 8, 12, 16, 24, 32, 48, 64, 96, 128, 160, 192, 256, 384, 512)
+GRAPH_MAX_ROWS = 1024          # no graph is captured for more rows than this
 STATUS_MESSAGES = {1: "a token id outside the vocabulary", 2: "a position beyond the rotary table",
                    4: "a cache slot beyond the pool"}
 
@@ -185,7 +186,8 @@ class ModelRunner:
         for b in GRAPH_BUCKETS:
             if n <= b <= self.cfg.max_num_seqs:
                 return b
-        return 0
+        # more sequences than the largest bucket within the limit: the limit itself is the last bucket
+        return self.cfg.max_num_seqs if n <= self.cfg.max_num_seqs <= GRAPH_MAX_ROWS else 0
 
     def _capture(self, bucket: int, ctx: StepContext) -> torch.cuda.CUDAGraph:
         # The graph always resolves device-fed ids (token_src is -1 where there are none),

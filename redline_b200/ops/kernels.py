@@ -8,6 +8,7 @@ compiled extension these functions raise.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_float, c_int, c_longlong, c_uint, c_void_p
 from typing import Dict, Optional, Tuple
 
@@ -295,7 +296,6 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, epilogue: int = E
 # ------------------------------------------------- tcgen05 gemm for 17 to 128 rows
 
 MID_MAX_ROWS = 128
-_mid_scratch: Dict[int, Tuple[torch.Tensor, torch.Tensor]] = {}
 
 
 def gemm_mid_ok(rows: int, x: torch.Tensor, w: torch.Tensor) -> bool:
@@ -304,45 +304,87 @@ def gemm_mid_ok(rows: int, x: torch.Tensor, w: torch.Tensor) -> bool:
     return 0 < rows <= MID_MAX_ROWS and gemm_tc_ok(x, w)
 
 
-def _mid_workspace(device: torch.device, floats: int, counters: int) -> Tuple[torch.Tensor, torch.Tensor]:
-    """The scratch area of the split products and their arrival counters (zero between launches), shared
-    by all products of a device (launches on a stream run one after another) and of a fixed size, so that
-    CUDA graphs keep pointing at it: a split product has at most one partial tile of 128 x 128 per SM."""
-    i = device.index if device.index is not None else torch.cuda.current_device()
-    if i not in _mid_scratch:
-        _mid_scratch[i] = (torch.empty(sm_count(device) * 128 * 128, dtype=torch.float32, device=device),
-                           torch.zeros(1 << 16, dtype=torch.int32, device=device))
-    part, cnt = _mid_scratch[i]
-    if part.numel() < floats or cnt.numel() < counters:
-        raise KernelError("gemm_mid: the product needs more scratch than the package keeps")
-    return part, cnt
+MID_ROUTED_ROWS = 64
 
 
-def gemm_mid(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, epilogue: int = EPI_BF16) -> None:
-    """y = epilogue(x @ w^T) for up to 128 rows with tcgen05 tensor cores (csrc/gemm_mid.cu): the weight
-    rows are the 128-row operand, the tokens the narrow one, K is split over CTAs and the partial tiles
-    are added in a fixed order.  bfloat16 x [M, K], w [N, K] (EPI_SWIGLU: [2 N, K], gate rows then up
-    rows), y bfloat16 [M, N]; epilogue EPI_BF16 or EPI_SWIGLU.
+def mid_rows(rows: int, *weights: torch.Tensor) -> bool:
+    """Whether a part should take ``rows`` rows with gemm_mid products over these weights: at most 64 rows
+    (measured on a B200 with 1B-model weights, decode steps of 32 / 48 / 64 sequences: 1.21 / 1.33 / 1.253 ms
+    against 1.23 / 1.36 / 1.267 with the library's products and separate norm and SwiGLU kernels; at 96 and
+    128 rows 1.72 / 1.91 against 1.67 / 1.90, so those stay with the library), bfloat16 weights with 16-byte
+    aligned rows.  ``REDLINE_MID_PRODUCTS=0`` says no (for comparisons)."""
+    if rows <= 0 or rows > MID_ROUTED_ROWS or os.environ.get("REDLINE_MID_PRODUCTS", "1") == "0":
+        return False
+    return all(w.dtype == torch.bfloat16 and w.is_contiguous() and w.shape[1] % 8 == 0 and w.data_ptr() % 16 == 0
+               for w in weights)
 
-    The engine does not route any product here yet: at 64 rows the library's kernels are faster (measured
-    on a B200, weights of 1B-model size: 10.8 / 11.9 / 16.4 / 20.1 us for the qkv, o, down and gated
-    gate/up shapes against 5.7 / 5.4 / 12.8 / 12.5 + 3.6 us)."""
-    _need_cuda(x, w, y)
+
+def mid_handover_buffers(width: int, device) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Buffers for a norm handed over between two gemm_mid products: xw [128, width] bfloat16 and the
+    per-feature-tile sums of squares [128, ceil(width / 128)] float32."""
+    return (torch.zeros((MID_MAX_ROWS, width), dtype=torch.bfloat16, device=device),
+            torch.zeros((MID_MAX_ROWS, mid_sum_columns(width)), dtype=torch.float32, device=device))
+
+
+def mid_sum_columns(width: int) -> int:
+    return (width + 127) // 128
+
+
+def gemm_mid(x: torch.Tensor, w: torch.Tensor, y: Optional[torch.Tensor], epilogue: int = EPI_BF16,
+             residual: Optional[torch.Tensor] = None,
+             hand_out: Optional[Tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = None,
+             hand_in: Optional[torch.Tensor] = None, eps: float = 0.0) -> None:
+    """epilogue(x @ w^T) for up to 128 rows with tcgen05 tensor cores (csrc/gemm_mid.cu): the weight rows
+    are the 128-row operand, the tokens the narrow one, K is split over the CTAs of a thread-block cluster
+    and the partial tiles are added through distributed shared memory in a fixed order.  bfloat16 x [M, K],
+    w [N, K] (EPI_SWIGLU: [2 N, K], gate rows then up rows).
+
+    EPI_BF16 / EPI_SWIGLU: y bfloat16 [M, N].  EPI_ADD_RESIDUAL: ``residual`` float32 [M, N] += the product
+    (y is not used); with ``hand_out = (next_norm_weight, xw, sums)`` (buffers of ``mid_handover_buffers``)
+    it also leaves xw = bfloat16(residual * weight) and the sums of residual^2 per feature tile.  A product
+    called with ``x = xw``, ``hand_in = sums`` and the norm's ``eps`` scales row m of its result by
+    rsqrt(sums[m].sum() / K + eps): the product of the normed stream."""
     lib = _lib("gemm_mid", "gemm_mid.cu")
-    f = _fn(lib, "rl_gemm_mid", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
-                                 c_void_p, c_void_p, c_int, c_void_p])
-    size = _fn(lib, "rl_gemm_mid_workspace", [c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+    f = _fn(lib, "rl_gemm_mid",
+            [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_int,
+             c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_void_p, c_void_p])
     M, K = x.shape
     gated = epilogue == EPI_SWIGLU
     N = w.shape[0] // 2 if gated else w.shape[0]
-    if (epilogue not in (EPI_BF16, EPI_SWIGLU) or w.shape[1] != K or y.dtype != torch.bfloat16 or y.shape[1] != N
-            or y.stride(1) != 1 or not gemm_mid_ok(M, x, w)):
-        raise KernelError(f"gemm_mid: shapes x{tuple(x.shape)} w{tuple(w.shape)} y{tuple(y.shape)} {y.dtype}")
-    floats, counters = ctypes.c_longlong(0), ctypes.c_int(0)
-    size(M, N, K, 1 if gated else 0, sm_count(x.device), ctypes.byref(floats), ctypes.byref(counters))
-    part, cnt = _mid_workspace(x.device, floats.value, counters.value)
-    _check(f(_ptr(x), x.stride(0), _ptr(w), _ptr(y), y.stride(0), epilogue, M, N, K, _ptr(part), _ptr(cnt),
-             _ptr(tc_status(x.device)), sm_count(x.device), _stream()), "gemm_mid")
+    if epilogue not in (EPI_BF16, EPI_SWIGLU, EPI_ADD_RESIDUAL) or w.shape[1] != K or not gemm_mid_ok(M, x, w):
+        raise KernelError(f"gemm_mid: shapes x{tuple(x.shape)} w{tuple(w.shape)} epilogue {epilogue}")
+    if epilogue == EPI_ADD_RESIDUAL:
+        _need_cuda(x, w, residual)
+        if (residual is None or residual.dtype != torch.float32 or residual.shape[0] < M or residual.shape[1] != N
+                or residual.stride(1) != 1 or residual.stride(0) % 4 != 0):
+            raise KernelError("gemm_mid: EPI_ADD_RESIDUAL needs residual float32 [M, N] with 16-byte aligned rows")
+    else:
+        _need_cuda(x, w, y)
+        if (y is None or y.dtype != torch.bfloat16 or y.shape[0] < M or y.shape[1] != N or y.stride(1) != 1
+                or hand_out is not None):
+            raise KernelError(f"gemm_mid: y must be bfloat16 [M, {N}] (and only EPI_ADD_RESIDUAL hands a norm out)")
+    norm_w = xw = sums_out = None
+    if hand_out is not None:
+        norm_w, xw, sums_out = hand_out
+        if (norm_w.numel() != N or norm_w.dtype not in (torch.bfloat16, torch.float32) or not norm_w.is_contiguous()
+                or xw.dtype != torch.bfloat16 or xw.shape[0] < M or xw.shape[1] != N or xw.stride(1) != 1
+                or sums_out.dtype != torch.float32 or sums_out.shape[0] < M or sums_out.stride(1) != 1
+                or sums_out.shape[1] < mid_sum_columns(N)):
+            raise KernelError("gemm_mid: hand_out needs a norm weight [N], xw bfloat16 [M, N] and sums float32 "
+                              "[M, ceil(N / 128)]")
+    if hand_in is not None:
+        if hand_in.dtype != torch.float32 or hand_in.shape[0] < M or hand_in.stride(1) != 1 or hand_in.shape[1] < 1:
+            raise KernelError("gemm_mid: hand_in must be float32 [M, n]")
+    _check(f(_ptr(x), x.stride(0), _ptr(w), _ptr(y) if y is not None else None, y.stride(0) if y is not None else 0,
+             epilogue, M, N, K, _ptr(residual) if residual is not None else None,
+             residual.stride(0) if residual is not None else 0,
+             _ptr(norm_w) if norm_w is not None else None,
+             1 if (norm_w is not None and norm_w.dtype == torch.float32) else 0,
+             _ptr(xw) if xw is not None else None, xw.stride(0) if xw is not None else 0,
+             _ptr(sums_out) if sums_out is not None else None, sums_out.stride(0) if sums_out is not None else 0,
+             _ptr(hand_in) if hand_in is not None else None, hand_in.stride(0) if hand_in is not None else 0,
+             hand_in.shape[1] if hand_in is not None else 0, float(eps), _ptr(tc_status(x.device)), _stream()),
+           "gemm_mid")
 
 
 # ------------------------------------------------------------------- attention

@@ -112,9 +112,18 @@ class GQAttention(Mixer):
         rt = self.rt
         T = ctx.T
         rms = norm.rms_params()
-        if (rms is None or self.b_o is not None or rt.dtype != torch.bfloat16
-                or not kernels.skinny_ok(T, self.w_qkv, rt.dtype) or not kernels.skinny_ok(T, self.w_o, rt.dtype)):
+        if rms is None or self.b_o is not None or rt.dtype != torch.bfloat16:
             return False
+        if kernels.skinny_ok(T, self.w_qkv, rt.dtype) and kernels.skinny_ok(T, self.w_o, rt.dtype):
+            return self._into_skinny(residual, rms, ctx, cache)
+        if kernels.mid_rows(T, self.w_qkv, self.w_o):
+            return self._into_mid(residual, rms, ctx, cache)
+        return False
+
+    def _into_skinny(self, residual, rms, ctx, cache) -> bool:
+        """At most 16 rows: products that stream the weights through CUDA cores."""
+        rt = self.rt
+        T = ctx.T
         qkv = rt.workspace.get("attn.qkv", (rt.max_tokens, self.qkv_size), rt.dtype)[:T]
         small = T <= kernels.SKINNY_UNSTAGED_ROWS
         hand = ctx.hand_in if small else None
@@ -133,6 +142,28 @@ class GQAttention(Mixer):
         out = norm_handover(self, "attn", ctx, residual.shape[1], kernels.SKINNY_UNSTAGED_ROWS) if small else None
         kernels.gemm_skinny(self.w_o, residual, kernels.EPI_ADD_RESIDUAL, T, x=attn,
                             hand_out=None if out is None else (out.norm.rms_params()[0], out.xw, out.sums))
+        op_mark(ctx, "o_proj+add", self.w_o, T)
+        ctx.hand_out = out
+        return True
+
+    def _into_mid(self, residual, rms, ctx, cache) -> bool:
+        """17 to 64 rows: tcgen05 products with the weights as the wide operand; the add to the stream
+        in the second one's epilogue, the norms handed from product to product."""
+        rt = self.rt
+        T = ctx.T
+        qkv = rt.workspace.get("attn.qkv", (rt.max_tokens, self.qkv_size), rt.dtype)[:T]
+        hand = ctx.hand_in
+        if hand is not None and hand.xw.shape[0] >= T:
+            kernels.gemm_mid(hand.xw[:T], self.w_qkv, qkv, kernels.EPI_BF16, hand_in=hand.sums, eps=rms[1])
+        else:
+            xn = rt.workspace.get("attn.xn_mid", (kernels.MID_MAX_ROWS, self.params.hidden_size), rt.dtype)[:T]
+            kernels.add_rmsnorm(residual, None, rms[0], xn, rms[1], rows=T)
+            kernels.gemm_mid(xn, self.w_qkv, qkv, kernels.EPI_BF16)
+        op_mark(ctx, "norm+qkv_proj", self.w_qkv, T)
+        attn = self._attend(qkv, ctx, cache)
+        out = norm_handover(self, "attn.mid", ctx, residual.shape[1], kernels.MID_MAX_ROWS, tile=128)
+        kernels.gemm_mid(attn, self.w_o, None, kernels.EPI_ADD_RESIDUAL, residual=residual,
+                         hand_out=None if out is None else (out.norm.rms_params()[0], out.xw, out.sums))
         op_mark(ctx, "o_proj+add", self.w_o, T)
         ctx.hand_out = out
         return True

@@ -166,10 +166,11 @@ class NormHandover:
     sums: torch.Tensor      # [T, n] float32; a row's sum of squares is sums[row].sum()
 
 
-def norm_handover(part: "Part", name: str, ctx, width: int, rows: int) -> Optional[NormHandover]:
+def norm_handover(part: "Part", name: str, ctx, width: int, rows: int, tile: int = 16) -> Optional[NormHandover]:
     """The hand-over that ``part``'s last product is to fill for ``ctx.next_norm`` (buffers named after
-    ``name`` in the workspace, for up to ``rows`` rows), or None if there is no such norm or it is not an
-    RMSNorm of this width.  ``REDLINE_NORM_HANDOVER=0`` turns hand-overs off (every norm its own kernel)."""
+    ``name`` in the workspace, for up to ``rows`` rows, a sum of squares for every ``tile`` features), or
+    None if there is no such norm or it is not an RMSNorm of this width.  ``REDLINE_NORM_HANDOVER=0`` turns
+    hand-overs off (every norm its own kernel)."""
     norm = ctx.next_norm
     if norm is None or os.environ.get("REDLINE_NORM_HANDOVER", "1") == "0":
         return None
@@ -178,7 +179,7 @@ def norm_handover(part: "Part", name: str, ctx, width: int, rows: int) -> Option
         return None
     ws = part.rt.workspace
     return NormHandover(norm, ws.get(name + ".hand_xw", (rows, width), torch.bfloat16),
-                        ws.get(name + ".hand_sums", (rows, (width + 15) // 16), torch.float32))
+                        ws.get(name + ".hand_sums", (rows, (width + tile - 1) // tile), torch.float32))
 
 
 def op_mark(ctx, op: str, weight: Optional[torch.Tensor] = None, rows: int = 0, nbytes: float = 0.0,

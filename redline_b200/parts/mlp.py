@@ -83,12 +83,21 @@ class SwiGLUMLP(FeedForward):
         return out
 
     def forward_into(self, residual, norm, ctx) -> bool:
-        p, rt = self.params, self.rt
+        rt = self.rt
         T = ctx.T
         rms = norm.rms_params()
-        if (rms is None or self.b_gate_up is not None or self.b_down is not None or rt.dtype != torch.bfloat16
-                or not kernels.skinny_ok(T, self.w_gate_up, rt.dtype) or not kernels.skinny_ok(T, self.w_down, rt.dtype)):
+        if rms is None or self.b_gate_up is not None or self.b_down is not None or rt.dtype != torch.bfloat16:
             return False
+        if kernels.skinny_ok(T, self.w_gate_up, rt.dtype) and kernels.skinny_ok(T, self.w_down, rt.dtype):
+            return self._into_skinny(residual, rms, ctx)
+        if kernels.mid_rows(T, self.w_gate_up, self.w_down):
+            return self._into_mid(residual, rms, ctx)
+        return False
+
+    def _into_skinny(self, residual, rms, ctx) -> bool:
+        """At most 16 rows: products that stream the weights through CUDA cores."""
+        p, rt = self.params, self.rt
+        T = ctx.T
         act = rt.workspace.get("ffn.act", (rt.max_tokens, p.intermediate_size), rt.dtype)[:T]
         small = T <= kernels.SKINNY_UNSTAGED_ROWS
         hand = ctx.hand_in if small else None
@@ -109,6 +118,27 @@ class SwiGLUMLP(FeedForward):
         out = norm_handover(self, "ffn", ctx, residual.shape[1], kernels.SKINNY_UNSTAGED_ROWS) if small else None
         kernels.gemm_skinny(self.w_down, residual, kernels.EPI_ADD_RESIDUAL, T, x=act,
                             hand_out=None if out is None else (out.norm.rms_params()[0], out.xw, out.sums))
+        op_mark(ctx, "down_proj+add", self.w_down, T)
+        ctx.hand_out = out
+        return True
+
+    def _into_mid(self, residual, rms, ctx) -> bool:
+        """17 to 64 rows: tcgen05 products with the weights as the wide operand; the gated activation in
+        the first one's epilogue, the add to the stream in the second one's, the norms handed over."""
+        p, rt = self.params, self.rt
+        T = ctx.T
+        act = rt.workspace.get("ffn.act", (rt.max_tokens, p.intermediate_size), rt.dtype)[:T]
+        hand = ctx.hand_in
+        if hand is not None and hand.xw.shape[0] >= T:
+            kernels.gemm_mid(hand.xw[:T], self.w_gate_up, act, kernels.EPI_SWIGLU, hand_in=hand.sums, eps=rms[1])
+        else:
+            xn = rt.workspace.get("ffn.xn_mid", (kernels.MID_MAX_ROWS, p.hidden_size), rt.dtype)[:T]
+            kernels.add_rmsnorm(residual, None, rms[0], xn, rms[1], rows=T)
+            kernels.gemm_mid(xn, self.w_gate_up, act, kernels.EPI_SWIGLU)
+        op_mark(ctx, "norm+gate_up+swiglu", self.w_gate_up, T)
+        out = norm_handover(self, "ffn.mid", ctx, residual.shape[1], kernels.MID_MAX_ROWS, tile=128)
+        kernels.gemm_mid(act, self.w_down, None, kernels.EPI_ADD_RESIDUAL, residual=residual,
+                         hand_out=None if out is None else (out.norm.rms_params()[0], out.xw, out.sums))
         op_mark(ctx, "down_proj+add", self.w_down, T)
         ctx.hand_out = out
         return True

@@ -69,7 +69,8 @@ def test_modes_give_the_same_tokens(models):
     prompts = [random_tokens(512, n, 70 + n) for n in (40, 46, 41, 44, 45, 43)]
     results = []
     for graphs, asyn, mix in [(False, False, True), (True, True, True), (True, False, False), (False, True, True)]:
-        eng = Engine(d, dtype="float32", max_num_seqs=8, max_num_batched_tokens=64, max_seq_len=256,
+        # (6 sequences at most: no power of two, so the widest decode steps need the limit itself as a graph size)
+        eng = Engine(d, dtype="float32", max_num_seqs=6, max_num_batched_tokens=64, max_seq_len=256,
                      kv_cache_tokens=2048, cuda_graphs=graphs, async_scheduling=asyn, mix_prefill_decode=mix)
         eng.record_steps = True
         outs = eng.generate(prompts, max_new_tokens=24, ignore_eos=True)
@@ -81,7 +82,8 @@ def test_modes_give_the_same_tokens(models):
         else:
             assert "mixed" not in kinds, kinds
         if graphs:
-            assert eng.runner.num_graph_steps > 0 and any(r.cuda_graph for r in eng.records)
+            assert eng.runner.num_graph_steps > 0 and any(r.num_seqs == 6 for r in eng.records)
+            assert all(r.cuda_graph for r in eng.records if r.kind == "decode")
         else:
             assert eng.runner.num_graph_steps == 0
         assert eng.runner.cache.num_open() == 0

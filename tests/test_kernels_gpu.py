@@ -108,8 +108,9 @@ def test_library_products_accumulate_in_float32(M, N, K):
     """Products of more than 16 rows are library calls.  The engine pins them to float32 accumulation all
     the way (no bfloat16 reduction of the parts of a split k dimension, no TF32): the float32 result is the
     float64 product to within float32 sums, and the bfloat16 result is the ROUNDED float64 product in all
-    but the few elements whose value lies on a rounding boundary (a reduction in bfloat16 would move one
-    element in ten)."""
+    but the elements whose value lies within the float32 sum's error of a rounding boundary (at K = 8192
+    the sum is off by about 2e-5 where a bfloat16 step is 8e-3: one element in two hundred; a reduction in
+    bfloat16, off by half a step, would move every third)."""
     from redline_b200.engine.runner import pin_library_products
     pin_library_products()
     g = torch.Generator(device="cuda").manual_seed(M + N + K)
@@ -117,11 +118,12 @@ def test_library_products_accumulate_in_float32(M, N, K):
     w = (torch.randn(N, K, device=DEV, generator=g) * 0.02).to(torch.bfloat16)
     ref = x.double() @ w.double().T
     yf = torch.empty(M, N, device=DEV, dtype=torch.float32)
-    close(linear(x, w, yf), ref, 2e-6 * math.sqrt(K / 2048) + 2e-6)
+    # a float32 sum of K terms, each rounded to 2^-24 of the running sum (a bfloat16 partial sum: 2^-9)
+    close(linear(x, w, yf), ref, 2.0 ** -23 * math.sqrt(K))
     y = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
     linear(x, w, y)
     moved = (y != ref.to(torch.bfloat16)).float().mean().item()
-    assert moved < 2e-3, f"{moved:.2%} of the bfloat16 results are not the rounded exact product"
+    assert moved < 2e-2, f"{moved:.2%} of the bfloat16 results are not the rounded exact product"
     assert not torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction and not torch.backends.cuda.matmul.allow_tf32
 
 
@@ -718,9 +720,10 @@ MID_SHAPES = [(64, 3072, 2048), (17, 2048, 8192), (128, 331, 200), (33, 1000, 72
 
 @pytest.mark.parametrize("M,N,K", MID_SHAPES)
 def test_gemm_mid_epilogues(M, N, K):
-    """The tcgen05 product for up to 128 rows (weights as the wide operand, K split over CTAs) against
-    float64: both epilogues, edge tiles in N and K, every width of the token operand; a second run gives
-    the same bits (the partial tiles are added in a fixed order, the counters are left at zero)."""
+    """The tcgen05 product for up to 128 rows (weights as the wide operand, K split over the CTAs of a
+    cluster) against float64: both storing epilogues, edge tiles in N and K, every width of the token
+    operand, every cluster size from 1 to 8; a second run gives the same bits (the partial tiles are added
+    in a fixed order)."""
     g = torch.Generator(device="cuda").manual_seed(M + N + K)
     x = torch.randn(M + 2, K, device=DEV, generator=g).to(torch.bfloat16)[:M]
     w = (torch.randn(2 * N, K, device=DEV, generator=g) * 0.05).to(torch.bfloat16)
@@ -747,6 +750,61 @@ def test_gemm_mid_epilogues(M, N, K):
     with pytest.raises(kernels.KernelError):
         kernels.gemm_mid(torch.zeros(129, K, device=DEV, dtype=torch.bfloat16), w,
                          torch.zeros(129, 2 * N, device=DEV, dtype=torch.bfloat16))
+
+
+@pytest.mark.parametrize("M,H,N2,K1", [(64, 2048, 3072, 2048), (17, 328, 200, 72), (128, 1000, 96, 8192),
+                                       (33, 4400, 64, 256), (100, 2048, 8192, 8192), (1, 136, 40, 640)])
+@pytest.mark.parametrize("w32", [False, True])
+def test_gemm_mid_residual_epilogue_and_norm_handed_over(M, H, N2, K1, w32):
+    """residual += x W1^T in the product's epilogue, which also leaves bfloat16(residual * norm_weight) and
+    the sums of squares per feature tile; the next product takes them and scales its rows: together the
+    RMSNorm between the two, against float64.  Rows and features beyond the product are not touched."""
+    g = torch.Generator(device="cuda").manual_seed(M + H + N2)
+    x = torch.randn(M, K1, device=DEV, generator=g).to(torch.bfloat16)
+    w1 = (torch.randn(H, K1, device=DEV, generator=g) * 0.05).to(torch.bfloat16)
+    res_all = torch.randn(M + 2, H + 4, device=DEV, generator=g) * 3
+    before = res_all.clone()
+    res = res_all[:M, :H]
+    nw = (1 + 0.1 * torch.randn(H, device=DEV, generator=g)).to(torch.float32 if w32 else torch.bfloat16)
+    w2 = (torch.randn(2 * N2, H, device=DEV, generator=g) * 0.05).to(torch.bfloat16)
+    eps = 1e-5
+    status = kernels.tc_status(x.device)
+    want_res = res.double() + x.double() @ w1.double().T
+    plain = res.clone()
+    kernels.gemm_mid(x, w1, None, kernels.EPI_ADD_RESIDUAL, residual=plain)         # without a hand-over
+    close(plain, want_res, 5e-5)                           # the product is added in float32, not rounded first
+    xw, sums = kernels.mid_handover_buffers(H, DEV)
+    xw.fill_(float("nan"))
+    sums.fill_(float("nan"))
+    kernels.gemm_mid(x, w1, None, kernels.EPI_ADD_RESIDUAL, residual=res, hand_out=(nw, xw, sums))
+    assert torch.equal(res, plain)
+    assert torch.equal(res_all[M:], before[M:]) and torch.equal(res_all[:, H:], before[:, H:])
+    got = res.double()                                     # what the kernel itself stored
+    close(xw[:M], got * nw.double(), 5e-3)
+    assert torch.isnan(xw[M:]).all()
+    ss = (got * got).sum(1)
+    assert ((sums[:M].double().sum(1) - ss).abs() <= 1e-5 * ss).all()
+    inv = torch.rsqrt(ss / H + eps)[:, None]
+    ref = (xw[:M].double() @ w2.double().T) * inv          # from the xw the kernel stored ...
+    exact = ((got * inv) * nw.double()) @ w2.double().T    # ... and the norm as it is defined
+    y = torch.full((M, 2 * N2), float("nan"), device=DEV, dtype=torch.bfloat16)
+    kernels.gemm_mid(xw[:M], w2, y, kernels.EPI_BF16, hand_in=sums, eps=eps)
+    close(y, ref, 1.2e-2)
+    close(y, exact, 1.5e-2)
+    act = torch.full((M, N2), float("nan"), device=DEV, dtype=torch.bfloat16)
+    kernels.gemm_mid(xw[:M], w2, act, kernels.EPI_SWIGLU, hand_in=sums, eps=eps)
+    P.STORE_DTYPE = torch.bfloat16
+    try:
+        want_act = P.swiglu(P.stored(ref[:, :N2].cpu()), P.stored(ref[:, N2:].cpu()))
+    finally:
+        P.STORE_DTYPE = None
+    close(act, want_act, 2e-2)
+    assert int(status.item()) == 0
+    with pytest.raises(kernels.KernelError):               # a hand-over only from `residual +=`
+        kernels.gemm_mid(x, w1, torch.zeros(M, H, device=DEV, dtype=torch.bfloat16), kernels.EPI_BF16,
+                         hand_out=(nw, xw, sums))
+    with pytest.raises(kernels.KernelError):               # the stream is float32
+        kernels.gemm_mid(x, w1, None, kernels.EPI_ADD_RESIDUAL, residual=res.to(torch.bfloat16))
 
 
 TC_SHAPES = [(128, 128, 64), (17, 331, 200), (256, 384, 512), (130, 200, 72), (2048, 3072, 2048), (300, 1000, 384),
