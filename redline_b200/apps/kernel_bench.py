@@ -152,13 +152,14 @@ def bench_gemm_tc(args) -> None:
         if args.library:
             torch.mm(x, w.t(), out=yl)
         else:
-            kernels.gemm_tc(x, w, y, epi)
+            kernels.gemm_tc(x, w, y, epi, args.tile_n)
 
     us = graph_time_us(fn, copies, use_graph=not args.no_graph)
     flops = 2.0 * M * wn * K
     pk = peaks()
     print(json.dumps({"kernel": "library_mm" if args.library else "gemm_tc", "rows": M, "n": N, "k": K,
-                      "epilogue": args.epilogue, "us": round(us, 2), "TFLOP/s": round(flops / us / 1e6, 1),
+                      "epilogue": args.epilogue, "tile_n": args.tile_n, "us": round(us, 2),
+                      "TFLOP/s": round(flops / us / 1e6, 1),
                       "frac_of_measured_bf16": round(flops / us / 1e6 / pk["bf16_tflops"], 3), "copies": copies}))
 
 
@@ -246,6 +247,8 @@ def main() -> int:
             p.add_argument("--n", type=int, default=3072)
             p.add_argument("--k", type=int, default=2048)
             p.add_argument("--epilogue", default="bf16", choices=["bf16", "f32", "residual", "swiglu"])
+            p.add_argument("--tile-n", type=int, default=0, choices=[0, 128, 256, 512],
+                           help="0: the kernel chooses; 128 / 256: one CTA per tile of that width; 512: CTA pairs")
             p.add_argument("--library", action="store_true", help="time the library product instead")
         if name == "skinny":
             p.add_argument("--rows", type=int, default=8)

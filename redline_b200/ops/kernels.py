@@ -279,7 +279,8 @@ def gemm_tc_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, epilogue: int = EPI_BF16, tile_n: int = 0) -> None:
     """y = epilogue(x @ w^T) with tcgen05 tensor cores, TMEM accumulators and TMA loads
     (csrc/gemm_tc.cu): bfloat16 x [M, K], w [N, K] (EPI_SWIGLU: [2 N, K], gate rows then up rows).
-    Epilogues as gemm_skinny's.  tile_n: 0 lets the kernel choose its tile width, 128 or 256 forces it."""
+    Epilogues as gemm_skinny's.  tile_n: 0 lets the kernel choose its tiling; 128 or 256 force one CTA per
+    128-row tile of that width, 512 forces CTA pairs (tcgen05.mma.cta_group::2) on 256 x 256 tiles."""
     _need_cuda(x, w, y)
     f = _fn(_lib("gemm_tc", "gemm_tc.cu"), "rl_gemm_tc",
             [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p])

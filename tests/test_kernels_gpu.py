@@ -811,10 +811,11 @@ TC_SHAPES = [(128, 128, 64), (17, 331, 200), (256, 384, 512), (130, 200, 72), (2
              (1, 128, 8), (640, 2048, 8192)]
 
 
-@pytest.mark.parametrize("tile_n", [128, 256])
+@pytest.mark.parametrize("tile_n", [128, 256, 512])
 @pytest.mark.parametrize("M,N,K", TC_SHAPES)
 def test_gemm_tc_epilogues(M, N, K, tile_n):
-    """The tcgen05 / TMEM / TMA product against float64, every epilogue, edge tiles in M, N and K."""
+    """The tcgen05 / TMEM / TMA product against float64, every epilogue, edge tiles in M, N and K; one CTA per
+    tile of 128 or 256 features, and CTA pairs on 256 x 256 tiles (tile_n 512)."""
     g = torch.Generator(device="cuda").manual_seed(M + N + K)
     x = torch.randn(M + 2, K, device=DEV, generator=g).to(torch.bfloat16)[:M]
     w = (torch.randn(2 * N, K, device=DEV, generator=g) * 0.05).to(torch.bfloat16)
