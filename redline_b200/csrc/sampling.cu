@@ -192,11 +192,30 @@ sample_partial_kernel(const float* __restrict__ logits, int vocab, int ld, Chunk
   const int per = (vocab + kSampleChunks - 1) / kSampleChunks;
   const int lo = chunk * per, hi = min(vocab, lo + per);
   const float* l = logits + static_cast<size_t>(row) * ld;
+  // A thread's first kSampleHeld values stay in registers (all their loads are in flight together, and the
+  // piece is read once); a piece longer than 256 * kSampleHeld goes on through memory.
+  constexpr int kSampleHeld = 8;
+  float v[kSampleHeld];
+#pragma unroll
+  for (int j = 0; j < kSampleHeld; ++j) {
+    const int i = lo + threadIdx.x + j * 256;
+    v[j] = i < hi ? l[i] : -FLT_MAX;
+  }
   Best b{-FLT_MAX, 0x7fffffff};
-  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) b = better(b, Best{l[i], i});
+#pragma unroll
+  for (int j = 0; j < kSampleHeld; ++j) {
+    const int i = lo + threadIdx.x + j * 256;
+    if (i < hi) b = better(b, Best{v[j], i});
+  }
+  for (int i = lo + threadIdx.x + kSampleHeld * 256; i < hi; i += 256) b = better(b, Best{l[i], i});
   b = block_best(b, bscratch);
   float s = 0.f;
-  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) s += expf(l[i] - b.v);
+#pragma unroll
+  for (int j = 0; j < kSampleHeld; ++j) {
+    const int i = lo + threadIdx.x + j * 256;
+    if (i < hi) s += expf(v[j] - b.v);
+  }
+  for (int i = lo + threadIdx.x + kSampleHeld * 256; i < hi; i += 256) s += expf(l[i] - b.v);
   s = block_sum(s, fscratch);
   if (threadIdx.x == 0) stats[row * kSampleChunks + chunk] = ChunkStat{b.v, b.i, s, 0.f};
 }
