@@ -274,7 +274,7 @@ def profile_step(args) -> int:
             raise SystemExit("--profile-batch / --profile-prompt: the first requests would reach the context "
                              "limit before the last one is admitted; use a shorter --profile-prompt")
         eng = Engine(model, dtype="bfloat16", max_num_seqs=batch, max_num_batched_tokens=2048, max_seq_len=CONTEXT,
-                     kv_cache_tokens=batch * (prompt + 128), cuda_graphs=not args.profile_eager, async_scheduling=False)
+                     kv_cache_tokens=max(batch * (prompt + 128), CONTEXT + 64), cuda_graphs=not args.profile_eager, async_scheduling=False)
         rng = np.random.RandomState(0)
         for i in range(batch):
             eng.add_request(rng.randint(0, eng.vocab_size, size=prompt).tolist(),

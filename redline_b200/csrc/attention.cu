@@ -313,7 +313,6 @@ __device__ __forceinline__ void rope_rotate8(uint4& x0, uint4& x1, const float* 
 __global__ void __launch_bounds__(128)
 decode_attn_mma_kernel(const DecodeArgs<bf16> a, const DecodeRope rope) {
   pdl_launch();
-  pdl_wait();
   constexpr int DB = kD / 32;   // 32-wide blocks of d for Q.K^T
   constexpr int DG = kD / 64;   // 64-wide groups of d for P.V
   constexpr float kLog2e = 1.4426950408889634f, kLn2 = 0.6931471805599453f;
@@ -340,12 +339,16 @@ decode_attn_mma_kernel(const DecodeArgs<bf16> a, const DecodeRope rope) {
   const int k0 = part * kPart + warp * 32;                            // this warp's 32 keys
   const int ps_shift = __ffs(a.page_size) - 1, ps_mask = a.page_size - 1;   // page sizes are powers of two
 
-  // ---- every load of the warp is issued up front: K and V (through the block table), then Q
-  // With rope.cos set the token's own k and v (key ctx - 1) are not in the cache yet: the threads whose
-  // fragments hold them take them from the token's row (k rotated: a thread's pieces db and db + DB / 2
-  // are the pairs d, d + D / 2) and write them into the cache for later steps.
+  // ---- every load of the warp is issued up front: K and V (through the block table), then Q.
+  // The keys before the token's own were written by earlier steps, and the step's metadata by a copy
+  // before its first kernel: their loads are issued BEFORE the wait on the kernels before this one, so
+  // that the trip through the block table and the cache's latency pass while the product before drains.
+  // The token's own key (ctx - 1) comes after the wait: with rope.cos set it is not in the cache yet and
+  // the threads whose fragments hold it take k and v from the token's row (k rotated: a thread's pieces
+  // db and db + DB / 2 are the pairs d, d + D / 2) and write them into the cache for later steps; without,
+  // the kernel before has just written it there.
   const bool fused = rope.cos != nullptr;
-  const int newest = fused ? ctx - 1 : -1;
+  const int newest = ctx - 1;
   int pos = ctx - 1;
   if (fused && pos >= rope.max_pos) {
     if (threadIdx.x == 0) atomicOr(rope.status, 2);
@@ -358,23 +361,12 @@ decode_attn_mma_kernel(const DecodeArgs<bf16> a, const DecodeRope rope) {
 #pragma unroll
   for (int nt = 0; nt < 4; ++nt) {
     const int key = k0 + nt * 8 + g;
-    const bool live = key < ctx;
+    const bool live = key < newest;
     const size_t page = live ? bt[key >> ps_shift] : 0;
-    const size_t at = (page * a.hkv + kvh) * head_stride + static_cast<size_t>(key & ps_mask) * kD + t * 8;
-    if (key == newest) {
-      const bf16* kp = trow + rope.k_col + kvh * kD + t * 8;
+    const bf16* kp = a.kcache + (page * a.hkv + kvh) * head_stride + static_cast<size_t>(key & ps_mask) * kD + t * 8;
 #pragma unroll
-      for (int db = 0; db < DB; ++db) kf[nt][db] = *reinterpret_cast<const uint4*>(kp + db * 32);
-#pragma unroll
-      for (int db = 0; db < DB / 2; ++db) rope_rotate8(kf[nt][db], kf[nt][db + DB / 2], cs + db * 32, sn + db * 32);
-#pragma unroll
-      for (int db = 0; db < DB; ++db) *reinterpret_cast<uint4*>(rope.kcache + at + db * 32) = kf[nt][db];
-    } else {
-      const bf16* kp = a.kcache + at;
-#pragma unroll
-      for (int db = 0; db < DB; ++db)
-        kf[nt][db] = live ? *reinterpret_cast<const uint4*>(kp + db * 32) : make_uint4(0, 0, 0, 0);
-    }
+    for (int db = 0; db < DB; ++db)
+      kf[nt][db] = live ? *reinterpret_cast<const uint4*>(kp + db * 32) : make_uint4(0, 0, 0, 0);
   }
   // V pieces: for each 16-key step the keys t*2, t*2+1, t*2+8, t*2+9, d = dg*64 + g*8 ..
   uint4 vf[2][4][DG];
@@ -383,23 +375,53 @@ decode_attn_mma_kernel(const DecodeArgs<bf16> a, const DecodeRope rope) {
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
       const int key = k0 + ks * 16 + t * 2 + (q & 1) + (q >> 1) * 8;
-      const bool live = key < ctx;
+      const bool live = key < newest;
       const size_t page = live ? bt[key >> ps_shift] : 0;
-      const size_t at = (page * a.hkv + kvh) * head_stride + static_cast<size_t>(key & ps_mask) * kD + g * 8;
-      if (key == newest) {
-        const bf16* vp = trow + rope.v_col + kvh * kD + g * 8;
+      const bf16* vp = a.vcache + (page * a.hkv + kvh) * head_stride + static_cast<size_t>(key & ps_mask) * kD + g * 8;
 #pragma unroll
-        for (int dg = 0; dg < DG; ++dg) {
-          vf[ks][q][dg] = *reinterpret_cast<const uint4*>(vp + dg * 64);
-          *reinterpret_cast<uint4*>(rope.vcache + at + dg * 64) = vf[ks][q][dg];
-        }
+      for (int dg = 0; dg < DG; ++dg)
+        vf[ks][q][dg] = live ? *reinterpret_cast<const uint4*>(vp + dg * 64) : make_uint4(0, 0, 0, 0);
+    }
+  pdl_wait();
+  if (newest >= k0 && newest < k0 + 32) {          // this warp holds the token's own key
+    const size_t page = bt[newest >> ps_shift];
+    const size_t at0 = (page * a.hkv + kvh) * head_stride + static_cast<size_t>(newest & ps_mask) * kD;
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+      if (k0 + nt * 8 + g != newest) continue;
+      const size_t at = at0 + t * 8;
+      if (fused) {
+        const bf16* kp = trow + rope.k_col + kvh * kD + t * 8;
+#pragma unroll
+        for (int db = 0; db < DB; ++db) kf[nt][db] = *reinterpret_cast<const uint4*>(kp + db * 32);
+#pragma unroll
+        for (int db = 0; db < DB / 2; ++db) rope_rotate8(kf[nt][db], kf[nt][db + DB / 2], cs + db * 32, sn + db * 32);
+#pragma unroll
+        for (int db = 0; db < DB; ++db) *reinterpret_cast<uint4*>(rope.kcache + at + db * 32) = kf[nt][db];
       } else {
-        const bf16* vp = a.vcache + at;
 #pragma unroll
-        for (int dg = 0; dg < DG; ++dg)
-          vf[ks][q][dg] = live ? *reinterpret_cast<const uint4*>(vp + dg * 64) : make_uint4(0, 0, 0, 0);
+        for (int db = 0; db < DB; ++db) kf[nt][db] = *reinterpret_cast<const uint4*>(a.kcache + at + db * 32);
       }
     }
+#pragma unroll
+    for (int ks = 0; ks < 2; ++ks)
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        if (k0 + ks * 16 + t * 2 + (q & 1) + (q >> 1) * 8 != newest) continue;
+        const size_t at = at0 + g * 8;
+        if (fused) {
+          const bf16* vp = trow + rope.v_col + kvh * kD + g * 8;
+#pragma unroll
+          for (int dg = 0; dg < DG; ++dg) {
+            vf[ks][q][dg] = *reinterpret_cast<const uint4*>(vp + dg * 64);
+            *reinterpret_cast<uint4*>(rope.vcache + at + dg * 64) = vf[ks][q][dg];
+          }
+        } else {
+#pragma unroll
+          for (int dg = 0; dg < DG; ++dg) vf[ks][q][dg] = *reinterpret_cast<const uint4*>(a.vcache + at + dg * 64);
+        }
+      }
+  }
   // Q fragments: rows g and g + 8 of the group, all of d
   uint4 qlo[DB], qhi[DB];
 #pragma unroll
