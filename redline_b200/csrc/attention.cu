@@ -21,6 +21,8 @@
 // window w > 0 keeps only keys with pos - w < key <= pos.  The cache of a layer is
 // K [pages, Hkv, page_size, D] and V alike; a token's page comes from its
 // sequence's row of the block table.
+#include <mutex>
+
 #include "common.cuh"
 
 #ifndef RL_HEAD_DIM
@@ -630,6 +632,7 @@ __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_gr
 
 }  // namespace rl
 #include "decode_stream.cuh"
+#include "decode_rows.cuh"
 namespace rl {
 #endif  // head size 64 or 128
 
@@ -1082,6 +1085,66 @@ inline bool decode_one_partition(const void* counters, int max_parts, int hq, in
 #endif
 }
 
+#ifdef RL_HAVE_MMA_DECODE
+// Rows kernel (decode_rows.cuh): how many CTAs the cluster of a row gets in a launch of `rows` rows on the
+// current device: the largest size up to 8 of which `rows` clusters are resident at once; 0 if not even
+// clusters of one are.  (The occupancy calculator is asked once per device.)
+static int rows_cluster_size(int rows, cudaError_t* err) {
+  static int rows_clusters[kMaxDevices][kRowsMaxCluster + 1];
+  static bool rows_ready[kMaxDevices] = {};
+  static std::mutex rows_lock;
+  *err = cudaSuccess;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) {
+    *err = e;
+    return 0;
+  }
+  if (dev < 0 || dev >= kMaxDevices) {
+    *err = cudaErrorInvalidDevice;
+    return 0;
+  }
+  {
+    std::lock_guard<std::mutex> guard(rows_lock);
+    if (!rows_ready[dev]) {
+      e = cudaFuncSetAttribute(decode_attn_rows_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(kRowsSmem));
+      if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(decode_attn_rows_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(kRowsSmem));
+      if (e != cudaSuccess) {
+        *err = e;
+        return 0;
+      }
+      for (int c = 1; c <= kRowsMaxCluster; ++c) {
+        cudaLaunchConfig_t qc = {};
+        qc.gridDim = dim3(c);
+        qc.blockDim = dim3(kStreamThreads);
+        qc.dynamicSmemBytes = kRowsSmem;
+        cudaLaunchAttribute qa[1];
+        qa[0].id = cudaLaunchAttributeClusterDimension;
+        qa[0].val.clusterDim.x = c;
+        qa[0].val.clusterDim.y = 1;
+        qa[0].val.clusterDim.z = 1;
+        qc.attrs = qa;
+        qc.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, decode_attn_rows_kernel<false>, &qc) != cudaSuccess) {
+          cudaGetLastError();
+          n = 0;
+        }
+        rows_clusters[dev][c] = n;
+      }
+      rows_ready[dev] = true;
+    }
+  }
+  int cx = kRowsMaxCluster;
+  while (cx > 1 && rows_clusters[dev][cx] < rows) --cx;
+  return rows_clusters[dev][cx] >= rows ? cx : 0;
+}
+
+#endif
+
 template <typename T>
 int launch_decode(const void* q, int q_stride, const void* kc, const void* vc, const int32_t* bt,
                   int max_blocks, const int32_t* items, float* part_o, float* part_ml, int max_parts,
@@ -1109,6 +1172,48 @@ int launch_decode(const void* q, int q_stride, const void* kc, const void* vc, c
   dim3 grid(max_parts, hkv, nitems);
 #ifdef RL_HAVE_MMA_DECODE
   if constexpr (sizeof(T) == 2) {
+    if (impl == 4) {
+      // one cluster per (item, kv head): the largest cluster size of which that many clusters are resident
+      // (groups of up to 16 heads, pages that divide a partition, 16-byte aligned rows)
+      const bool aligned = q_stride % 8 == 0 && out_stride % 8 == 0 &&
+                           ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(out) |
+                             reinterpret_cast<uintptr_t>(kc) | reinterpret_cast<uintptr_t>(vc)) & 15) == 0;
+      if (!(hq / hkv <= 16 && page_size >= 16 && kPart % page_size == 0 && aligned && nitems > 0))
+        return static_cast<int>(cudaErrorInvalidValue);
+      cudaError_t e = cudaSuccess;
+      const int rows = nitems * hkv;
+      const int cx = rows_cluster_size(rows, &e);
+      if (e != cudaSuccess) return static_cast<int>(e);
+      if (cx < 1) return static_cast<int>(cudaErrorNotSupported);
+      DecodeRope sr = {};
+      if (rope != nullptr && rope->cos != nullptr) {
+        sr.cos = rope->cos;
+        sr.sin = rope->sin;
+        sr.max_pos = rope->max_pos;
+        sr.k_col = rope->k_col;
+        sr.v_col = rope->v_col;
+        sr.kcache = const_cast<bf16*>(a.kcache);
+        sr.vcache = const_cast<bf16*>(a.vcache);
+        sr.status = rope->status;
+      }
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(rows * cx);
+      cfg.blockDim = dim3(kStreamThreads);
+      cfg.dynamicSmemBytes = kRowsSmem;
+      cfg.stream = stream;
+      cudaLaunchAttribute at[2];
+      at[0].id = cudaLaunchAttributeClusterDimension;
+      at[0].val.clusterDim.x = cx;
+      at[0].val.clusterDim.y = 1;
+      at[0].val.clusterDim.z = 1;
+      at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      at[1].val.programmaticStreamSerializationAllowed = 1;
+      cfg.attrs = at;
+      cfg.numAttrs = pdl_enabled() ? 2 : 1;
+      if (hq / hkv > 8)
+        return static_cast<int>(cudaLaunchKernelEx(&cfg, decode_attn_rows_kernel<true>, a, sr));
+      return static_cast<int>(cudaLaunchKernelEx(&cfg, decode_attn_rows_kernel<false>, a, sr));
+    }
     if (decode_streams(q, q_stride, kc, vc, part_o, counters, out, out_stride, max_parts, nitems, hq, hkv, page_size,
                        impl)) {
       // (a kernel's shared-memory limit and the SM count belong to a device: looked up once on each)
@@ -1292,7 +1397,9 @@ int rl_attn_tile_rows() { return 4 * kBQ; }
 // impl: 0 = the best kernel that applies: the streaming tensor-core kernel (bfloat16, head size
 // 64 or 128, at most 16 heads per group, pages of 16 to 128 keys, at most 512 items), else the
 // one-partition-per-CTA tensor-core kernel, else the CUDA-core kernel; 1 = the CUDA-core kernel;
-// 2 = the one-partition-per-CTA tensor-core kernel or an error; 3 = the streaming kernel or an error.
+// 2 = the one-partition-per-CTA tensor-core kernel or an error; 3 = the streaming kernel or an error;
+// 4 = one cluster per (item, kv head) (decode_rows.cuh: for few rows of similar length) or an error: when the
+// launch has more rows than clusters can be resident.
 int rl_attn_decode(int dtype, const void* q, int q_stride, const void* kc, const void* vc,
                    const int32_t* bt, int max_blocks, const int32_t* items, float* part_o,
                    float* part_ml, int max_parts, int* counters, void* out, int out_stride, int nitems,
@@ -1305,6 +1412,18 @@ int rl_attn_decode(int dtype, const void* q, int q_stride, const void* kc, const
   return launch_decode<bf16>(q, q_stride, kc, vc, bt, max_blocks, items, part_o, part_ml, max_parts,
                              counters, out, out_stride, nitems, hq, hkv, page_size, window, scale, impl,
                              nullptr, stream);
+}
+
+// The cluster size that rl_attn_decode with impl 4 gives a row in a launch of nitems items (0: it refuses the
+// launch: too many rows, or a head size without tensor-core decode kernels).
+int rl_attn_decode_rows_cluster(int nitems, int hkv) {
+#ifdef RL_HAVE_MMA_DECODE
+  cudaError_t e = cudaSuccess;
+  const int cx = rows_cluster_size(nitems * hkv, &e);
+  return e == cudaSuccess ? cx : 0;
+#else
+  return 0;
+#endif
 }
 
 // 1 if rl_attn_decode with these arguments runs the streaming kernel (bfloat16 only), else 0.
@@ -1334,18 +1453,20 @@ int rl_attn_decode_rope_ok(const void* q, int q_stride, const void* kc, const vo
 // UNROTATED [q | ... k at k_col ... | ... v at v_col ...]; cos / sin are float [max_pos, D / 2] tables; a
 // token's position is its context length - 1; its rotated k and its v are written into kc and vc at that
 // position (through the block table).  status: device int, bit 1 is set for a position outside the
-// tables.  Returns cudaErrorInvalidValue where neither tensor-core kernel applies.
+// tables.  impl: 0 or 4, as for rl_attn_decode.  Returns cudaErrorInvalidValue where no tensor-core kernel
+// applies.
 int rl_attn_decode_rope(const void* q, int q_stride, void* kc, void* vc, const int32_t* bt, int max_blocks,
                         const int32_t* items, float* part_o, float* part_ml, int max_parts, int* counters, void* out,
                         int out_stride, int nitems, int hq, int hkv, int page_size, int window, float scale,
                         const float* cos_t, const float* sin_t, int max_pos, int k_col, int v_col, int* status,
-                        cudaStream_t stream) {
+                        int impl, cudaStream_t stream) {
   if (nitems <= 0) return 0;
-  if (cos_t == nullptr || sin_t == nullptr || status == nullptr || k_col % 8 != 0 || v_col % 8 != 0)
+  if (cos_t == nullptr || sin_t == nullptr || status == nullptr || k_col % 8 != 0 || v_col % 8 != 0 ||
+      (impl != 0 && impl != 4))
     return static_cast<int>(cudaErrorInvalidValue);
   DecodeRopeHost r = {cos_t, sin_t, max_pos, k_col, v_col, status};
   return launch_decode<bf16>(q, q_stride, kc, vc, bt, max_blocks, items, part_o, part_ml, max_parts, counters, out,
-                             out_stride, nitems, hq, hkv, page_size, window, scale, 0, &r, stream);
+                             out_stride, nitems, hq, hkv, page_size, window, scale, impl, &r, stream);
 }
 
 int rl_attn_prefill(int dtype, const void* q, int q_stride, const void* kc, const void* vc,

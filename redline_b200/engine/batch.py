@@ -143,6 +143,9 @@ class StepContext:
     status: torch.Tensor
     has_src: bool = False
     any_sampling: bool = False
+    # the single-token sequences' context lengths (new token included): the longest and their sum
+    decode_max_ctx: int = 0
+    decode_sum_ctx: int = 0
     host: Optional["HostBatch"] = None
     profiler: Optional[object] = None          # engine.profiler.OpProfiler while per-op profiling is on
     # a norm handed over between parts (parts.base.NormHandover); set and cleared by the block
@@ -244,8 +247,12 @@ class BatchBuilder:
         want_flat: List[int] = []
         t = 0
         to = 0
+        dec_max = dec_sum = 0
         for s in segments:
             n = len(s.tokens)
+            if n == 1:
+                dec_max = max(dec_max, s.start_pos + 1)
+                dec_sum += s.start_pos + 1
             sp = s.sampling
             fed = s.src_row >= 0
             if sp is not None:
@@ -312,4 +319,5 @@ class BatchBuilder:
         views = self._views(lay, dev, T, S, R, L)
         return StepContext(T=T, S=S, R=R, num_decode=nd, num_tiles=li, decode_parts=decode_parts,
                            max_items=self.max_seqs, parts_capacity=self.parts_capacity, status=self.status,
-                           has_src=has_src, any_sampling=any_sampling, host=hb, **views)
+                           has_src=has_src, any_sampling=any_sampling, decode_max_ctx=dec_max,
+                           decode_sum_ctx=dec_sum, host=hb, **views)

@@ -73,6 +73,11 @@ class DecoderModel:
             raise ValueError(f"the model's mixers want the step's work lists cut in different ways: {sorted(named)}")
         return next(iter(named)) if named else None
 
+    def decode_variants(self, ctx) -> Tuple[int, ...]:
+        """What every layer's mixer will run for the step's single-token sequences (``Mixer.decode_variant``):
+        steps with the same answer can share a CUDA graph."""
+        return tuple(b.mixer.decode_variant(ctx) for b in self.blocks)
+
     def state_specs(self) -> Dict[int, StateSpec]:
         out = {}
         for i, call in enumerate(self.spec.order):

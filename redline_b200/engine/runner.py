@@ -100,8 +100,9 @@ class ModelRunner:
         self._states = [self.states.of_call(i) for i in range(len(order))]
         self.model.nvtx_layers = cfg.nvtx_layers
         self.profiler = None                       # engine.profiler.OpProfiler while per-op profiling is on
-        self._graphs: Dict[int, torch.cuda.CUDAGraph] = {}
-        self._graph_kernels: Dict[int, int] = {}   # kernels of this package in each captured graph
+        # one graph per padded size and per answer of the mixers to "which kernel for the single tokens"
+        self._graphs: Dict[Tuple[int, Tuple[int, ...]], torch.cuda.CUDAGraph] = {}
+        self._graph_kernels: Dict[Tuple[int, Tuple[int, ...]], int] = {}   # kernels of this package in each graph
         self.num_kernel_launches = 0               # kernels of this package run by steps so far
         self.num_graph_steps = 0
         self.num_eager_steps = 0
@@ -147,13 +148,14 @@ class ModelRunner:
             ctx.profiler = self.profiler
             self.profiler.begin("decode" if single == len(segments) else ("prefill" if single == 0 else "mixed"))
         if bucket:
-            g = self._graphs.get(bucket)
+            key = (bucket, self.model.decode_variants(ctx))
+            g = self._graphs.get(key)
             if g is None:
-                g = self._capture(bucket, ctx)
+                g = self._capture(key, ctx)
             else:
                 g.replay()
             self.num_graph_steps += 1
-            self.num_kernel_launches += self._graph_kernels[bucket]
+            self.num_kernel_launches += self._graph_kernels[key]
         else:
             before = kernels.LAUNCHES
             self._forward(ctx, sample, ctx.has_src)
@@ -189,7 +191,7 @@ class ModelRunner:
         # more sequences than the largest bucket within the limit: the limit itself is the last bucket
         return self.cfg.max_num_seqs if n <= self.cfg.max_num_seqs <= GRAPH_MAX_ROWS else 0
 
-    def _capture(self, bucket: int, ctx: StepContext) -> torch.cuda.CUDAGraph:
+    def _capture(self, key: Tuple[int, Tuple[int, ...]], ctx: StepContext) -> torch.cuda.CUDAGraph:
         # The graph always resolves device-fed ids (token_src is -1 where there are none),
         # so one graph serves steps with and without them.  The step runs once eagerly
         # (compiles kernels, sizes workspaces), is captured, and the first replay runs it
@@ -201,8 +203,8 @@ class ModelRunner:
         before = kernels.LAUNCHES
         with torch.cuda.graph(g):
             self._forward(ctx, True, True)
-        self._graph_kernels[bucket] = kernels.LAUNCHES - before
-        self._graphs[bucket] = g
+        self._graph_kernels[key] = kernels.LAUNCHES - before
+        self._graphs[key] = g
         self.sampler.tokens.copy_(fed)
         g.replay()
         return g

@@ -415,7 +415,8 @@ def attn_decode(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcache: to
     counters  int32 [nitems * num_kv_heads], zero (the tensor-core kernel needs and keeps them zero)
     impl      0: the best kernel that applies (streaming tensor-core for launches with many partitions,
               one-partition tensor-core, CUDA-core); 1: CUDA-core; 2: one-partition tensor-core or error;
-              3: streaming tensor-core or error
+              3: streaming tensor-core or error; 4: one cluster per (item, kv head), partial results
+              merged through distributed shared memory (few rows of similar length) or error
     """
     _need_cuda(q, kcache, out)
     f = _fn(_attn(head_dim), "rl_attn_decode",
@@ -448,6 +449,42 @@ def attn_decode_streams(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vc
                   _ptr(out), out.stride(0), max_parts, nitems, num_heads, num_kv_heads, page_size, impl))
 
 
+_rows_cluster: Dict[Tuple[int, int, int], int] = {}
+
+
+def attn_decode_rows_cluster(nitems: int, num_kv_heads: int, head_dim: int, device: torch.device) -> int:
+    """CTAs per row that ``attn_decode`` with impl 4 would use for a launch of ``nitems`` items (0: it does not
+    take such a launch: more rows than clusters can be resident, or no tensor-core decode kernel for this
+    head size)."""
+    if device.type != "cuda" or head_dim not in (64, 128) or nitems <= 0:
+        return 0
+    key = (device.index if device.index is not None else torch.cuda.current_device(), nitems * num_kv_heads, head_dim)
+    if key not in _rows_cluster:
+        f = _fn(_attn(head_dim), "rl_attn_decode_rows_cluster", [c_int, c_int])
+        with torch.cuda.device(key[0]):
+            _rows_cluster[key] = int(f(nitems, num_kv_heads))
+    return _rows_cluster[key]
+
+
+def attn_decode_rows_pays(nitems: int, num_kv_heads: int, head_dim: int, max_ctx: int, sum_ctx: int, window: int,
+                          device: torch.device) -> bool:
+    """Whether the decode kernel of one cluster per (item, kv head) (impl 4) is expected to beat the others for
+    a launch of ``nitems`` rows of at most ``max_ctx`` and together ``sum_ctx`` keys.  Its time goes with the
+    longest row (a row has its cluster's SMs only), the streaming kernel's with all keys plus the count and
+    merge of its pieces.  The constants are measured on a B200 (head size 64, 8 kv heads): 4.4 us plus
+    1.7 us per 32-key sub-block of a warp's run, against 8 us plus the keys' bytes at 6 TB/s."""
+    csize = attn_decode_rows_cluster(nitems, num_kv_heads, head_dim, device)
+    if csize <= 0 or max_ctx <= 0:
+        return False
+    if window > 0:
+        max_ctx, sum_ctx = min(max_ctx, window), min(sum_ctx, nitems * window)
+    warps = csize * (12 if head_dim == 64 else 6)
+    sub_blocks = (max_ctx + 31) // 32
+    t_rows = 4.4 + 1.7 * (head_dim / 64.0) * ((sub_blocks + warps - 1) // warps)
+    t_stream = 8.0 + sum_ctx * num_kv_heads * head_dim * 4 / 6.0e6
+    return t_rows < t_stream
+
+
 def attn_decode_rope_ok(qkv: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcache: torch.Tensor,
                         part_o: torch.Tensor, counters: Optional[torch.Tensor], out: torch.Tensor, max_parts: int,
                         nitems: int, num_heads: int, num_kv_heads: int, head_dim: int, page_size: int,
@@ -467,16 +504,17 @@ def attn_decode_rope(qkv: torch.Tensor, q_stride: int, kcache: torch.Tensor, vca
                      block_table: torch.Tensor, items: torch.Tensor, part_o: torch.Tensor, part_ml: torch.Tensor,
                      max_parts: int, counters: torch.Tensor, out: torch.Tensor, nitems: int, num_heads: int,
                      num_kv_heads: int, head_dim: int, page_size: int, window: int, scale: float,
-                     cos: torch.Tensor, sin: torch.Tensor, k_col: int, v_col: int, status: torch.Tensor) -> None:
+                     cos: torch.Tensor, sin: torch.Tensor, k_col: int, v_col: int, status: torch.Tensor,
+                     impl: int = 0) -> None:
     """``attn_decode`` by a tensor-core kernel with the rotary encoding and the cache write done in the
     kernel: ``qkv`` holds the UNROTATED rows [q | k | v] of the query tokens (k at column ``k_col``, v at
     ``v_col``); a token's position is its context length - 1; its rotated k and its v are written into the
-    cache there.  Only where ``attn_decode_rope_ok`` says so."""
+    cache there.  Only where ``attn_decode_rope_ok`` says so.  impl 0 or 4 as for ``attn_decode``."""
     _need_cuda(qkv, kcache, out)
     f = _fn(_attn(head_dim), "rl_attn_decode_rope",
             [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
              c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_int, c_int, c_int,
-             c_void_p, c_void_p])
+             c_void_p, c_int, c_void_p])
     need = nitems * num_heads * max_parts
     if part_o.numel() < need * head_dim or part_ml.numel() < need * 2:
         raise KernelError("attn_decode_rope: partition workspace too small")
@@ -487,7 +525,7 @@ def attn_decode_rope(qkv: torch.Tensor, q_stride: int, kcache: torch.Tensor, vca
     _check(f(_ptr(qkv), q_stride, _ptr(kcache), _ptr(vcache), _ptr(block_table), block_table.shape[1], _ptr(items),
              _ptr(part_o), _ptr(part_ml), max_parts, _ptr(counters), _ptr(out), out.stride(0), nitems, num_heads,
              num_kv_heads, page_size, window, float(scale), _ptr(cos), _ptr(sin), cos.shape[0], k_col, v_col,
-             _ptr(status), _stream()), "attn_decode_rope")
+             _ptr(status), impl, _stream()), "attn_decode_rope")
 
 
 def attn_prefill(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcache: torch.Tensor,

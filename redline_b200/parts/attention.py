@@ -11,6 +11,7 @@ scale is 1 / sqrt(head_dim) unless given, a window w > 0 keeps only the last w k
 from __future__ import annotations
 
 import math
+import os
 from dataclasses import dataclass
 from typing import Dict, Optional
 
@@ -168,6 +169,15 @@ class GQAttention(Mixer):
         ctx.hand_out = out
         return True
 
+    def decode_variant(self, ctx) -> int:
+        """4 where the decode kernel of one cluster per (sequence, kv head) is expected to be the fastest (few
+        sequences of similar length), else 0 (the kernels choose among themselves)."""
+        p, rt = self.params, self.rt
+        if rt.dtype != torch.bfloat16 or ctx.num_decode <= 0 or os.environ.get("REDLINE_DECODE_ROWS", "1") == "0":
+            return 0
+        return 4 if kernels.attn_decode_rows_pays(ctx.num_decode, p.num_kv_heads, p.head_dim, ctx.decode_max_ctx,
+                                                  ctx.decode_sum_ctx, p.window, rt.device) else 0
+
     def _counters(self, max_items: int) -> torch.Tensor:
         """Arrival counters of the decode kernel's fused merge: zero between launches."""
         c = getattr(self, "_cnt", None)
@@ -187,6 +197,7 @@ class GQAttention(Mixer):
         g = ctx.groups[cache.group]
         attn = ws.get("attn.out", (rt.max_tokens, self.q_size), rt.dtype)[:T]
         part_o = part_ml = None
+        variant = self.decode_variant(ctx) if ctx.num_decode > 0 else 0
         if ctx.num_decode > 0:
             part_o = ws.get("attn.part_o", (ctx.max_items * p.num_heads * ctx.parts_capacity * p.head_dim,),
                             torch.float32)
@@ -203,7 +214,7 @@ class GQAttention(Mixer):
                                          part_o, part_ml, ctx.decode_parts, self._counters(ctx.max_items), attn,
                                          ctx.num_decode, p.num_heads, p.num_kv_heads, p.head_dim, rt.page_size,
                                          p.window, self.scale, tables[0], tables[1], self.q_size,
-                                         self.q_size + self.kv_size, ctx.status)
+                                         self.q_size + self.kv_size, ctx.status, impl=variant)
                 self._mark_attention(ctx, "rope+kv_write+attention_decode", "decode")
                 return attn
         if tables is None:
@@ -218,7 +229,7 @@ class GQAttention(Mixer):
             kernels.attn_decode(qkv, self.qkv_size, cache.k, cache.v, g.block_table, ctx.decode_info,
                                 part_o, part_ml, ctx.decode_parts, self._counters(ctx.max_items), attn,
                                 ctx.num_decode, p.num_heads, p.num_kv_heads, p.head_dim, rt.page_size,
-                                p.window, self.scale)
+                                p.window, self.scale, impl=variant)
             self._mark_attention(ctx, "attention_decode", "decode")
         if ctx.num_tiles > 0:
             kernels.attn_prefill(qkv, self.qkv_size, cache.k, cache.v, g.block_table, ctx.tile_seq,

@@ -225,6 +225,13 @@ class Mixer(Part):
         model that name a tiling must name the same one."""
         return None
 
+    def decode_variant(self, ctx) -> int:
+        """Which of its kernels this mixer will run for the step's single-token sequences, as a number of its
+        own (0 if it has one way only).  It must depend on nothing but ``ctx.num_decode``,
+        ``ctx.decode_max_ctx`` and ``ctx.decode_sum_ctx``: a CUDA graph of a step is replayed only for steps
+        whose mixers answer alike."""
+        return 0
+
     def forward(self, x: torch.Tensor, ctx, cache: Optional[LayerCache],
                 state: Optional[torch.Tensor]) -> torch.Tensor:
         """x [T, H] -> [T, H] (what is added to the residual stream).  ``state`` is this

@@ -345,6 +345,30 @@ def test_attention_decode_streaming_kernel(Hq, Hkv, D, page_size):
     assert int(kernels.tc_status(torch.device(DEV)).item()) == 0
 
 
+@pytest.mark.parametrize("Hq,Hkv,D", [(4, 2, 64), (32, 8, 64), (3, 1, 128), (16, 1, 64), (24, 8, 128), (7, 7, 64)])
+@pytest.mark.parametrize("page_size", [16, 32, 64, 128])
+def test_attention_decode_rows_kernel(Hq, Hkv, D, page_size):
+    """impl 4 insists on the kernel that gives every (item, kv head) a cluster of its own and merges the
+    partial results through distributed shared memory: the same cases as the other tensor-core kernels
+    (rows shorter than a sub-block, rows that end on a sub-block's or a page's edge, windows)."""
+    run_attention("bfloat16", Hq, Hkv, D, [0, 31, 32, 33, 63, 64, 65], [1] * 7, page_size=page_size, seed=11, decode_impl=4)
+    run_attention("bfloat16", Hq, Hkv, D, [255, 256, 300, 511, 512, 1030], [1] * 6, page_size=page_size, seed=12, decode_impl=4)
+    for window in (1, 20, 100, 300):
+        run_attention("bfloat16", Hq, Hkv, D, [5, 99, 290, 700], [1] * 4, page_size=page_size, window=window, seed=13,
+                      decode_impl=4)
+    assert int(kernels.tc_status(torch.device(DEV)).item()) == 0
+
+
+def test_attention_decode_rows_kernel_long_rows_and_many_rows():
+    """Clusters of 2 (64 rows of 4,000 keys: every warp a run of several sub-blocks), of 8 (8 rows), and of
+    one CTA (128 rows of many lengths)."""
+    decode_only_case(32, 8, 64, [4000 + 13 * i for i in range(8)], 16, 0, 4, seed=61)
+    decode_only_case(32, 8, 64, [4096], 16, 0, 4, seed=62)
+    decode_only_case(16, 8, 128, [1500, 3000, 77, 2047, 2048, 4096, 4097], 32, 0, 4, seed=63)
+    decode_only_case(32, 8, 64, [2000 + 97 * i for i in range(12)] + [1, 130, 5, 640], 64, 1000, 4, seed=64)
+    assert int(kernels.tc_status(torch.device(DEV)).item()) == 0
+
+
 def decode_only_case(Hq, Hkv, D, lens, page_size, window, impl, seed):
     """Decode attention straight on a random cache (no rotation, no cache write): the reference
     gathers each item's keys and does the softmax in float64."""
@@ -400,14 +424,15 @@ def test_attention_decode_streaming_kernel_many_units_per_cta():
 
 @pytest.mark.parametrize("Hq,Hkv,D", [(32, 8, 64), (16, 2, 128), (4, 4, 64)])
 @pytest.mark.parametrize("page_size,window", [(16, 0), (64, 0), (16, 300)])
-@pytest.mark.parametrize("streams", [True, False])
-def test_attention_decode_with_rotation_and_cache_write_in_the_kernel(Hq, Hkv, D, page_size, window, streams):
+@pytest.mark.parametrize("mode", ["stream", "one", "rows"])
+def test_attention_decode_with_rotation_and_cache_write_in_the_kernel(Hq, Hkv, D, page_size, window, mode):
     """attn_decode_rope against rope_kv_write followed by attn_decode: the same outputs, and the same k and
     v rows written into the cache at the tokens' own positions (and nowhere else); with many partitions
-    (the streaming kernel) and with few (the one-partition kernel)."""
+    (the streaming kernel), with few (the one-partition kernel), and by the kernel of one cluster per row."""
     g = torch.Generator().manual_seed(51)
+    streams = mode == "stream"
     lens = [700, 1, 129, 2048, 33, 1500, 260, 2047]          # context lengths including the new token
-    lens = lens * 4 if streams else lens[:5]
+    lens = lens * 4 if streams else (lens[:5] if mode == "one" else lens)
     B = len(lens)
     cos, sin = plain_rope_tables(D, 10000.0, 2200)
     cos, sin = cos.to(DEV).contiguous(), sin.to(DEV).contiguous()
@@ -442,16 +467,18 @@ def test_attention_decode_with_rotation_and_cache_write_in_the_kernel(Hq, Hkv, D
     kernels.rope_kv_write(qkv1, pos, slots, cos, sin, kc1, vc1, Hq, Hkv, D, page_size, status)
     po, pm, cnt, want = buffers()
     kernels.attn_decode(qkv1, qkv1.shape[1], kc1, vc1, btd, items, po, pm, parts, cnt, want, B, Hq, Hkv, D,
-                        page_size, window, scale, 3 if streams else 2)
+                        page_size, window, scale, 2 if mode == "one" else 3)
     # the one kernel
     kc2, vc2, qkv2 = kc0.clone(), vc0.clone(), qkv0.clone()
     po, pm, cnt, got = buffers()
-    assert kernels.attn_decode_streams(qkv2, qkv2.shape[1], kc2, vc2, po, cnt, got, parts, B, Hq, Hkv, D,
-                                       page_size) == streams
+    if mode != "rows":
+        assert kernels.attn_decode_streams(qkv2, qkv2.shape[1], kc2, vc2, po, cnt, got, parts, B, Hq, Hkv, D,
+                                           page_size) == streams
     assert kernels.attn_decode_rope_ok(qkv2, qkv2.shape[1], kc2, vc2, po, cnt, got, parts, B, Hq, Hkv, D, page_size,
                                        Hq * D, (Hq + Hkv) * D)
     kernels.attn_decode_rope(qkv2, qkv2.shape[1], kc2, vc2, btd, items, po, pm, parts, cnt, got, B, Hq, Hkv, D,
-                             page_size, window, scale, cos, sin, Hq * D, (Hq + Hkv) * D, status)
+                             page_size, window, scale, cos, sin, Hq * D, (Hq + Hkv) * D, status,
+                             impl=4 if mode == "rows" else 0)
     assert status.item() == 0 and int(cnt.abs().max()) == 0
     assert torch.equal(qkv2, qkv0), "the token rows stay unrotated"
     close(got, want, 4e-3)
@@ -523,6 +550,8 @@ def test_a_far_key_is_found_among_hundreds(dtype):
         run_attention(dtype, Hq, Hkv, D, [total - 1], [1], seed=9, sharp=sharp, decode_impl=1)
         if dtype == "bfloat16":
             run_attention(dtype, Hq, Hkv, D, [total - 1], [1], seed=9, sharp=sharp, decode_impl=2)
+            run_attention(dtype, Hq, Hkv, D, [total - 1], [1], seed=9, sharp=sharp, decode_impl=3)
+            run_attention(dtype, Hq, Hkv, D, [total - 1], [1], seed=9, sharp=sharp, decode_impl=4)
         run_attention(dtype, Hq, Hkv, D, [total - 40], [40], seed=9, sharp=sharp)   # prefill kernel
         run_attention(dtype, Hq, Hkv, D, [total - 40], [40], seed=9, sharp=sharp, prefill_impl=1)
         if dtype == "bfloat16":
