@@ -1087,9 +1087,10 @@ inline bool decode_one_partition(const void* counters, int max_parts, int hq, in
 
 #ifdef RL_HAVE_MMA_DECODE
 // Rows kernel (decode_rows.cuh): how many CTAs the cluster of a row gets in a launch of `rows` rows on the
-// current device: the largest size up to 8 of which `rows` clusters are resident at once; 0 if not even
-// clusters of one are.  (The occupancy calculator is asked once per device.)
-static int rows_cluster_size(int rows, cudaError_t* err) {
+// current device: the largest size up to 8 of which `rows` clusters are resident at once; 1 if not even
+// that many clusters of one CTA are (*resident then says how many: each takes several rows); 0 if the kernel
+// cannot run at all.  (The occupancy calculator is asked once per device.)
+static int rows_cluster_size(int rows, cudaError_t* err, int* resident = nullptr) {
   static int rows_clusters[kMaxDevices][kRowsMaxCluster + 1];
   static bool rows_ready[kMaxDevices] = {};
   static std::mutex rows_lock;
@@ -1119,7 +1120,7 @@ static int rows_cluster_size(int rows, cudaError_t* err) {
       for (int c = 1; c <= kRowsMaxCluster; ++c) {
         cudaLaunchConfig_t qc = {};
         qc.gridDim = dim3(c);
-        qc.blockDim = dim3(kStreamThreads);
+        qc.blockDim = dim3(kRowsThreads);
         qc.dynamicSmemBytes = kRowsSmem;
         cudaLaunchAttribute qa[1];
         qa[0].id = cudaLaunchAttributeClusterDimension;
@@ -1140,7 +1141,8 @@ static int rows_cluster_size(int rows, cudaError_t* err) {
   }
   int cx = kRowsMaxCluster;
   while (cx > 1 && rows_clusters[dev][cx] < rows) --cx;
-  return rows_clusters[dev][cx] >= rows ? cx : 0;
+  if (resident != nullptr) *resident = rows_clusters[dev][cx];
+  return rows_clusters[dev][cx] >= 1 ? cx : 0;
 }
 
 #endif
@@ -1182,9 +1184,11 @@ int launch_decode(const void* q, int q_stride, const void* kc, const void* vc, c
         return static_cast<int>(cudaErrorInvalidValue);
       cudaError_t e = cudaSuccess;
       const int rows = nitems * hkv;
-      const int cx = rows_cluster_size(rows, &e);
+      int resident = 0;
+      const int cx = rows_cluster_size(rows, &e, &resident);
       if (e != cudaSuccess) return static_cast<int>(e);
       if (cx < 1) return static_cast<int>(cudaErrorNotSupported);
+      const int clusters = rows < resident ? rows : resident;
       DecodeRope sr = {};
       if (rope != nullptr && rope->cos != nullptr) {
         sr.cos = rope->cos;
@@ -1197,8 +1201,8 @@ int launch_decode(const void* q, int q_stride, const void* kc, const void* vc, c
         sr.status = rope->status;
       }
       cudaLaunchConfig_t cfg = {};
-      cfg.gridDim = dim3(rows * cx);
-      cfg.blockDim = dim3(kStreamThreads);
+      cfg.gridDim = dim3(clusters * cx);
+      cfg.blockDim = dim3(kRowsThreads);
       cfg.dynamicSmemBytes = kRowsSmem;
       cfg.stream = stream;
       cudaLaunchAttribute at[2];
@@ -1211,8 +1215,8 @@ int launch_decode(const void* q, int q_stride, const void* kc, const void* vc, c
       cfg.attrs = at;
       cfg.numAttrs = pdl_enabled() ? 2 : 1;
       if (hq / hkv > 8)
-        return static_cast<int>(cudaLaunchKernelEx(&cfg, decode_attn_rows_kernel<true>, a, sr));
-      return static_cast<int>(cudaLaunchKernelEx(&cfg, decode_attn_rows_kernel<false>, a, sr));
+        return static_cast<int>(cudaLaunchKernelEx(&cfg, decode_attn_rows_kernel<true>, a, rows, sr));
+      return static_cast<int>(cudaLaunchKernelEx(&cfg, decode_attn_rows_kernel<false>, a, rows, sr));
     }
     if (decode_streams(q, q_stride, kc, vc, part_o, counters, out, out_stride, max_parts, nitems, hq, hkv, page_size,
                        impl)) {
@@ -1415,12 +1419,24 @@ int rl_attn_decode(int dtype, const void* q, int q_stride, const void* kc, const
 }
 
 // The cluster size that rl_attn_decode with impl 4 gives a row in a launch of nitems items (0: it refuses the
-// launch: too many rows, or a head size without tensor-core decode kernels).
-int rl_attn_decode_rows_cluster(int nitems, int hkv) {
+// launch: a head size without tensor-core decode kernels); *resident: how many such clusters run at once
+// (fewer than nitems * hkv: a cluster takes several rows, one after another).
+int rl_attn_decode_rows_cluster(int nitems, int hkv, int* resident) {
 #ifdef RL_HAVE_MMA_DECODE
   cudaError_t e = cudaSuccess;
-  const int cx = rows_cluster_size(nitems * hkv, &e);
+  int r = 0;
+  const int cx = rows_cluster_size(nitems * hkv, &e, &r);
+  if (resident != nullptr) *resident = r;
   return e == cudaSuccess ? cx : 0;
+#else
+  return 0;
+#endif
+}
+
+// Warps of a CTA of that kernel (a row's keys are cut into cluster size x this many runs).
+int rl_attn_decode_rows_warps() {
+#ifdef RL_HAVE_MMA_DECODE
+  return kRowsWarps;
 #else
   return 0;
 #endif

@@ -12,6 +12,9 @@
 // nothing waits on a flag: the streaming kernel spends 8 of its 19 microseconds at batch 8 x 4,096 keys on
 // exactly that.
 //
+// A launch with more rows than clusters can be resident runs clusters of one CTA that take several rows
+// each, one after another.
+//
 // The cost: a row has its cluster's SMs and no others.  With rows of very different lengths the longest
 // one sets the kernel's time, where the streaming kernel shares all keys among all warps; the caller
 // chooses (rl_attn_decode, impl 4).
@@ -25,13 +28,18 @@
 
 namespace rl {
 
+// (13 warps at head size 64, which shared memory has rings for, leave a thread 128 registers: the kernel
+// spills and batch 8 x 4,096 keys takes 15.7 us instead of 14.7.)
+constexpr int kRowsWarps = kStreamWarps;
+constexpr int kRowsThreads = kRowsWarps * 32;
+
 struct RowsShared {
   float cta_o[16][kD];      // this CTA's numerators, head by head
   float cta_ml[16][2];      // (max in log2 units, denominator); an empty CTA leaves (-inf, 0)
 };
 constexpr int kRowsLd = kD + 4;        // floats per head in a warp's partial result: numerators, max, denominator
 static_assert(16 * kRowsLd * 4 <= 2 * kStreamStageBytes, "a warp's partial result lies in its own ring");
-constexpr size_t kRowsSmem = static_cast<size_t>(kStreamWarps) * 2 * kStreamStageBytes + sizeof(RowsShared) + 16;
+constexpr size_t kRowsSmem = static_cast<size_t>(kRowsWarps) * 2 * kStreamStageBytes + sizeof(RowsShared) + 16;
 constexpr int kRowsMaxCluster = 8;
 
 __device__ __forceinline__ uint32_t rows_cluster_rank() {
@@ -59,29 +67,31 @@ __device__ __forceinline__ float2 rows_ld_cluster(const float* p, uint32_t rank)
 
 // HI: groups of more than 8 heads (rows g + 8 of the MMA tile are in use).
 template <bool HI>
-__global__ void __launch_bounds__(kStreamThreads, 1)
-decode_attn_rows_kernel(const DecodeArgs<bf16> a, const DecodeRope rope) {
+__global__ void __launch_bounds__(kRowsThreads, 1)
+decode_attn_rows_kernel(const DecodeArgs<bf16> a, int nrows, const DecodeRope rope) {
   constexpr int DB = kD / 32, DG = kD / 64;
   constexpr float kLog2e = 1.4426950408889634f;
   constexpr int CPR = kD / 8;            // 16-byte chunks per row
   constexpr int RPR = 32 / CPR;          // rows that one round of the warp's copies covers
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  RowsShared* sh = reinterpret_cast<RowsShared*>(smem_raw + kStreamWarps * 2 * kStreamStageBytes);
+  RowsShared* sh = reinterpret_cast<RowsShared*>(smem_raw + kRowsWarps * 2 * kStreamStageBytes);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int G = a.hq / a.hkv;
   const int csize = static_cast<int>(rows_cluster_size()), rank = static_cast<int>(rows_cluster_rank());
-  const int rowi = blockIdx.x / csize;                  // the cluster's row
+  // the cluster's rows: one, or (a launch of more rows than clusters are resident) several, one after another
+#pragma unroll 1
+  for (int rowi = blockIdx.x / csize; rowi < nrows; rowi += gridDim.x / csize) {
   const int item = rowi / a.hkv, kvh = rowi - item * a.hkv;
   // (items and block tables were written before the step's kernels began)
   const int4 info = a.items[item];
   const int tok = info.x, seq = info.y, ctx = info.z;
-  if (ctx <= 0) return;                                 // (the same for the whole cluster)
+  if (ctx <= 0) continue;                               // (the same for the whole cluster)
   const int lo = (a.window > 0 && ctx > a.window) ? ctx - a.window : 0;
   const bool fused = rope.cos != nullptr;
 
   // ---- this warp's run of sub-blocks
   const int sb_first = lo / kSub, n_sb = (ctx - 1) / kSub - sb_first + 1;
-  const int W = csize * kStreamWarps, wi = rank * kStreamWarps + warp;
+  const int W = csize * kRowsWarps, wi = rank * kRowsWarps + warp;
   const int per = n_sb / W, rem = n_sb - per * W;
   const int my_n = per + (wi < rem ? 1 : 0);
   const int my_sb = sb_first + wi * per + min(wi, rem);
@@ -378,15 +388,15 @@ decode_attn_rows_kernel(const DecodeArgs<bf16> a, const DecodeRope rope) {
   }
   __syncthreads();
   // ---- the CTA's warps in order (a warp without keys has max -inf and weighs nothing)
-  for (int idx = threadIdx.x; idx < G * (kD / 2); idx += kStreamThreads) {
+  for (int idx = threadIdx.x; idx < G * (kD / 2); idx += kRowsThreads) {
     const int r = idx / (kD / 2), d = (idx - r * (kD / 2)) * 2;
     float m = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < kStreamWarps; ++w)
+    for (int w = 0; w < kRowsWarps; ++w)
       m = fmaxf(m, reinterpret_cast<const float*>(smem_raw + w * 2 * kStreamStageBytes)[r * kRowsLd + kD]);
     float den = 0.f, n0 = 0.f, n1 = 0.f;
 #pragma unroll
-    for (int w = 0; w < kStreamWarps; ++w) {
+    for (int w = 0; w < kRowsWarps; ++w) {
       const float* pw = reinterpret_cast<const float*>(smem_raw + w * 2 * kStreamStageBytes) + r * kRowsLd;
       const float mw = pw[kD];
       const float f = mw == -INFINITY ? 0.f : ex2_approx(mw - m);
@@ -401,7 +411,7 @@ decode_attn_rows_kernel(const DecodeArgs<bf16> a, const DecodeRope rope) {
   // ---- the cluster's CTAs in order, by the first one
   rows_cluster_barrier();
   if (rank == 0) {
-    for (int idx = threadIdx.x; idx < G * (kD / 2); idx += kStreamThreads) {
+    for (int idx = threadIdx.x; idx < G * (kD / 2); idx += kRowsThreads) {
       const int r = idx / (kD / 2), d = (idx - r * (kD / 2)) * 2;
       float2 ml[kRowsMaxCluster], v[kRowsMaxCluster];
 #pragma unroll
@@ -427,7 +437,8 @@ decode_attn_rows_kernel(const DecodeArgs<bf16> a, const DecodeRope rope) {
       *reinterpret_cast<__nv_bfloat162*>(a.out + static_cast<size_t>(tok) * a.out_stride + (kvh * G + r) * kD + d) = hh;
     }
   }
-  rows_cluster_barrier();       // no CTA leaves while its shared memory may still be read
+  rows_cluster_barrier();       // no CTA leaves, or goes on to its next row, while its sums may still be read
+  }
 }
 
 }  // namespace rl

@@ -449,20 +449,22 @@ def attn_decode_streams(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vc
                   _ptr(out), out.stride(0), max_parts, nitems, num_heads, num_kv_heads, page_size, impl))
 
 
-_rows_cluster: Dict[Tuple[int, int, int], int] = {}
+_rows_cluster: Dict[Tuple[int, int, int], Tuple[int, int]] = {}
 
 
-def attn_decode_rows_cluster(nitems: int, num_kv_heads: int, head_dim: int, device: torch.device) -> int:
-    """CTAs per row that ``attn_decode`` with impl 4 would use for a launch of ``nitems`` items (0: it does not
-    take such a launch: more rows than clusters can be resident, or no tensor-core decode kernel for this
-    head size)."""
+def attn_decode_rows_cluster(nitems: int, num_kv_heads: int, head_dim: int, device: torch.device) -> Tuple[int, int]:
+    """(CTAs per row, clusters resident at once) that ``attn_decode`` with impl 4 would use for a launch of
+    ``nitems`` items; (0, 0) if it does not take such a launch (no tensor-core decode kernel for this head
+    size).  With fewer resident clusters than rows a cluster takes several rows, one after another."""
     if device.type != "cuda" or head_dim not in (64, 128) or nitems <= 0:
-        return 0
+        return 0, 0
     key = (device.index if device.index is not None else torch.cuda.current_device(), nitems * num_kv_heads, head_dim)
     if key not in _rows_cluster:
-        f = _fn(_attn(head_dim), "rl_attn_decode_rows_cluster", [c_int, c_int])
+        f = _fn(_attn(head_dim), "rl_attn_decode_rows_cluster", [c_int, c_int, c_void_p])
+        resident = ctypes.c_int(0)
         with torch.cuda.device(key[0]):
-            _rows_cluster[key] = int(f(nitems, num_kv_heads))
+            csize = int(f(nitems, num_kv_heads, ctypes.byref(resident)))
+        _rows_cluster[key] = (csize, resident.value)
     return _rows_cluster[key]
 
 
@@ -470,18 +472,23 @@ def attn_decode_rows_pays(nitems: int, num_kv_heads: int, head_dim: int, max_ctx
                           device: torch.device) -> bool:
     """Whether the decode kernel of one cluster per (item, kv head) (impl 4) is expected to beat the others for
     a launch of ``nitems`` rows of at most ``max_ctx`` and together ``sum_ctx`` keys.  Its time goes with the
-    longest row (a row has its cluster's SMs only), the streaming kernel's with all keys plus the count and
-    merge of its pieces.  The constants are measured on a B200 (head size 64, 8 kv heads): 4.4 us plus
-    1.7 us per 32-key sub-block of a warp's run, against 8 us plus the keys' bytes at 6 TB/s."""
-    csize = attn_decode_rows_cluster(nitems, num_kv_heads, head_dim, device)
-    if csize <= 0 or max_ctx <= 0:
+    longest row (a row has its cluster's SMs only) times the rows a cluster takes in turn, the streaming
+    kernel's with all keys plus the count and merge of its pieces.  The constants are fitted to times on a
+    B200 (head size 64, 8 kv heads, batches 1 to 128 at 512 to 8,192 keys): 4.4 us plus, per row a cluster
+    takes, 1.7 us per 32-key sub-block of a warp's run (and 0.7 + 0.25 x turns when it takes more than
+    one), against 8 us plus the keys' bytes at 5.3 TB/s."""
+    csize, resident = attn_decode_rows_cluster(nitems, num_kv_heads, head_dim, device)
+    if csize <= 0 or resident <= 0 or max_ctx <= 0:
         return False
     if window > 0:
         max_ctx, sum_ctx = min(max_ctx, window), min(sum_ctx, nitems * window)
-    warps = csize * (12 if head_dim == 64 else 6)
+    warps = csize * int(_fn(_attn(head_dim), "rl_attn_decode_rows_warps", [])())
     sub_blocks = (max_ctx + 31) // 32
-    t_rows = 4.4 + 1.7 * (head_dim / 64.0) * ((sub_blocks + warps - 1) // warps)
-    t_stream = 8.0 + sum_ctx * num_kv_heads * head_dim * 4 / 6.0e6
+    rows = nitems * num_kv_heads
+    turns = (rows + resident - 1) // resident
+    per_turn = 1.7 * (head_dim / 64.0) * ((sub_blocks + warps - 1) // warps) + (0.7 + 0.25 * turns if turns > 1 else 0.0)
+    t_rows = 4.4 + turns * per_turn
+    t_stream = 8.0 + sum_ctx * num_kv_heads * head_dim * 4 / 5.3e6
     return t_rows < t_stream
 
 

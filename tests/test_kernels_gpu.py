@@ -360,12 +360,15 @@ def test_attention_decode_rows_kernel(Hq, Hkv, D, page_size):
 
 
 def test_attention_decode_rows_kernel_long_rows_and_many_rows():
-    """Clusters of 2 (64 rows of 4,000 keys: every warp a run of several sub-blocks), of 8 (8 rows), and of
-    one CTA (128 rows of many lengths)."""
+    """Clusters of 2 (64 rows of 4,000 keys: every warp a run of several sub-blocks), of 8 (8 rows), of one
+    CTA (128 rows of many lengths), and more rows than clusters are resident (320 and 1,000 rows: a CTA takes
+    several, one after another, and its rings and sums are used again)."""
     decode_only_case(32, 8, 64, [4000 + 13 * i for i in range(8)], 16, 0, 4, seed=61)
     decode_only_case(32, 8, 64, [4096], 16, 0, 4, seed=62)
     decode_only_case(16, 8, 128, [1500, 3000, 77, 2047, 2048, 4096, 4097], 32, 0, 4, seed=63)
     decode_only_case(32, 8, 64, [2000 + 97 * i for i in range(12)] + [1, 130, 5, 640], 64, 1000, 4, seed=64)
+    decode_only_case(32, 8, 64, [1 + (37 * i) % 700 for i in range(40)], 16, 0, 4, seed=65)
+    decode_only_case(8, 8, 128, [1 + (53 * i) % 300 for i in range(125)], 32, 100, 4, seed=66)
     assert int(kernels.tc_status(torch.device(DEV)).item()) == 0
 
 

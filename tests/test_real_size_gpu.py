@@ -7,10 +7,13 @@ in bfloat16, on the paths that only these sizes reach:
 * a 300-token prompt whole and cut at 130 / 170: the tcgen05 gate/up product, the library
   products at hundreds of rows, the tcgen05 prompt attention without and with a cached past,
   the head over 128,256 columns;
-* 40 single-token steps of 8 sequences at contexts beyond 2,048 keys: more than 1,024
-  (item, head, partition) units, so the streaming decode attention with the rotation and the
-  cache write inside runs in the engine, after the skinny products with the norms handed over;
-  eagerly and, in bfloat16, as CUDA graphs of the padded batch with the sampler inside;
+* 40 single-token steps of 8 sequences at contexts beyond 2,048 keys: the decode attention of
+  one cluster per (sequence, kv head), and with that one switched off the streaming kernel (more
+  than 1,024 (item, head, partition) units), both with the rotation and the cache write inside,
+  after the skinny products with the norms handed over; eagerly and, in bfloat16, as CUDA graphs
+  of the padded batch with the sampler inside;
+* 8 sequences of very different lengths and then 8 of similar ones in one engine: the engine
+  chooses the streaming kernel for the first and the clusters for the second, a CUDA graph each;
 * a pure-decode batch of 24 sequences: library products at 24 rows and a launch of many
   short attention rows;
 * generation through the scheduler with CUDA graphs and asynchronous scheduling, tokens fed
@@ -108,11 +111,14 @@ def test_prompt_whole_and_cut_with_a_cached_past(dtype, models):
     eng.runner.cache.check_invariants()
 
 
-@pytest.mark.parametrize("dtype,graphs", [("float32", False), ("bfloat16", False), ("bfloat16", True)])
-def test_eight_sequences_decoding_beyond_2048_keys(dtype, graphs, models):
-    """8 sequences x 8 kv heads x 17 or 18 partitions of 128 keys are more than 1,024 units: the decode
-    attention of these steps is the streaming kernel, which also rotates q and k and writes the cache."""
+@pytest.mark.parametrize("dtype,graphs,clusters", [("float32", False, True), ("bfloat16", False, True),
+                                                   ("bfloat16", True, True), ("bfloat16", True, False)])
+def test_eight_sequences_decoding_beyond_2048_keys(dtype, graphs, clusters, models, monkeypatch):
+    """8 sequences of similar length: the decode attention of these steps gives every (sequence, kv head) a
+    cluster of two CTAs.  With that kernel switched off, 8 sequences x 8 kv heads x 17 or 18 partitions of
+    128 keys are more than 1,024 units: the streaming kernel.  Both also rotate q and k and write the cache."""
     from redline_b200.ops import kernels
+    monkeypatch.setenv("REDLINE_DECODE_ROWS", "1" if clusters else "0")
     w = models[dtype][1]
     eng = real_engine(models, dtype, cuda_graphs=graphs)
     steps = 40
@@ -129,6 +135,8 @@ def test_eight_sequences_decoding_beyond_2048_keys(dtype, graphs, models):
         for i in range(8):
             got[i].append(out[i:i + 1])
     assert (eng.runner.num_graph_steps - graph_steps == steps - 1) if graphs else eng.runner.num_graph_steps == 0
+    if graphs:                                            # which kernel the mixers named for these steps
+        assert {v for _, variants in eng.runner._graphs for v in variants} == ({4} if clusters else {0})
     eng.runner.check_status()
     assert int(kernels.tc_status(eng.runner.device).item()) == 0
     for i, (s, n) in enumerate(zip(seqs, lens)):
@@ -138,10 +146,44 @@ def test_eight_sequences_decoding_beyond_2048_keys(dtype, graphs, models):
     eng.runner.cache.check_invariants()
 
 
+def test_lengths_decide_the_decode_attention_kernel(models):
+    """One engine, CUDA graphs on: 8 sequences of which one is fifty times as long as the others decode
+    together (the keys are shared among all warps: the streaming kernel), then 8 of similar length (a cluster
+    per row).  The logits of both against the plain implementation, and one graph for each choice."""
+    from redline_b200.ops import kernels
+    dtype = "bfloat16"
+    w = models[dtype][1]
+    dev = torch.device("cuda")
+    assert kernels.attn_decode_rows_pays(8, 8, 64, 4096, 8 * 4096, 0, dev)
+    assert not kernels.attn_decode_rows_pays(8, 8, 64, 4096, 4096 + 7 * 128, 0, dev)
+    assert not kernels.attn_decode_rows_pays(64, 8, 64, 516, 64 * 516, 0, dev)
+    eng = real_engine(models, dtype, cuda_graphs=True)
+    steps = 6
+    for phase, lens in enumerate([[2100, 40, 41, 42, 43, 44, 45, 46], [300 + 3 * i for i in range(8)]]):
+        seqs = [random_tokens(V, n + steps, 80 + 10 * phase + i) for i, n in enumerate(lens)]
+        got = [[] for _ in seqs]
+        for i, (s, n) in enumerate(zip(seqs, lens)):
+            got[i].append(eng.step_tokens([(i, s[:n], [n - 1])]).cpu().numpy())
+        for t in range(steps - 1):
+            out = eng.step_tokens([(i, s[n + t:n + t + 1], [0]) for i, (s, n) in enumerate(zip(seqs, lens))],
+                                  graphs=True).cpu().numpy()
+            for i in range(8):
+                got[i].append(out[i:i + 1])
+        chosen = {v for _, variants in eng.runner._graphs for v in variants}
+        assert chosen == ({0} if phase == 0 else {0, 4}), chosen
+        for i, (s, n) in enumerate(zip(seqs, lens)):
+            want = oracle_rows(w, s[:n + steps - 1], range(n - 1, n + steps - 1), dtype)
+            check(np.concatenate(got[i]), want, dtype, f"phase {phase}, sequence {i}")
+            eng.close_request(i)
+    eng.runner.check_status()
+    eng.runner.cache.check_invariants()
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_twenty_four_sequences_decoding_together(dtype, models):
-    """17 to 127 rows: the products of these steps are library calls, the attention a launch of many
-    rows of five or six partitions each (24 x 8 x 6 = 1,152 units)."""
+    """17 to 64 rows: the products of these steps are the tcgen05 products with the weights as the wide
+    operand (K split over a cluster), the attention a launch of 192 rows of five or six partitions each:
+    more rows than clusters are resident, so a cluster takes two, one after the other."""
     w = models[dtype][1]
     eng = real_engine(models, dtype, kv_cache_tokens=24 * 768, max_seq_len=768, max_num_seqs=24, max_logit_rows=64)
     steps = 8
