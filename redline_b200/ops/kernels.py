@@ -450,6 +450,7 @@ def attn_decode_streams(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vc
 
 
 _rows_cluster: Dict[Tuple[int, int, int], Tuple[int, int]] = {}
+_rows_warps: Dict[int, int] = {}
 
 
 def attn_decode_rows_cluster(nitems: int, num_kv_heads: int, head_dim: int, device: torch.device) -> Tuple[int, int]:
@@ -482,7 +483,9 @@ def attn_decode_rows_pays(nitems: int, num_kv_heads: int, head_dim: int, max_ctx
         return False
     if window > 0:
         max_ctx, sum_ctx = min(max_ctx, window), min(sum_ctx, nitems * window)
-    warps = csize * int(_fn(_attn(head_dim), "rl_attn_decode_rows_warps", [])())
+    if head_dim not in _rows_warps:
+        _rows_warps[head_dim] = int(_fn(_attn(head_dim), "rl_attn_decode_rows_warps", [])())
+    warps = csize * _rows_warps[head_dim]
     sub_blocks = (max_ctx + 31) // 32
     rows = nitems * num_kv_heads
     turns = (rows + resident - 1) // resident

@@ -175,8 +175,14 @@ class GQAttention(Mixer):
         p, rt = self.params, self.rt
         if rt.dtype != torch.bfloat16 or ctx.num_decode <= 0 or os.environ.get("REDLINE_DECODE_ROWS", "1") == "0":
             return 0
-        return 4 if kernels.attn_decode_rows_pays(ctx.num_decode, p.num_kv_heads, p.head_dim, ctx.decode_max_ctx,
-                                                  ctx.decode_sum_ctx, p.window, rt.device) else 0
+        # (the layers of a model mostly ask the same question: the step's context keeps the answers)
+        memo = ctx.__dict__.setdefault("_decode_variants", {})
+        key = (p.num_kv_heads, p.head_dim, p.window)
+        if key not in memo:
+            memo[key] = 4 if kernels.attn_decode_rows_pays(ctx.num_decode, p.num_kv_heads, p.head_dim,
+                                                           ctx.decode_max_ctx, ctx.decode_sum_ctx, p.window,
+                                                           rt.device) else 0
+        return memo[key]
 
     def _counters(self, max_items: int) -> torch.Tensor:
         """Arrival counters of the decode kernel's fused merge: zero between launches."""
