@@ -1189,6 +1189,17 @@ int launch_decode(const void* q, int q_stride, const void* kc, const void* vc, c
       if (e != cudaSuccess) return static_cast<int>(e);
       if (cx < 1) return static_cast<int>(cudaErrorNotSupported);
       const int clusters = rows < resident ? rows : resident;
+      // more rows than clusters: the warps of a CTA in as few groups (a divisor of their number) as give
+      // every row a group at once, else one warp to a row and several rows in turn
+      int groups = 1;
+      if (rows > resident) {
+        groups = kRowsWarps;
+        for (int d = 2; d < kRowsWarps; ++d)
+          if (kRowsWarps % d == 0 && static_cast<long long>(resident) * d >= rows) {
+            groups = d;
+            break;
+          }
+      }
       DecodeRope sr = {};
       if (rope != nullptr && rope->cos != nullptr) {
         sr.cos = rope->cos;
@@ -1215,8 +1226,8 @@ int launch_decode(const void* q, int q_stride, const void* kc, const void* vc, c
       cfg.attrs = at;
       cfg.numAttrs = pdl_enabled() ? 2 : 1;
       if (hq / hkv > 8)
-        return static_cast<int>(cudaLaunchKernelEx(&cfg, decode_attn_rows_kernel<true>, a, rows, sr));
-      return static_cast<int>(cudaLaunchKernelEx(&cfg, decode_attn_rows_kernel<false>, a, rows, sr));
+        return static_cast<int>(cudaLaunchKernelEx(&cfg, decode_attn_rows_kernel<true>, a, rows, groups, sr));
+      return static_cast<int>(cudaLaunchKernelEx(&cfg, decode_attn_rows_kernel<false>, a, rows, groups, sr));
     }
     if (decode_streams(q, q_stride, kc, vc, part_o, counters, out, out_stride, max_parts, nitems, hq, hkv, page_size,
                        impl)) {

@@ -12,8 +12,9 @@
 // nothing waits on a flag: the streaming kernel spends 8 of its 19 microseconds at batch 8 x 4,096 keys on
 // exactly that.
 //
-// A launch with more rows than clusters can be resident runs clusters of one CTA that take several rows
-// each, one after another.
+// A launch with more rows than clusters can be resident runs clusters of one CTA whose warps form groups,
+// a row to each group at the same time (and, if that is still not enough, several one after another); a
+// group adds its warps' results at a barrier of its own and writes the row itself.
 //
 // The cost: a row has its cluster's SMs and no others.  With rows of very different lengths the longest
 // one sets the kernel's time, where the streaming kernel shares all keys among all warps; the caller
@@ -68,7 +69,7 @@ __device__ __forceinline__ float2 rows_ld_cluster(const float* p, uint32_t rank)
 // HI: groups of more than 8 heads (rows g + 8 of the MMA tile are in use).
 template <bool HI>
 __global__ void __launch_bounds__(kRowsThreads, 1)
-decode_attn_rows_kernel(const DecodeArgs<bf16> a, int nrows, const DecodeRope rope) {
+decode_attn_rows_kernel(const DecodeArgs<bf16> a, int nrows, int groups, const DecodeRope rope) {
   constexpr int DB = kD / 32, DG = kD / 64;
   constexpr float kLog2e = 1.4426950408889634f;
   constexpr int CPR = kD / 8;            // 16-byte chunks per row
@@ -81,9 +82,15 @@ decode_attn_rows_kernel(const DecodeArgs<bf16> a, int nrows, const DecodeRope ro
   // (Like the streaming kernel it does not tell its dependents to launch early: measured in the decode step,
   // at the kernel's start or after the runs, the step then takes 1.18 ms instead of 0.82: the kernels after it
   // move in and wait where this kernel's and the next one's CTAs should run.)
-  // the cluster's rows: one, or (a launch of more rows than clusters are resident) several, one after another
+  // The cluster's row.  A launch with more rows than clusters can be resident runs clusters of ONE CTA whose
+  // warps form `groups` groups, a row to each at the same time (rows 0 .. CTAs - 1 go to the first groups
+  // of the CTAs, the next to their second groups, ...: as many SMs as there are stream), and if that is not
+  // enough, a group takes several rows one after another.
+  const int gsize = kRowsWarps / groups;                // warps of a group (groups divides kRowsWarps)
+  const int gi = warp / gsize, wg = warp - gi * gsize;
+  const int nclusters = gridDim.x / csize;
 #pragma unroll 1
-  for (int rowi = blockIdx.x / csize; rowi < nrows; rowi += gridDim.x / csize) {
+  for (int rowi = gi * nclusters + blockIdx.x / csize; rowi < nrows; rowi += groups * nclusters) {
   const int item = rowi / a.hkv, kvh = rowi - item * a.hkv;
   // (items and block tables were written before the step's kernels began)
   const int4 info = a.items[item];
@@ -94,7 +101,7 @@ decode_attn_rows_kernel(const DecodeArgs<bf16> a, int nrows, const DecodeRope ro
 
   // ---- this warp's run of sub-blocks
   const int sb_first = lo / kSub, n_sb = (ctx - 1) / kSub - sb_first + 1;
-  const int W = csize * kRowsWarps, wi = rank * kRowsWarps + warp;
+  const int W = csize * gsize, wi = rank * gsize + wg;
   const int per = n_sb / W, rem = n_sb - per * W;
   const int my_n = per + (wi < rem ? 1 : 0);
   const int my_sb = sb_first + wi * per + min(wi, rem);
@@ -388,6 +395,32 @@ decode_attn_rows_kernel(const DecodeArgs<bf16> a, int nrows, const DecodeRope ro
         *reinterpret_cast<float4*>(dst + 4) = make_float4(o[dg][4][2 * h + e], o[dg][5][2 * h + e], o[dg][6][2 * h + e], o[dg][7][2 * h + e]);
       }
     if (t == 0) *reinterpret_cast<float2*>(mine + r * kRowsLd + kD) = make_float2(h ? m_hi : m_lo, h ? l_hi : l_lo);
+  }
+  if (csize == 1) {
+    // ---- a cluster of one CTA: the group's warps in order, straight to the output (a warp without keys has
+    // max -inf and weighs nothing); only the group meets, at a barrier of its own
+    const int gthreads = gsize * 32;
+    asm volatile("bar.sync %0, %1;" ::"r"(1 + gi), "r"(gthreads) : "memory");
+    for (int idx = wg * 32 + lane; idx < G * (kD / 2); idx += gthreads) {
+      const int r = idx / (kD / 2), d = (idx - r * (kD / 2)) * 2;
+      float m = -INFINITY;
+      for (int w = gi * gsize; w < (gi + 1) * gsize; ++w)
+        m = fmaxf(m, reinterpret_cast<const float*>(smem_raw + w * 2 * kStreamStageBytes)[r * kRowsLd + kD]);
+      float den = 0.f, n0 = 0.f, n1 = 0.f;
+      for (int w = gi * gsize; w < (gi + 1) * gsize; ++w) {
+        const float* pw = reinterpret_cast<const float*>(smem_raw + w * 2 * kStreamStageBytes) + r * kRowsLd;
+        const float mw = pw[kD];
+        const float f = mw == -INFINITY ? 0.f : ex2_approx(mw - m);
+        const float2 v = *reinterpret_cast<const float2*>(pw + d);
+        den += f * pw[kD + 1];
+        n0 += f * v.x;
+        n1 += f * v.y;
+      }
+      const __nv_bfloat162 hh = __floats2bfloat162_rn(n0 / den, n1 / den);
+      *reinterpret_cast<__nv_bfloat162*>(a.out + static_cast<size_t>(tok) * a.out_stride + (kvh * G + r) * kD + d) = hh;
+    }
+    asm volatile("bar.sync %0, %1;" ::"r"(1 + gi), "r"(gthreads) : "memory");     // before the rings are used again
+    continue;
   }
   __syncthreads();
   // ---- the CTA's warps in order (a warp without keys has max -inf and weighs nothing)

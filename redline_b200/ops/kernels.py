@@ -475,9 +475,9 @@ def attn_decode_rows_pays(nitems: int, num_kv_heads: int, head_dim: int, max_ctx
     a launch of ``nitems`` rows of at most ``max_ctx`` and together ``sum_ctx`` keys.  Its time goes with the
     longest row (a row has its cluster's SMs only) times the rows a cluster takes in turn, the streaming
     kernel's with all keys plus the count and merge of its pieces.  The constants are fitted to times on a
-    B200 (head size 64, 8 kv heads, batches 1 to 128 at 512 to 8,192 keys): 4.4 us plus, per row a cluster
-    takes, 1.7 us per 32-key sub-block of a warp's run (and 0.7 + 0.25 x turns when it takes more than
-    one), against 8 us plus the keys' bytes at 5.3 TB/s."""
+    B200 (head size 64, 8 kv heads, batches 1 to 128 at 512 to 8,192 keys): 4.4 us plus, per row a group of
+    warps takes, 1.7 us per 32-key sub-block of a warp's run (and 0.7 + 0.25 x turns when it takes more than
+    one), but no less than the keys' bytes at 6.2 TB/s; against 8 us plus the keys' bytes at 5.3 TB/s."""
     csize, resident = attn_decode_rows_cluster(nitems, num_kv_heads, head_dim, device)
     if csize <= 0 or resident <= 0 or max_ctx <= 0:
         return False
@@ -485,13 +485,18 @@ def attn_decode_rows_pays(nitems: int, num_kv_heads: int, head_dim: int, max_ctx
         max_ctx, sum_ctx = min(max_ctx, window), min(sum_ctx, nitems * window)
     if head_dim not in _rows_warps:
         _rows_warps[head_dim] = int(_fn(_attn(head_dim), "rl_attn_decode_rows_warps", [])())
-    warps = csize * _rows_warps[head_dim]
-    sub_blocks = (max_ctx + 31) // 32
+    warps = _rows_warps[head_dim]
     rows = nitems * num_kv_heads
-    turns = (rows + resident - 1) // resident
-    per_turn = 1.7 * (head_dim / 64.0) * ((sub_blocks + warps - 1) // warps) + (0.7 + 0.25 * turns if turns > 1 else 0.0)
-    t_rows = 4.4 + turns * per_turn
-    t_stream = 8.0 + sum_ctx * num_kv_heads * head_dim * 4 / 5.3e6
+    groups = 1                      # (as the launcher chooses them)
+    if rows > resident:
+        groups = next((d for d in range(2, warps) if warps % d == 0 and resident * d >= rows), warps)
+    turns = (rows + resident * groups - 1) // (resident * groups)
+    sub_blocks = (max_ctx + 31) // 32
+    per_row = csize * (warps // groups)
+    nbytes = sum_ctx * num_kv_heads * head_dim * 4
+    per_turn = 1.7 * (head_dim / 64.0) * ((sub_blocks + per_row - 1) // per_row) + (0.7 + 0.25 * turns if turns > 1 else 0.0)
+    t_rows = 4.4 + max(turns * per_turn, nbytes / 6.2e6)
+    t_stream = 8.0 + nbytes / 5.3e6
     return t_rows < t_stream
 
 

@@ -156,7 +156,8 @@ def test_lengths_decide_the_decode_attention_kernel(models):
     dev = torch.device("cuda")
     assert kernels.attn_decode_rows_pays(8, 8, 64, 4096, 8 * 4096, 0, dev)
     assert not kernels.attn_decode_rows_pays(8, 8, 64, 4096, 4096 + 7 * 128, 0, dev)
-    assert not kernels.attn_decode_rows_pays(64, 8, 64, 516, 64 * 516, 0, dev)
+    assert kernels.attn_decode_rows_pays(64, 8, 64, 516, 64 * 516, 0, dev)                 # (three warps to a row)
+    assert not kernels.attn_decode_rows_pays(64, 8, 64, 4096, 4096 + 63 * 64, 0, dev)
     eng = real_engine(models, dtype, cuda_graphs=True)
     steps = 6
     for phase, lens in enumerate([[2100, 40, 41, 42, 43, 44, 45, 46], [300 + 3 * i for i in range(8)]]):
