@@ -171,7 +171,8 @@ __device__ uint32_t select_top_p(const float* l, int vocab, float mx, float inv_
   return prefix;
 }
 
-// First stage for greedy rows: the row is cut into kSampleChunks pieces, one CTA each, which
+// First stage for greedy rows: the row is cut into pieces (kSampleChunks of them, or a quarter as many
+// when the launch has many rows: CTAs of 2,000 values each are mostly start and end), one CTA each, which
 // leave (max, arg max, sum of exp(l - max)) of their piece.  sample_kernel combines them.
 constexpr int kSampleChunks = 64;
 
@@ -182,19 +183,22 @@ struct ChunkStat {
   float pad;
 };
 
+template <int kSampleHeld>
 __global__ void __launch_bounds__(256)
-sample_partial_kernel(const float* __restrict__ logits, int vocab, int ld, ChunkStat* __restrict__ stats) {
+sample_partial_kernel(const float* __restrict__ logits, int vocab, int ld, ChunkStat* __restrict__ stats, int chunks) {
   pdl_launch();
   pdl_wait();
   __shared__ Best bscratch[32];
   __shared__ float fscratch[32];
   const int row = blockIdx.x, chunk = blockIdx.y;
-  const int per = (vocab + kSampleChunks - 1) / kSampleChunks;
+  const int per = (vocab + chunks - 1) / chunks;
   const int lo = chunk * per, hi = min(vocab, lo + per);
   const float* l = logits + static_cast<size_t>(row) * ld;
+  // (the second stage reads kSampleChunks slots a row: those beyond this launch's pieces are marked empty)
+  if (chunk == 0 && threadIdx.x < kSampleChunks - chunks)
+    stats[row * kSampleChunks + chunks + threadIdx.x] = ChunkStat{-FLT_MAX, 0x7fffffff, 0.f, 0.f};
   // A thread's first kSampleHeld values stay in registers (all their loads are in flight together, and the
   // piece is read once); a piece longer than 256 * kSampleHeld goes on through memory.
-  constexpr int kSampleHeld = 8;
   float v[kSampleHeld];
 #pragma unroll
   for (int j = 0; j < kSampleHeld; ++j) {
@@ -347,7 +351,12 @@ int rl_sample(const float* logits, int rows, int vocab, int ld, const float* tem
   if (rows <= 0) return 0;
   ChunkStat* stats = reinterpret_cast<ChunkStat*>(scratch);
   if (stats != nullptr) {
-    launch_kernel(sample_partial_kernel, dim3(rows, kSampleChunks), dim3(256), 0, stream, logits, vocab, ld, stats);
+    if (rows >= 16)
+      launch_kernel(sample_partial_kernel<32>, dim3(rows, kSampleChunks / 4), dim3(256), 0, stream, logits, vocab, ld,
+                    stats, kSampleChunks / 4);
+    else
+      launch_kernel(sample_partial_kernel<8>, dim3(rows, kSampleChunks), dim3(256), 0, stream, logits, vocab, ld,
+                    stats, kSampleChunks);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return static_cast<int>(e);
   }

@@ -43,6 +43,17 @@ def test_greedy_ties_and_logprobs():
     assert tok.tolist() == [int(ref[i].argmax()) if i != 3 else 17 for i in range(12)]
     want = torch.log_softmax(ref, -1)[torch.arange(12), torch.tensor(tok.astype(np.int64))]
     assert np.abs(lp - want.numpy()).max() < 1e-4
+    # 16 rows and more: the first stage cuts a row into fewer, longer pieces (and marks the unused slots
+    # empty); a vocabulary that is no multiple of anything, a tie across two pieces, a maximum in the last one
+    for V, R in [(128256, 16), (331, 20), (50001, 33)]:
+        l = torch.randn(R, V, device=DEV)
+        l[1, 5] = l[1, V - 2] = l[1].max() + 2.0
+        l[2, V - 1] = 40.0
+        tok, lp = run(l, 0.0, 0, 1.0, 0, 0)
+        ref = l.double().cpu()
+        assert tok.tolist() == [int(ref[i].argmax()) if i != 1 else 5 for i in range(R)]
+        want = torch.log_softmax(ref, -1)[torch.arange(R), torch.tensor(tok.astype(np.int64))]
+        assert np.abs(lp - want.numpy()).max() < 1e-4
 
 
 @pytest.mark.parametrize("T,k,p", [(1.0, 0, 1.0), (0.7, 5, 1.0), (1.3, 0, 0.8), (0.9, 20, 0.6)])
