@@ -14,6 +14,7 @@ Error cases follow src/cuda/model/weights.cpp:180-246 and src/core/safetensors.c
 
 from __future__ import annotations
 
+import sys
 from typing import Dict, Iterable, List, Tuple
 
 import torch
@@ -158,6 +159,12 @@ def load(reader: CheckpointReader, expected: Dict[str, TensorSpec], dtype: torch
             n *= int(x)
         offsets.append(total)
         total += (n * torch.empty((), dtype=dt).element_size() + ALIGN - 1) // ALIGN * ALIGN
+    narrowed = sorted(m for _, members, _, dt in plan for m in members
+                      if dt == torch.bfloat16 and reader.tensor(m).dtype == torch.float16)
+    if narrowed:
+        # said once and aloud: float16 has three more mantissa bits than the bfloat16 the engine computes in
+        print(f"[redline_b200] {reader.model_dir}: {len(narrowed)} float16 tensors are converted to bfloat16 "
+              f"(first: {narrowed[0]}); --dtype float32 keeps every stored bit", file=sys.stderr, flush=True)
     up = BlobUploader(total, device)
     out: Dict[str, torch.Tensor] = {}
     for (key, members, shape, dt), off in zip(plan, offsets):

@@ -83,13 +83,16 @@ def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path):
         assert word in msg
 
 
-def test_dtypes_kept_and_head_tied(tmp_path):
+def test_dtypes_kept_and_head_tied(tmp_path, capsys):
     w = P.random_weights(C.TINY_B, 1, dtype=torch.bfloat16)
     w["model.norm.weight"] = w["model.norm.weight"].float()               # stored in 32-bit: stays
     w["model.layers.0.mlp.down_proj.weight"] = w["model.layers.0.mlp.down_proj.weight"].to(torch.float16)
     P.write_model_dir(str(tmp_path), C.TINY_B, w)
     m = cpu_model(C.TINY_B)
+    capsys.readouterr()
     m.load_weights(CheckpointReader(str(tmp_path)))
+    said = capsys.readouterr().err                                          # float16 is narrowed, and said so
+    assert "1 float16 tensors are converted to bfloat16" in said and "down_proj" in said
     assert m.final_norm.weight.dtype == torch.float32
     assert m.blocks[0].ffn.w_down.dtype == torch.bfloat16
     assert m.embedding.weight.dtype == torch.bfloat16
@@ -98,6 +101,7 @@ def test_dtypes_kept_and_head_tied(tmp_path):
     assert torch.equal(m.blocks[2].mixer.w_qkv[:q.shape[0]], q)
     m32 = cpu_model(C.TINY_B, torch.float32)
     m32.load_weights(CheckpointReader(str(tmp_path)))
+    assert "float16" not in capsys.readouterr().err                         # (a float32 engine keeps every bit)
     assert m32.embedding.weight.dtype == torch.float32 and m32.blocks[1].mixer.w_qkv.dtype == torch.float32
     # untied configuration whose file has no lm_head: the table is shared all the same
     wa = P.random_weights(C.TINY_A, 1, dtype=torch.bfloat16)
