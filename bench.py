@@ -309,13 +309,13 @@ def profile_prefill(args) -> int:
         model = write_model(tmp, args.layers)
         T = PREFILL_TOKENS
         eng = Engine(model, dtype="bfloat16", max_num_seqs=2, max_num_batched_tokens=T, max_seq_len=T + 16,
-                     kv_cache_tokens=2 * T + 64, cuda_graphs=False, async_scheduling=False)
+                     kv_cache_tokens=2 * T + 64, cuda_graphs=True, async_scheduling=False)
         toks = np.random.RandomState(1).randint(0, eng.vocab_size, size=T).tolist()
         for i in range(4):
             torch.cuda.synchronize()
             if i == 3:
                 torch.cuda.profiler.start()
-            eng.step_tokens([("p", toks, [T - 1])])
+            eng.step_tokens([("p", toks, [T - 1])], graphs=True)       # (as prefill_run: the step is a CUDA graph)
             torch.cuda.synchronize()
             if i == 3:
                 torch.cuda.profiler.stop()
@@ -331,12 +331,13 @@ def prefill_run(model: str, tokens: int, reps: int = 6, warmup: int = 3) -> Dict
     position on the device).  "ms": per prompt when ``reps`` prompts are submitted one after another
     between one pair of CUDA events (the host's preparation of a prompt then runs while the GPU works on
     the one before, as in serving); "latency_ms": one prompt alone on an idle GPU, host preparation
-    included (median of ``reps``)."""
+    included (median of ``reps``).  A step that is one full portion of a prompt is replayed as a CUDA graph,
+    sampler included, as in generation."""
     import numpy as np
     import torch
     from redline_b200.engine.engine import Engine
     eng = Engine(model, dtype="bfloat16", max_num_seqs=2, max_num_batched_tokens=tokens, max_seq_len=tokens + 16,
-                 kv_cache_tokens=2 * tokens + 64, cuda_graphs=False, async_scheduling=False)
+                 kv_cache_tokens=2 * tokens + 64, cuda_graphs=True, async_scheduling=False)
     rng = np.random.RandomState(1)
     toks = rng.randint(0, eng.vocab_size, size=tokens).tolist()
     times = []
@@ -344,7 +345,7 @@ def prefill_run(model: str, tokens: int, reps: int = 6, warmup: int = 3) -> Dict
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
         a.record()
-        eng.step_tokens([("p", toks, [tokens - 1])])
+        eng.step_tokens([("p", toks, [tokens - 1])], graphs=True)
         b.record()
         torch.cuda.synchronize()
         eng.close_request("p")
@@ -354,7 +355,7 @@ def prefill_run(model: str, tokens: int, reps: int = 6, warmup: int = 3) -> Dict
     torch.cuda.synchronize()
     a.record()
     for i in range(reps):
-        eng.step_tokens([(f"q{i}", toks, [tokens - 1])])
+        eng.step_tokens([(f"q{i}", toks, [tokens - 1])], graphs=True)
         eng.close_request(f"q{i}")
     b.record()
     torch.cuda.synchronize()

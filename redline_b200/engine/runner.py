@@ -100,9 +100,10 @@ class ModelRunner:
         self._states = [self.states.of_call(i) for i in range(len(order))]
         self.model.nvtx_layers = cfg.nvtx_layers
         self.profiler = None                       # engine.profiler.OpProfiler while per-op profiling is on
-        # one graph per padded size and per answer of the mixers to "which kernel for the single tokens"
-        self._graphs: Dict[Tuple[int, Tuple[int, ...]], torch.cuda.CUDAGraph] = {}
-        self._graph_kernels: Dict[Tuple[int, Tuple[int, ...]], int] = {}   # kernels of this package in each graph
+        # one graph per padded size and per answer of the mixers to "which kernel for the single tokens", and
+        # one per shape of a full prompt portion (see _chunk_key)
+        self._graphs: Dict[tuple, torch.cuda.CUDAGraph] = {}
+        self._graph_kernels: Dict[tuple, int] = {}   # kernels of this package in each graph
         self.num_kernel_launches = 0               # kernels of this package run by steps so far
         self.num_graph_steps = 0
         self.num_eager_steps = 0
@@ -141,14 +142,16 @@ class ModelRunner:
         ``tokens[:R]`` / ``logprobs[:R]`` are filled too.  A segment with ``src_row`` >= 0
         takes its token from that row of the sampler's tokens as the previous step left them."""
         profiling = self.profiler is not None          # (a graph cannot be cut into ops: profiled steps are eager)
-        bucket = self._graph_bucket(segments) if (allow_graph and self.cfg.cuda_graphs and sample and not profiling) else 0
+        graphs = allow_graph and self.cfg.cuda_graphs and sample and not profiling
+        bucket = self._graph_bucket(segments) if graphs else 0
+        chunk = self._chunk_key(segments) if (graphs and not bucket) else None
         ctx = self.builder.build(segments, pad_to=bucket)
         if profiling:
             single = sum(1 for s in segments if len(s.tokens) == 1)
             ctx.profiler = self.profiler
             self.profiler.begin("decode" if single == len(segments) else ("prefill" if single == 0 else "mixed"))
-        if bucket:
-            key = (bucket, self.model.decode_variants(ctx))
+        if bucket or chunk is not None:
+            key = (bucket, self.model.decode_variants(ctx)) if bucket else chunk
             g = self._graphs.get(key)
             if g is None:
                 g = self._capture(key, ctx)
@@ -191,7 +194,20 @@ class ModelRunner:
         # more sequences than the largest bucket within the limit: the limit itself is the last bucket
         return self.cfg.max_num_seqs if n <= self.cfg.max_num_seqs <= GRAPH_MAX_ROWS else 0
 
-    def _capture(self, key: Tuple[int, Tuple[int, ...]], ctx: StepContext) -> torch.cuda.CUDAGraph:
+    def _chunk_key(self, segments: Sequence[Segment]) -> Optional[tuple]:
+        """The key of the CUDA graph of a step that is ONE full portion of a prompt (as many tokens as a step
+        takes, which is what every step but the last of a long prompt is, and the whole step of a prompt of
+        exactly that length), or None.  Such steps all launch the same kernels with the same arguments: where
+        the portion starts, its pages and the wanted row are in the step's metadata on the device."""
+        if len(segments) != 1 or self.states.pools:
+            return None
+        s = segments[0]
+        n = len(s.tokens)
+        if n != self.cfg.max_num_batched_tokens or n < 128 or s.src_row >= 0 or len(s.want) > 1:
+            return None
+        return ("portion", n, len(s.want))
+
+    def _capture(self, key: tuple, ctx: StepContext) -> torch.cuda.CUDAGraph:
         # The graph always resolves device-fed ids (token_src is -1 where there are none),
         # so one graph serves steps with and without them.  The step runs once eagerly
         # (compiles kernels, sizes workspaces), is captured, and the first replay runs it

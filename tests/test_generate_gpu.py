@@ -285,3 +285,44 @@ def test_logits_of_generation_with_graphs_and_tokens_fed_on_the_device(name, dty
         assert [int(g.argmax()) for g in got] == o["output_ids"]
     assert eng.runner.cache.num_open() == 0
     eng.runner.cache.check_invariants()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_full_prompt_portions_replay_one_graph(dtype, tmp_path):
+    """Steps that are one full portion of a prompt (as many tokens as the engine takes a step) are one CUDA
+    graph per number of wanted rows: captured for the first portion, replayed for the next two, which start
+    later, lie in other pages and attend to a cached past.  Logits against the plain implementation, and
+    the same as without graphs."""
+    from gpu_utils import check_logits, engine_for, make_model
+    cfg = C.TINY_A
+    d, w = make_model(tmp_path, cfg, seed=71, sharpen=6.0 if dtype == "float32" else 3.0)
+    V = cfg["vocab_size"]
+    long = random_tokens(V, 3 * 128 + 20, 7)
+    short = random_tokens(V, 128, 8)
+    got = {}
+    for graphs in (True, False):
+        eng = engine_for(d, dtype, cuda_graphs=graphs, async_scheduling=False, max_num_seqs=2,
+                         max_num_batched_tokens=128, kv_cache_tokens=1024, max_seq_len=512)
+        rows = []
+        for i in range(3):                               # full portions; the third wants its last row
+            out = eng.step_tokens([("a", long[128 * i:128 * (i + 1)], [127] if i == 2 else [])], graphs=True)
+            rows.append(out.cpu().numpy())
+        rows.append(eng.step_tokens([("a", long[384:], [0, 19])], graphs=True).cpu().numpy())     # the rest: eager
+        rows.append(eng.step_tokens([("b", short, [127])], graphs=True).cpu().numpy())
+        got[graphs] = rows
+        if graphs:
+            keys = sorted(k for k in eng.runner._graphs if k[0] == "portion")
+            assert keys == [("portion", 128, 0), ("portion", 128, 1)], keys
+            assert eng.runner.num_graph_steps == 4
+        else:
+            assert eng.runner.num_graph_steps == 0
+        eng.runner.check_status()
+        eng.close_request("a")
+        eng.close_request("b")
+        eng.runner.cache.check_invariants()
+    a_rows = np.concatenate([got[True][2], got[True][3]])
+    check_logits(a_rows, cfg, w, long, dtype, rows=[383, 384, 403])
+    check_logits(got[True][4], cfg, w, short, dtype, rows=[127])
+    if dtype == "float32":
+        for x, y in zip(got[True], got[False]):
+            assert np.array_equal(x, y)
