@@ -326,3 +326,17 @@ def test_full_prompt_portions_replay_one_graph(dtype, tmp_path):
     if dtype == "float32":
         for x, y in zip(got[True], got[False]):
             assert np.array_equal(x, y)
+
+
+def test_generation_of_a_long_prompt_replays_the_portion_graph(models):
+    """Through the scheduler (asynchronous, graphs on): a 400-token prompt in an engine of 128 tokens a step
+    runs three full portions as one CUDA graph before its short rest; the tokens are the plain greedy ones."""
+    from redline_b200.engine.engine import Engine
+    d, w = models["tiny_a"]
+    prompt = random_tokens(512, 400, 5)
+    eng = Engine(d, dtype="float32", max_num_seqs=2, max_num_batched_tokens=128, max_seq_len=512, kv_cache_tokens=1024,
+                 cuda_graphs=True, async_scheduling=True)
+    out = eng.generate([prompt], max_new_tokens=10, ignore_eos=True)[0]
+    assert ("portion", 128, 0) in eng.runner._graphs
+    assert out["output_ids"] == P.greedy_generate(P.plain_config(C.TINY_A), w, prompt, 10)
+    eng.runner.check_status()
