@@ -6,9 +6,10 @@
 // mma.sync.m16n8k16.  What differs is who gets which keys and how the partial results meet.  The live keys
 // of a row are cut into as many equal runs of sub-blocks as the row's cluster has warps (CTAs of the
 // cluster in rank order, warps in order: runs in the order of the keys).  At the end every warp leaves its
-// (max, denominator, numerators) in its own, then idle, ring; the CTA adds its warps' in order; the cluster
-// meets at its hardware barrier; the first CTA adds the CTAs' sums in order, reading them through
-// distributed shared memory, and writes the row.  Nothing goes through global memory, nothing is counted,
+// (max, denominator, numerators) in its own, then idle, ring; the CTA adds its warps' in order and puts the
+// sums into a slot of its own in the shared memory of the cluster's first CTA (a store through distributed
+// shared memory); the cluster meets at its hardware barrier; the first CTA adds the slots in order and
+// writes the row.  Nothing goes through global memory, nothing is counted,
 // nothing waits on a flag: the streaming kernel spends 8 of its 19 microseconds at batch 8 x 4,096 keys on
 // exactly that.
 //
@@ -34,14 +35,16 @@ namespace rl {
 constexpr int kRowsWarps = kStreamWarps;
 constexpr int kRowsThreads = kRowsWarps * 32;
 
+// The largest cluster: what shared memory has room for beside the rings (the first CTA keeps a slot for the
+// sums of every other CTA of its cluster).
+constexpr int kRowsMaxCluster = (kD == 64) ? 8 : 4;
 struct RowsShared {
-  float cta_o[16][kD];      // this CTA's numerators, head by head
-  float cta_ml[16][2];      // (max in log2 units, denominator); an empty CTA leaves (-inf, 0)
+  float cta_o[kRowsMaxCluster][16][kD];      // slot c: the numerators of CTA c of the cluster, head by head
+  float cta_ml[kRowsMaxCluster][16][2];      // (max in log2 units, denominator); an empty CTA leaves (-inf, 0)
 };
 constexpr int kRowsLd = kD + 4;        // floats per head in a warp's partial result: numerators, max, denominator
 static_assert(16 * kRowsLd * 4 <= 2 * kStreamStageBytes, "a warp's partial result lies in its own ring");
 constexpr size_t kRowsSmem = static_cast<size_t>(kRowsWarps) * 2 * kStreamStageBytes + sizeof(RowsShared) + 16;
-constexpr int kRowsMaxCluster = 8;
 
 __device__ __forceinline__ uint32_t rows_cluster_rank() {
   uint32_t r;
@@ -57,13 +60,11 @@ __device__ __forceinline__ void rows_cluster_barrier() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-// Two floats at a shared-memory address of this CTA's layout, read from CTA `rank` of the cluster.
-__device__ __forceinline__ float2 rows_ld_cluster(const float* p, uint32_t rank) {
+// Two floats to a shared-memory address of this CTA's layout in CTA `rank` of the cluster.
+__device__ __forceinline__ void rows_st_cluster(float* p, uint32_t rank, float2 v) {
   uint32_t remote;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32s(p)), "r"(rank));
-  float2 v;
-  asm volatile("ld.shared::cluster.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(remote));
-  return v;
+  asm volatile("st.shared::cluster.v2.f32 [%0], {%1, %2};" ::"r"(remote), "f"(v.x), "f"(v.y) : "memory");
 }
 
 // HI: groups of more than 8 heads (rows g + 8 of the MMA tile are in use).
@@ -441,39 +442,40 @@ decode_attn_rows_kernel(const DecodeArgs<bf16> a, int nrows, int groups, const D
       n0 += f * v.x;
       n1 += f * v.y;
     }
-    *reinterpret_cast<float2*>(&sh->cta_o[r][d]) = make_float2(n0, n1);
-    if (d == 0) *reinterpret_cast<float2*>(&sh->cta_ml[r][0]) = make_float2(m, den);
+    // into slot `rank` of the cluster's first CTA (its own slot 0 for that CTA itself)
+    if (rank == 0) {
+      *reinterpret_cast<float2*>(&sh->cta_o[0][r][d]) = make_float2(n0, n1);
+      if (d == 0) *reinterpret_cast<float2*>(&sh->cta_ml[0][r][0]) = make_float2(m, den);
+    } else {
+      rows_st_cluster(&sh->cta_o[rank][r][d], 0, make_float2(n0, n1));
+      if (d == 0) rows_st_cluster(&sh->cta_ml[rank][r][0], 0, make_float2(m, den));
+    }
   }
-  // ---- the cluster's CTAs in order, by the first one
+  // ---- the cluster's CTAs in order, by the first one, from its own shared memory (the barrier's release and
+  // acquire make the other CTAs' stores visible there); the others are done
   rows_cluster_barrier();
   if (rank == 0) {
     for (int idx = threadIdx.x; idx < G * (kD / 2); idx += kRowsThreads) {
       const int r = idx / (kD / 2), d = (idx - r * (kD / 2)) * 2;
-      float2 ml[kRowsMaxCluster], v[kRowsMaxCluster];
-#pragma unroll
-      for (int c = 0; c < kRowsMaxCluster; ++c)
-        if (c < csize) {
-          ml[c] = rows_ld_cluster(&sh->cta_ml[r][0], c);
-          v[c] = rows_ld_cluster(&sh->cta_o[r][d], c);
-        }
       float m = -INFINITY;
 #pragma unroll
       for (int c = 0; c < kRowsMaxCluster; ++c)
-        if (c < csize) m = fmaxf(m, ml[c].x);
+        if (c < csize) m = fmaxf(m, sh->cta_ml[c][r][0]);
       float den = 0.f, n0 = 0.f, n1 = 0.f;
 #pragma unroll
       for (int c = 0; c < kRowsMaxCluster; ++c)
         if (c < csize) {
-          const float f = ml[c].x == -INFINITY ? 0.f : ex2_approx(ml[c].x - m);
-          den += f * ml[c].y;
-          n0 += f * v[c].x;
-          n1 += f * v[c].y;
+          const float mc = sh->cta_ml[c][r][0];
+          const float f = mc == -INFINITY ? 0.f : ex2_approx(mc - m);
+          const float2 v = *reinterpret_cast<const float2*>(&sh->cta_o[c][r][d]);
+          den += f * sh->cta_ml[c][r][1];
+          n0 += f * v.x;
+          n1 += f * v.y;
         }
       const __nv_bfloat162 hh = __floats2bfloat162_rn(n0 / den, n1 / den);
       *reinterpret_cast<__nv_bfloat162*>(a.out + static_cast<size_t>(tok) * a.out_stride + (kvh * G + r) * kD + d) = hh;
     }
   }
-  rows_cluster_barrier();       // no CTA leaves, or goes on to its next row, while its sums may still be read
   }
 }
 
